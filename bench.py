@@ -1,0 +1,329 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-aggregation hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the path over the workload's graph: Y = Â·H (the forward
+aggregation of a GraphSum layer).  Rank 0 prints ONE JSON line.  Throughput is in
+nnz·F per second (one multiply-add per stored nonzero per feature).
+
+Workloads (all synthetic, seeded):
+  c2       R-MAT scale 20, edge factor 16, symmetrised, +I, F=64   (single-GPU headline)
+  rmat26   R-MAT scale 26, edge factor 16, directed, +I, F=32
+  custom   --scale/--edge-factor/--features/--symmetrise
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+WORKLOADS = {
+    "c2": dict(scale=20, edge_factor=16, features=64, symmetrise=True, seed=20261127),
+    "rmat26": dict(scale=26, edge_factor=16, features=32, symmetrise=False, seed=20261130),
+    "rmat22": dict(scale=22, edge_factor=16, features=32, symmetrise=False, seed=20261131),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--scale", type=int)
+    ap.add_argument("--edge-factor", type=int, default=16)
+    ap.add_argument("--features", type=int)
+    ap.add_argument("--symmetrise", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cusparse", action="store_true")
+    return ap.parse_args()
+
+
+def workload_config(args):
+    if args.workload == "custom":
+        return dict(scale=args.scale, edge_factor=args.edge_factor, features=args.features,
+                    symmetrise=args.symmetrise, seed=20261199)
+    cfg = dict(WORKLOADS[args.workload])
+    if args.features:
+        cfg["features"] = args.features
+    return cfg
+
+
+def build_graph(cfg, device):
+    """CSR by source, global degrees (int32 tensors on `device`)."""
+    from drone_b200 import graphgen as gg
+    n, u, v = gg.rmat_graph(cfg["scale"], cfg["edge_factor"], seed=cfg["seed"], device=device,
+                            symmetrise=cfg["symmetrise"], self_loops="add")
+    index, dst = gg.csr_by_source(u, v, n)
+    in_deg, out_deg = gg.degrees(u, v, n)
+    del u, v
+    return n, index, dst, in_deg, out_deg
+
+
+def algorithmic_bytes(n, nnz, f):
+    """Each array touched once: int32 index + fp32 value per nonzero, row pointers, H read, Y written."""
+    return 8 * nnz + 4 * (n + 1) + 8 * n * f
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index=0, period=0.05):
+        super().__init__(daemon=True)
+        self.period = period
+        self.samples = []
+        self.reasons = set()
+        self.stop_flag = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception as e:  # no NVML: report that instead of clocks
+            self.err = repr(e)
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def finish(self):
+        self.stop_flag.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "NVML unavailable: " + self.err}
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": float(self.max_mhz), "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def cpu_spmm_baseline(index, dst, val, f, seed, budget_s=12.0):
+    """Times the oracle's float CSR product on all host threads (bounded: whole workload, few repeats)."""
+    from oracle import oracle
+    oracle.build()
+    n = len(index) - 1
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, f), dtype=np.float32)
+    y = np.empty((n, f), np.float32)
+    threads = oracle.max_threads()
+    oracle.spmm_csr_f32(index, dst, val, x, threads=threads, out=y)  # warm-up / page-in
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - t_start < budget_s and len(times) < 20):
+        t0 = time.perf_counter()
+        oracle.spmm_csr_f32(index, dst, val, x, threads=threads, out=y)
+        times.append(time.perf_counter() - t0)
+    return times, threads
+
+
+def run_reference(args, cfg):
+    """The path on the host cores: the oracle's OpenMP CSR product (the reference's own CPU job is a Go
+    program that cannot be built here; its GPU path needs cuSPARSE, which is timed separately)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    device = torch.device("cuda:0") if torch.cuda.is_available() else torch.device("cpu")
+    n, index, dst, in_deg, out_deg = build_graph(cfg, device)
+    from oracle import oracle
+    oracle.build()
+    index_h, dst_h = index.cpu().numpy(), dst.cpu().numpy()
+    val = oracle.csr_values_f32(index_h, dst_h, in_deg.cpu().numpy(), out_deg.cpu().numpy())
+    nnz, f = len(dst_h), cfg["features"]
+    rng = np.random.default_rng(cfg["seed"])
+    x = rng.standard_normal((n, f), dtype=np.float32)
+    y = np.empty((n, f), np.float32)
+    threads = oracle.max_threads()
+    for _ in range(max(args.warmup, 1)):
+        oracle.spmm_csr_f32(index_h, dst_h, val, x, threads=threads, out=y)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.spmm_csr_f32(index_h, dst_h, val, x, threads=threads, out=y)
+    dt = time.perf_counter() - t0
+    value = args.steps * nnz * f / dt
+    line = {
+        "impl": "reference", "metric": "spmm_nnzF_per_s", "value": value, "unit": "nnz*F/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_descr(args, cfg, n, nnz),
+        "cpu_baseline": {"value": value, "unit": "nnz*F/s", "cores": threads, "kind": "port",
+                         "sample": "whole workload, one CSR SpMM per step, all host threads (OpenMP row-parallel)"},
+        "e2e": {"value": value, "unit": "nnz*F/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_descr(args, cfg, n, nnz):
+    return {"workload": "%s: R-MAT scale %d ef %d%s +I, Y = A_hat * H, F=%d" % (
+        args.workload, cfg["scale"], cfg["edge_factor"], " symmetrised" if cfg["symmetrise"] else " directed",
+        cfg["features"]), "vertices": n, "nnz": nnz, "features": cfg["features"],
+        "l2_policy": "operands rotate over 3 buffer sets; CSR + H + Y exceed the 126 MB L2"}
+
+
+def run_ours(args, cfg):
+    import drone_b200 as db
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the aggregation path has no CPU fallback")
+    if world > 1:
+        raise SystemExit("bench.py: multi-GPU path not wired yet")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    lib = db.lib()
+
+    n, index, dst, in_deg, out_deg = build_graph(cfg, device)
+    nnz, f = dst.numel(), cfg["features"]
+    plan = db.AggregationPlan(index, dst, in_degree=in_deg, out_degree=out_deg, orientations=db.PLAN_AT)
+    st = plan.stats()
+    nbuf = 3
+    gen = torch.Generator(device=device)
+    gen.manual_seed(cfg["seed"])
+    xs = [torch.randn((n, f), device=device, generator=gen) for _ in range(nbuf)]
+    ys = [torch.empty((n, f), device=device) for _ in range(nbuf)]
+
+    for i in range(max(args.warmup, 3)):
+        plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(index=local_rank)
+    sampler.start()
+    launches0 = lib.drone_kernel_launch_count()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    torch.cuda.synchronize()
+    evs[0].record()
+    for i in range(args.steps):
+        plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    launches = lib.drone_kernel_launch_count() - launches0
+    total_ms = evs[0].elapsed_time(evs[-1])
+    per_step = np.array([evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)])
+    clocks = sampler.finish()
+
+    ms = total_ms / args.steps
+    value = nnz * f / (ms * 1e-3)
+    b_alg = algorithmic_bytes(n, nnz, f)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    achieved = b_alg / (ms * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get(args.workload)
+
+    # end to end: host operands through the C ABI, copies inside the timed region
+    xh = torch.empty((n, f), dtype=torch.float32).pin_memory()
+    yh = torch.empty((n, f), dtype=torch.float32).pin_memory()
+    xh.copy_(xs[0])
+    plan.spmm_host(db.OP_AT, xh, yh)
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        plan.spmm_host(db.OP_AT, xh, yh)
+    e2e_s = (time.perf_counter() - t0) / args.e2e_steps
+    checksum = float(yh[:1024].double().sum())
+    e2e = {"value": nnz * f / e2e_s, "unit": "nnz*F/s", "h2d_bytes_per_step": 4 * n * f,
+           "d2h_bytes_per_step": 4 * n * f, "ms_per_step": 1e3 * e2e_s, "steps": args.e2e_steps,
+           "checksum": checksum}
+
+    line = {
+        "metric": "spmm_nnzF_per_s", "value": value, "unit": "nnz*F/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_descr(args, cfg, n, nnz),
+        "ms_per_step_median": float(np.median(per_step)), "ms_per_step_min": float(per_step.min()),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes": b_alg,
+                     "kernel": "one drone_spmm call = spmm_short_rows + spmm_chunks + spmm_reduce_partials"},
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        "plan": {"short_row_limit": st.short_row_limit, "chunk_nnz": st.chunk_nnz,
+                 "long_rows": st.n_long_rows[1], "chunks": st.n_chunks[1], "split_rows": st.n_split_rows[1],
+                 "partials": st.n_partials[1]},
+    }
+
+    if not args.no_cusparse:
+        try:
+            from baseline import cusparse_ref
+            rp, co, va = plan.csr(db.OP_AT)
+            res = {}
+            for alg, name in ((0, "ALG_DEFAULT"), (2, "CSR_ALG2"), (3, "CSR_ALG3")):
+                ref = cusparse_ref.CusparseSpmm(rp, co, va, xs[0], ys[0], alg=alg)
+                for _ in range(3):
+                    ref.run()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = max(3, min(args.steps, 10))
+                e0.record()
+                for _ in range(reps):
+                    ref.run()
+                e1.record()
+                torch.cuda.synchronize()
+                t = e0.elapsed_time(e1) / reps
+                res[name] = {"ms": t, "nnzF_per_s": nnz * f / (t * 1e-3), "buffer_bytes": ref.buffer_bytes()}
+                ref.close()
+            line["cusparse"] = res
+        except Exception as e:  # the head-to-head is informative, never fatal
+            line["cusparse"] = {"error": repr(e)}
+
+    if not args.no_cpu_baseline:
+        from oracle import oracle
+        index_h, dst_h = index.cpu().numpy(), dst.cpu().numpy()
+        val_h = plan.csr(db.OP_AT)
+        times, threads = cpu_spmm_baseline(val_h[0].cpu().numpy(), val_h[1].cpu().numpy(), val_h[2].cpu().numpy(), f,
+                                           cfg["seed"])
+        best = min(times)
+        line["cpu_baseline"] = {"value": nnz * f / best, "unit": "nnz*F/s", "cores": threads, "kind": "port",
+                                "sample": "whole workload, best of %d runs of the oracle's OpenMP float CSR SpMM"
+                                          % len(times), "ms": 1e3 * best}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    cfg = workload_config(args)
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,81 @@
+"""ctypes binding of libdrone_b200.so (the C ABI declared in include/drone_b200.h).
+
+Loading fails loudly when the library is missing: there is no CPU or PyTorch
+fallback for any entry point.
+"""
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "lib", "libdrone_b200.so")
+
+OP_A = 0
+OP_AT = 1
+PLAN_A = 1
+PLAN_AT = 2
+PLAN_BOTH = 3
+
+
+class DroneError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__("drone_b200 error %d: %s" % (code, message))
+        self.code = code
+
+
+class PlanStats(C.Structure):
+    _fields_ = [
+        ("n_rows", C.c_int),
+        ("nnz", C.c_int),
+        ("short_row_limit", C.c_int),
+        ("chunk_nnz", C.c_int),
+        ("n_long_rows", C.c_int * 2),
+        ("n_chunks", C.c_int * 2),
+        ("n_split_rows", C.c_int * 2),
+        ("n_partials", C.c_int * 2),
+        ("scratch_bytes", C.c_longlong),
+    ]
+
+
+_lib = None
+
+
+def _declare(lib):
+    vp, i, f, ll = C.c_void_p, C.c_int, C.c_float, C.c_longlong
+    sigs = {
+        "drone_version": (i, []),
+        "drone_last_error": (C.c_char_p, []),
+        "drone_kernel_launch_count": (ll, []),
+        "drone_compute_csr_values": (i, [vp, vp, vp, vp, i, vp, vp]),
+        "drone_plan_create": (i, [C.POINTER(vp), i, i, vp, vp, vp, vp, vp, i, vp]),
+        "drone_plan_destroy": (i, [vp]),
+        "drone_plan_get_stats": (i, [vp, C.POINTER(PlanStats)]),
+        "drone_plan_get_csr": (i, [vp, i, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
+        "drone_spmm": (i, [vp, i, i, vp, i, vp, i, vp]),
+        "drone_spmm_host": (i, [vp, i, i, vp, vp]),
+        "drone_host_alloc": (i, [C.POINTER(vp), C.c_size_t]),
+        "drone_host_free": (i, [vp]),
+        "drone_rmat_edges": (i, [i, ll, C.c_ulonglong, C.c_double, C.c_double, C.c_double, ll, vp, vp, vp]),
+        "drone_rmat_edges_host": (i, [i, ll, C.c_ulonglong, C.c_double, C.c_double, C.c_double, ll, vp, vp]),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+
+
+def lib():
+    """The loaded library.  Raises if it has not been built (python -m drone_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "drone_b200: %s is missing. Build it with `python -m drone_b200.build`; "
+                "there is no fallback path." % LIB_PATH)
+        _lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+        _declare(_lib)
+    return _lib
+
+
+def check(code):
+    if code != 0:
+        raise DroneError(code, lib().drone_last_error().decode("utf-8", "replace"))

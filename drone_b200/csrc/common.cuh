@@ -1,0 +1,52 @@
+// Shared host-side helpers of the library: status codes, the per-thread error
+// message, CUDA call checking and the launch counter.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/drone_b200.h"
+
+namespace drone {
+
+// Message of the last failing call on this thread; read by drone_last_error().
+char *last_error_buffer();
+
+int set_error(int code, const char *fmt, ...);
+
+extern std::atomic<long long> g_kernel_launches;
+
+inline void count_launch(int n = 1) { g_kernel_launches.fetch_add(n, std::memory_order_relaxed); }
+
+inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+}  // namespace drone
+
+// Evaluate a CUDA runtime call; on failure record the message and return DRONE_E_CUDA
+// from the enclosing function.
+#define DRONE_CUDA(call)                                                              \
+    do {                                                                              \
+        cudaError_t err__ = (call);                                                   \
+        if (err__ != cudaSuccess)                                                     \
+            return drone::set_error(DRONE_E_CUDA, "%s failed at %s:%d: %s", #call,    \
+                                    __FILE__, __LINE__, cudaGetErrorString(err__));   \
+    } while (0)
+
+// After a kernel launch: pick up launch-configuration errors without synchronising.
+#define DRONE_LAUNCH_CHECK(name)                                                      \
+    do {                                                                              \
+        cudaError_t err__ = cudaGetLastError();                                       \
+        if (err__ != cudaSuccess)                                                     \
+            return drone::set_error(DRONE_E_CUDA, "launch of %s failed at %s:%d: %s", \
+                                    name, __FILE__, __LINE__,                         \
+                                    cudaGetErrorString(err__));                       \
+        drone::count_launch();                                                        \
+    } while (0)
+
+#define DRONE_REQUIRE(cond, ...)                                       \
+    do {                                                               \
+        if (!(cond)) return drone::set_error(DRONE_E_INVALID, __VA_ARGS__); \
+    } while (0)

@@ -1,0 +1,434 @@
+// Plan construction: coefficient kernel, transposed CSR, and the split of rows
+// into short rows and fixed-size chunks of long rows.  Everything here runs once
+// per graph; none of it is on the per-layer path.
+#include "plan.cuh"
+
+#include <cub/cub.cuh>
+#include <cstdlib>
+#include <new>
+
+namespace drone {
+
+static thread_local char t_error[512];
+std::atomic<long long> g_kernel_launches{0};
+
+char *last_error_buffer() { return t_error; }
+
+int set_error(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof(t_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+// ---------------------------------------------------------------------------
+// kernels
+// ---------------------------------------------------------------------------
+
+// values[i] = 1/sqrt(outDeg[u]*inDeg[v]) for edge i = u->v, one warp per source
+// row.  The arithmetic follows the reference expression literally
+// (cuda_gcn/src/cuda/cuda_kernel.cu:151): the degree product is formed in
+// double, narrowed to float for sqrtf, and the reciprocal is a double division
+// narrowed to float on the store.
+__global__ void csr_values_kernel(const int *__restrict__ index, const int *__restrict__ dst,
+                                  const int *__restrict__ in_deg, const int *__restrict__ out_deg,
+                                  int n_rows, float *__restrict__ values) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+    for (int u = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; u < n_rows; u += warps_per_grid) {
+        const int s = index[u], e = index[u + 1];
+        const double od = 1.0 * out_deg[u];
+        for (int i = s + lane; i < e; i += 32) {
+            const int v = dst[i];
+            const float root = sqrtf((float)(od * in_deg[v]));
+            values[i] = (float)(1.0 / root);
+        }
+    }
+}
+
+// src[k] = row that owns nonzero k (upper bound search in rowptr).
+__global__ void expand_rows_kernel(const int *__restrict__ rowptr, int n_rows, int nnz,
+                                   int *__restrict__ src) {
+    for (long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x; k < nnz;
+         k += (long long)gridDim.x * blockDim.x) {
+        int lo = 0, hi = n_rows;  // find the last row with rowptr[row] <= k
+        while (hi - lo > 1) {
+            const int mid = lo + ((hi - lo) >> 1);
+            if (rowptr[mid] <= (int)k) lo = mid; else hi = mid;
+        }
+        src[k] = lo;
+    }
+}
+
+__global__ void histogram_kernel(const int *__restrict__ keys, int n, int *__restrict__ counts) {
+    for (long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x; k < n;
+         k += (long long)gridDim.x * blockDim.x)
+        atomicAdd(counts + keys[k], 1);
+}
+
+// colT[i] = src[perm[i]], valT[i] = val[perm[i]]
+__global__ void gather_transposed_kernel(const int *__restrict__ perm, const int *__restrict__ src,
+                                         const float *__restrict__ val, int nnz,
+                                         int *__restrict__ col_t, float *__restrict__ val_t) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nnz;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int p = perm[i];
+        col_t[i] = src[p];
+        val_t[i] = val[p];
+    }
+}
+
+__global__ void iota_kernel(int *a, int n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        a[i] = (int)i;
+}
+
+// Per row: number of chunks (0 for short rows), number of partial slots, split flag.
+__global__ void count_chunks_kernel(const int *__restrict__ rowptr, int n_rows, int short_limit,
+                                    int chunk_nnz, int *__restrict__ n_chunks,
+                                    int *__restrict__ n_slots, int *__restrict__ is_split,
+                                    int *__restrict__ is_long) {
+    for (long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x; r <= n_rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        int c = 0;
+        if (r < n_rows) {
+            const int deg = rowptr[r + 1] - rowptr[r];
+            if (deg > short_limit) c = (deg + chunk_nnz - 1) / chunk_nnz;
+        }
+        n_chunks[r] = c;
+        n_slots[r] = c > 1 ? c : 0;
+        is_split[r] = c > 1 ? 1 : 0;
+        is_long[r] = c > 0 ? 1 : 0;
+    }
+}
+
+__global__ void fill_chunks_kernel(const int *__restrict__ rowptr, int n_rows, int chunk_nnz,
+                                   const int *__restrict__ chunk_off, const int *__restrict__ slot_off,
+                                   const int *__restrict__ split_off, Chunk *__restrict__ chunks,
+                                   SplitRow *__restrict__ split) {
+    for (long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x; r < n_rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        const int nc = chunk_off[r + 1] - chunk_off[r];
+        if (nc == 0) continue;
+        const int s = rowptr[r], e = rowptr[r + 1];
+        const int c0 = chunk_off[r];
+        const int p0 = slot_off[r];
+        for (int c = 0; c < nc; ++c) {
+            Chunk ch;
+            ch.row = (int)r;
+            ch.k0 = s + c * chunk_nnz;
+            ch.len = min(chunk_nnz, e - ch.k0);
+            ch.slot = nc > 1 ? p0 + c : -1;
+            chunks[c0 + c] = ch;
+        }
+        if (nc > 1) {
+            SplitRow sr;
+            sr.row = (int)r;
+            sr.slot0 = p0;
+            sr.nslots = nc;
+            sr.pad = 0;
+            split[split_off[r]] = sr;
+        }
+    }
+}
+
+__global__ void max_nslots_kernel(const SplitRow *__restrict__ split, int n, int *out) {
+    int m = 0;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        m = max(m, split[i].nslots);
+    atomicMax(out, m);
+}
+
+static inline int grid_for(long long n, int block = 256, int cap = 148 * 32) {
+    long long g = (n + block - 1) / block;
+    if (g < 1) g = 1;
+    if (g > cap) g = cap;
+    return (int)g;
+}
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+
+static int env_int(const char *name, int dflt) {
+    const char *s = getenv(name);
+    if (!s || !*s) return dflt;
+    const int v = atoi(s);
+    return v > 0 ? v : dflt;
+}
+
+static void free_side(Side &s) {
+    cudaFree(s.rowptr);
+    cudaFree(s.col);
+    cudaFree(s.val);
+    cudaFree(s.chunks);
+    cudaFree(s.split);
+    s = Side();
+}
+
+// Build side[DRONE_OP_AT] from side[DRONE_OP_A] (arrays of A must be on the device).
+static int build_transpose(drone_plan *p, cudaStream_t st) {
+    const Side &a = p->side[DRONE_OP_A];
+    Side &t = p->side[DRONE_OP_AT];
+    const int n = p->n_rows, nnz = p->nnz;
+    DRONE_CUDA(cudaMalloc(&t.rowptr, sizeof(int) * (size_t)(n + 1)));
+    DRONE_CUDA(cudaMalloc(&t.col, sizeof(int) * (size_t)(nnz > 0 ? nnz : 1)));
+    DRONE_CUDA(cudaMalloc(&t.val, sizeof(float) * (size_t)(nnz > 0 ? nnz : 1)));
+
+    // row pointer of the transpose: histogram of destinations, then exclusive scan
+    int *counts = nullptr;
+    DRONE_CUDA(cudaMalloc(&counts, sizeof(int) * (size_t)(n + 1)));
+    DRONE_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)(n + 1), st));
+    if (nnz > 0) {
+        histogram_kernel<<<grid_for(nnz), 256, 0, st>>>(a.col, nnz, counts);
+        DRONE_LAUNCH_CHECK("histogram_kernel");
+    }
+    size_t tmp_bytes = 0;
+    void *tmp = nullptr;
+    DRONE_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, counts, t.rowptr, n + 1, st));
+    DRONE_CUDA(cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1));
+    DRONE_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, counts, t.rowptr, n + 1, st));
+    count_launch();
+    DRONE_CUDA(cudaStreamSynchronize(st));
+    cudaFree(tmp);
+    cudaFree(counts);
+
+    if (nnz > 0) {
+        // stable sort of edge ids by destination: sources stay ascending inside a row
+        int *src = nullptr, *keys_alt = nullptr, *perm = nullptr, *perm_alt = nullptr, *keys = nullptr;
+        DRONE_CUDA(cudaMalloc(&src, sizeof(int) * (size_t)nnz));
+        DRONE_CUDA(cudaMalloc(&keys, sizeof(int) * (size_t)nnz));
+        DRONE_CUDA(cudaMalloc(&keys_alt, sizeof(int) * (size_t)nnz));
+        DRONE_CUDA(cudaMalloc(&perm, sizeof(int) * (size_t)nnz));
+        DRONE_CUDA(cudaMalloc(&perm_alt, sizeof(int) * (size_t)nnz));
+        expand_rows_kernel<<<grid_for(nnz), 256, 0, st>>>(a.rowptr, n, nnz, src);
+        DRONE_LAUNCH_CHECK("expand_rows_kernel");
+        iota_kernel<<<grid_for(nnz), 256, 0, st>>>(perm, nnz);
+        DRONE_LAUNCH_CHECK("iota_kernel");
+        DRONE_CUDA(cudaMemcpyAsync(keys, a.col, sizeof(int) * (size_t)nnz, cudaMemcpyDeviceToDevice, st));
+        int end_bit = 1;
+        while (end_bit < 31 && (1LL << end_bit) < (long long)n) ++end_bit;
+        cub::DoubleBuffer<int> kb(keys, keys_alt);
+        cub::DoubleBuffer<int> vb(perm, perm_alt);
+        tmp_bytes = 0;
+        DRONE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, kb, vb, nnz, 0, end_bit, st));
+        DRONE_CUDA(cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1));
+        DRONE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tmp_bytes, kb, vb, nnz, 0, end_bit, st));
+        count_launch();
+        gather_transposed_kernel<<<grid_for(nnz), 256, 0, st>>>(vb.Current(), src, a.val, nnz, t.col, t.val);
+        DRONE_LAUNCH_CHECK("gather_transposed_kernel");
+        DRONE_CUDA(cudaStreamSynchronize(st));
+        cudaFree(tmp);
+        cudaFree(src);
+        cudaFree(keys);
+        cudaFree(keys_alt);
+        cudaFree(perm);
+        cudaFree(perm_alt);
+    }
+    return DRONE_OK;
+}
+
+// Work lists of the long rows of one orientation.
+static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
+    const int n = p->n_rows;
+    int *buf = nullptr;  // 8 arrays of n+1 ints: counts x4, offsets x4
+    const size_t stride = (size_t)(n + 1);
+    DRONE_CUDA(cudaMalloc(&buf, sizeof(int) * stride * 8));
+    int *cnt[4] = {buf, buf + stride, buf + 2 * stride, buf + 3 * stride};
+    int *off[4] = {buf + 4 * stride, buf + 5 * stride, buf + 6 * stride, buf + 7 * stride};
+    count_chunks_kernel<<<grid_for(n + 1), 256, 0, st>>>(s.rowptr, n, p->short_row_limit, p->chunk_nnz,
+                                                        cnt[0], cnt[1], cnt[2], cnt[3]);
+    DRONE_LAUNCH_CHECK("count_chunks_kernel");
+    size_t tmp_bytes = 0;
+    void *tmp = nullptr;
+    DRONE_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, cnt[0], off[0], n + 1, st));
+    DRONE_CUDA(cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1));
+    for (int i = 0; i < 4; ++i) {
+        DRONE_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, cnt[i], off[i], n + 1, st));
+        count_launch();
+    }
+    int totals[4];
+    for (int i = 0; i < 4; ++i)
+        DRONE_CUDA(cudaMemcpyAsync(&totals[i], off[i] + n, sizeof(int), cudaMemcpyDeviceToHost, st));
+    DRONE_CUDA(cudaStreamSynchronize(st));
+    s.n_chunks = totals[0];
+    s.n_partials = totals[1];
+    s.n_split_rows = totals[2];
+    s.n_long_rows = totals[3];
+    s.max_nslots = 0;
+    if (s.n_chunks > 0) {
+        DRONE_CUDA(cudaMalloc(&s.chunks, sizeof(Chunk) * (size_t)s.n_chunks));
+        DRONE_CUDA(cudaMalloc(&s.split, sizeof(SplitRow) * (size_t)(s.n_split_rows > 0 ? s.n_split_rows : 1)));
+        fill_chunks_kernel<<<grid_for(n), 256, 0, st>>>(s.rowptr, n, p->chunk_nnz, off[0], off[1], off[2],
+                                                       s.chunks, s.split);
+        DRONE_LAUNCH_CHECK("fill_chunks_kernel");
+        if (s.n_split_rows > 0) {
+            int *d_max = cnt[0];  // reuse
+            DRONE_CUDA(cudaMemsetAsync(d_max, 0, sizeof(int), st));
+            max_nslots_kernel<<<grid_for(s.n_split_rows), 256, 0, st>>>(s.split, s.n_split_rows, d_max);
+            DRONE_LAUNCH_CHECK("max_nslots_kernel");
+            DRONE_CUDA(cudaMemcpyAsync(&s.max_nslots, d_max, sizeof(int), cudaMemcpyDeviceToHost, st));
+        }
+        DRONE_CUDA(cudaStreamSynchronize(st));
+    }
+    cudaFree(tmp);
+    cudaFree(buf);
+    s.ready = true;
+    return DRONE_OK;
+}
+
+static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_index, const int *d_dst,
+                            const float *d_values, const int *d_in_degree, const int *d_out_degree,
+                            int orientations, cudaStream_t st) {
+    DRONE_CUDA(cudaGetDevice(&p->device));
+    p->n_rows = n_rows;
+    p->nnz = nnz;
+    p->short_row_limit = env_int("DRONE_SHORT_ROW_LIMIT", 32);
+    // Chunks of 256 nonzeros keep the serial work of one warp near ten microseconds;
+    // very large graphs take longer chunks so that the chunk list stays below 1% of
+    // the CSR stream.
+    p->chunk_nnz = env_int("DRONE_CHUNK_NNZ", nnz > (1 << 28) ? 1024 : 256);
+    if (p->chunk_nnz < p->short_row_limit) p->chunk_nnz = p->short_row_limit;
+
+    Side &a = p->side[DRONE_OP_A];
+    const size_t nnz_alloc = (size_t)(nnz > 0 ? nnz : 1);
+    DRONE_CUDA(cudaMalloc(&a.rowptr, sizeof(int) * (size_t)(n_rows + 1)));
+    DRONE_CUDA(cudaMalloc(&a.col, sizeof(int) * nnz_alloc));
+    DRONE_CUDA(cudaMalloc(&a.val, sizeof(float) * nnz_alloc));
+    DRONE_CUDA(cudaMemcpyAsync(a.rowptr, d_index, sizeof(int) * (size_t)(n_rows + 1), cudaMemcpyDeviceToDevice, st));
+    if (nnz > 0) {
+        DRONE_CUDA(cudaMemcpyAsync(a.col, d_dst, sizeof(int) * (size_t)nnz, cudaMemcpyDeviceToDevice, st));
+        if (d_values) {
+            DRONE_CUDA(cudaMemcpyAsync(a.val, d_values, sizeof(float) * (size_t)nnz, cudaMemcpyDeviceToDevice, st));
+        } else {
+            csr_values_kernel<<<grid_for((long long)n_rows * 32), 256, 0, st>>>(a.rowptr, a.col, d_in_degree,
+                                                                              d_out_degree, n_rows, a.val);
+            DRONE_LAUNCH_CHECK("csr_values_kernel");
+        }
+    }
+    DRONE_CUDA(cudaStreamSynchronize(st));
+
+    if (orientations & DRONE_PLAN_AT) {
+        int rc = build_transpose(p, st);
+        if (rc) return rc;
+        rc = build_work_lists(p, p->side[DRONE_OP_AT], st);
+        if (rc) return rc;
+    }
+    if (orientations & DRONE_PLAN_A) {
+        int rc = build_work_lists(p, a, st);
+        if (rc) return rc;
+    } else {
+        free_side(a);
+    }
+    return DRONE_OK;
+}
+
+}  // namespace drone
+
+using namespace drone;
+
+extern "C" {
+
+int drone_version(void) { return 1000; }
+
+const char *drone_last_error(void) { return last_error_buffer(); }
+
+long long drone_kernel_launch_count(void) { return g_kernel_launches.load(); }
+
+int drone_compute_csr_values(const int *d_index, const int *d_dst, const int *d_in_degree,
+                             const int *d_out_degree, int n_rows, float *d_values, void *stream) {
+    DRONE_REQUIRE(n_rows >= 0, "drone_compute_csr_values: n_rows=%d is negative", n_rows);
+    if (n_rows == 0) return DRONE_OK;
+    DRONE_REQUIRE(d_index && d_dst && d_in_degree && d_out_degree && d_values,
+                  "drone_compute_csr_values: NULL pointer argument");
+    csr_values_kernel<<<grid_for((long long)n_rows * 32), 256, 0, (cudaStream_t)stream>>>(
+        d_index, d_dst, d_in_degree, d_out_degree, n_rows, d_values);
+    DRONE_LAUNCH_CHECK("csr_values_kernel");
+    return DRONE_OK;
+}
+
+int drone_plan_create(drone_plan **out, int n_rows, int nnz, const int *d_index, const int *d_dst,
+                      const float *d_values, const int *d_in_degree, const int *d_out_degree,
+                      int orientations, void *stream) {
+    DRONE_REQUIRE(out != nullptr, "drone_plan_create: out is NULL");
+    *out = nullptr;
+    DRONE_REQUIRE(n_rows >= 0 && nnz >= 0, "drone_plan_create: negative size (n_rows=%d, nnz=%d)", n_rows, nnz);
+    DRONE_REQUIRE(d_index != nullptr, "drone_plan_create: d_index is NULL");
+    DRONE_REQUIRE(nnz == 0 || d_dst != nullptr, "drone_plan_create: d_dst is NULL with nnz=%d", nnz);
+    DRONE_REQUIRE(nnz == 0 || d_values != nullptr || (d_in_degree && d_out_degree),
+                  "drone_plan_create: need d_values or both degree arrays");
+    DRONE_REQUIRE((orientations & DRONE_PLAN_BOTH) != 0 && (orientations & ~DRONE_PLAN_BOTH) == 0,
+                  "drone_plan_create: orientations=%d is not a combination of DRONE_PLAN_A/AT", orientations);
+    drone_plan *p = new (std::nothrow) drone_plan();
+    if (!p) return set_error(DRONE_E_INVALID, "drone_plan_create: out of host memory");
+    const int rc = plan_create_impl(p, n_rows, nnz, d_index, d_dst, d_values, d_in_degree, d_out_degree,
+                                    orientations, (cudaStream_t)stream);
+    if (rc != DRONE_OK) {
+        drone_plan_destroy(p);
+        return rc;
+    }
+    *out = p;
+    return DRONE_OK;
+}
+
+int drone_plan_destroy(drone_plan *p) {
+    if (!p) return DRONE_OK;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(p->device);
+    free_side(p->side[0]);
+    free_side(p->side[1]);
+    cudaFree(p->scratch);
+    cudaFree(p->stage_x);
+    cudaFree(p->stage_y);
+    if (p->own_stream) cudaStreamDestroy(p->own_stream);
+    if (prev >= 0) cudaSetDevice(prev);
+    delete p;
+    return DRONE_OK;
+}
+
+int drone_plan_get_stats(const drone_plan *p, drone_plan_stats *out) {
+    DRONE_REQUIRE(p && out, "drone_plan_get_stats: NULL argument");
+    memset(out, 0, sizeof(*out));
+    out->n_rows = p->n_rows;
+    out->nnz = p->nnz;
+    out->short_row_limit = p->short_row_limit;
+    out->chunk_nnz = p->chunk_nnz;
+    for (int o = 0; o < 2; ++o) {
+        out->n_long_rows[o] = p->side[o].n_long_rows;
+        out->n_chunks[o] = p->side[o].n_chunks;
+        out->n_split_rows[o] = p->side[o].n_split_rows;
+        out->n_partials[o] = p->side[o].n_partials;
+    }
+    out->scratch_bytes = (long long)p->scratch_bytes;
+    return DRONE_OK;
+}
+
+int drone_plan_get_csr(const drone_plan *p, int orientation, const int **d_rowptr, const int **d_col,
+                       const float **d_val) {
+    DRONE_REQUIRE(p != nullptr, "drone_plan_get_csr: plan is NULL");
+    DRONE_REQUIRE(orientation == DRONE_OP_A || orientation == DRONE_OP_AT,
+                  "drone_plan_get_csr: orientation=%d", orientation);
+    const Side &s = p->side[orientation];
+    DRONE_REQUIRE(s.ready, "drone_plan_get_csr: orientation %d was not prepared by drone_plan_create", orientation);
+    if (d_rowptr) *d_rowptr = s.rowptr;
+    if (d_col) *d_col = s.col;
+    if (d_val) *d_val = s.val;
+    return DRONE_OK;
+}
+
+int drone_host_alloc(void **out, size_t bytes) {
+    DRONE_REQUIRE(out != nullptr, "drone_host_alloc: out is NULL");
+    DRONE_CUDA(cudaHostAlloc(out, bytes > 0 ? bytes : 1, cudaHostAllocDefault));
+    return DRONE_OK;
+}
+
+int drone_host_free(void *ptr) {
+    if (ptr) DRONE_CUDA(cudaFreeHost(ptr));
+    return DRONE_OK;
+}
+
+}  // extern "C"

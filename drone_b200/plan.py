@@ -1,0 +1,131 @@
+"""Host-side handle of an aggregation plan over torch device tensors.
+
+torch is used for device memory and streams only; every computation is a call
+through the C ABI (include/drone_b200.h).
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import OP_A, OP_AT, PLAN_A, PLAN_AT, PLAN_BOTH, PlanStats, check
+
+
+def _stream_ptr(stream=None):
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def _dev_i32(t, name):
+    if t is None:
+        return None
+    if not (t.is_cuda and t.dtype == torch.int32 and t.is_contiguous()):
+        raise ValueError("%s must be a contiguous int32 CUDA tensor" % name)
+    return t
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def compute_csr_values(index, dst, in_degree, out_degree, stream=None):
+    """Edge coefficients 1/sqrt(outDeg[u]*inDeg[v]) (cuda_gcn/src/cuda/cuda_kernel.cu:144-155)."""
+    index, dst = _dev_i32(index, "index"), _dev_i32(dst, "dst")
+    in_degree, out_degree = _dev_i32(in_degree, "in_degree"), _dev_i32(out_degree, "out_degree")
+    values = torch.empty(dst.numel(), dtype=torch.float32, device=dst.device)
+    with torch.cuda.device(dst.device):
+        check(_lib.lib().drone_compute_csr_values(_ptr(index), _ptr(dst), _ptr(in_degree), _ptr(out_degree),
+                                                  index.numel() - 1, _ptr(values), _stream_ptr(stream)))
+    return values
+
+
+class AggregationPlan:
+    """Plan for Y = A·X / Y = Aᵀ·X over one local subgraph given as CSR by source vertex
+    (struct Graph of cuda_gcn/src/cuda/graph.h:17-41).  Stands where CUDAGraphSum's
+    constructor sets cuSPARSE up (cuda_gcn/src/cuda/cuda_module.cu:149-202)."""
+
+    def __init__(self, index, dst, values=None, in_degree=None, out_degree=None, orientations=PLAN_BOTH,
+                 stream=None):
+        index, dst = _dev_i32(index, "index"), _dev_i32(dst, "dst")
+        in_degree, out_degree = _dev_i32(in_degree, "in_degree"), _dev_i32(out_degree, "out_degree")
+        if values is not None and not (values.is_cuda and values.dtype == torch.float32 and values.is_contiguous()):
+            raise ValueError("values must be a contiguous float32 CUDA tensor")
+        self.device = index.device
+        self.n_rows = index.numel() - 1
+        self.nnz = dst.numel()
+        self._h = C.c_void_p(0)
+        with torch.cuda.device(self.device):
+            check(_lib.lib().drone_plan_create(C.byref(self._h), self.n_rows, self.nnz, _ptr(index), _ptr(dst),
+                                               _ptr(values), _ptr(in_degree), _ptr(out_degree), int(orientations),
+                                               _stream_ptr(stream)))
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            _lib.lib().drone_plan_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def stats(self):
+        st = PlanStats()
+        check(_lib.lib().drone_plan_get_stats(self._h, C.byref(st)))
+        return st
+
+    def csr(self, orientation):
+        """(rowptr, col, val) of one orientation, copied into fresh torch tensors."""
+        rp, co, va = C.c_void_p(0), C.c_void_p(0), C.c_void_p(0)
+        check(_lib.lib().drone_plan_get_csr(self._h, orientation, C.byref(rp), C.byref(co), C.byref(va)))
+        out = []
+        for ptr, n, dt in ((rp, self.n_rows + 1, torch.int32), (co, self.nnz, torch.int32), (va, self.nnz, torch.float32)):
+            if n == 0:
+                out.append(torch.empty(0, dtype=dt, device=self.device))
+            else:
+                out.append(_view_device_memory(ptr.value, n, dt, self.device).clone())
+        return tuple(out)
+
+    def spmm(self, orientation, x, out=None, stream=None):
+        """out[r,:] = sum_k val[k]*x[col[k],:] (rows of the chosen orientation).  x: [n_rows, F] float32."""
+        if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1):
+            raise ValueError("x must be a 2-D float32 CUDA tensor with unit inner stride")
+        if x.shape[0] != self.n_rows:
+            raise ValueError("x has %d rows, plan has %d" % (x.shape[0], self.n_rows))
+        f = x.shape[1]
+        if out is None:
+            out = torch.empty((self.n_rows, f), dtype=torch.float32, device=x.device)
+        elif not (out.is_cuda and out.dtype == torch.float32 and out.shape == (self.n_rows, f) and out.stride(1) == 1):
+            raise ValueError("out must be a [n_rows, F] float32 CUDA tensor with unit inner stride")
+        ldx = x.stride(0) if self.n_rows > 1 else max(f, x.stride(0))
+        ldy = out.stride(0) if self.n_rows > 1 else max(f, out.stride(0))
+        with torch.cuda.device(self.device):
+            check(_lib.lib().drone_spmm(self._h, int(orientation), f, _ptr(x), int(ldx), _ptr(out), int(ldy),
+                                        _stream_ptr(stream)))
+        return out
+
+    def spmm_host(self, orientation, x_host, out_host):
+        """Same with host numpy/torch CPU buffers (pinned for DMA); synchronous."""
+        f = x_host.shape[1]
+        xp = x_host.data_ptr() if hasattr(x_host, "data_ptr") else x_host.ctypes.data
+        yp = out_host.data_ptr() if hasattr(out_host, "data_ptr") else out_host.ctypes.data
+        check(_lib.lib().drone_spmm_host(self._h, int(orientation), int(f), C.c_void_p(xp), C.c_void_p(yp)))
+        return out_host
+
+
+class _DeviceArray:
+    """Borrowed device memory described through the CUDA array interface."""
+
+    def __init__(self, ptr, n, typestr):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def _view_device_memory(ptr, n, dtype, device):
+    typestr = {torch.int32: "<i4", torch.float32: "<f4"}[dtype]
+    with torch.cuda.device(device):
+        return torch.as_tensor(_DeviceArray(ptr, n, typestr), device=device)

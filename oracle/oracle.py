@@ -1,0 +1,188 @@
+"""numpy-facing wrappers of the CPU oracle (oracle/drone_oracle.c, oracle/pagerank_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
+CPU-baseline / reference legs of bench.py; never by the drone_b200 package.
+Parity status is stated in the headers of the two C files.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_build", "libdrone_oracle.so")
+
+
+def build(force=False):
+    """Compile the oracle with the committed Makefile (gcc, a few seconds)."""
+    srcs = [os.path.join(_HERE, f) for f in ("drone_oracle.c", "pagerank_oracle.c", "Makefile")]
+    if force or not os.path.exists(_SO) or any(os.path.getmtime(s) > os.path.getmtime(_SO) for s in srcs):
+        subprocess.run(["make", "-C", _HERE, "-B" if force else "-s"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return _SO
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            build()
+        _lib = C.CDLL(_SO)
+        _lib.oracle_pr_drone_cpu.restype = C.c_int
+        _lib.oracle_pr_drone_cuda_f32.restype = C.c_int
+        _lib.oracle_pr_drone_cuda_f64.restype = C.c_int
+        _lib.oracle_build_graph.restype = C.c_int
+        _lib.oracle_max_threads.restype = C.c_int
+    return _lib
+
+
+def _p(a, t):
+    return a.ctypes.data_as(C.POINTER(t))
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def max_threads():
+    return int(lib().oracle_max_threads())
+
+
+def build_graph(global_v, u, v):
+    """First-seen local numbering and CSR by source (cuda_gcn/src/cuda/graph.cu:54-103).
+    Returns (n_local, g2l[global_v], l2g[n_local], index[n_local+1], dst[E])."""
+    u, v = _i32(u), _i32(v)
+    e = len(u)
+    g2l = np.empty(global_v, np.int32)
+    l2g = np.empty(global_v, np.int32)
+    index = np.empty(global_v + 1, np.int32)
+    dst = np.empty(max(e, 1), np.int32)
+    n = lib().oracle_build_graph(global_v, e, _p(u, C.c_int), _p(v, C.c_int), _p(g2l, C.c_int),
+                                 _p(l2g, C.c_int), _p(index, C.c_int), _p(dst, C.c_int))
+    return n, g2l, l2g[:n].copy(), index[:n + 1].copy(), dst[:e].copy()
+
+
+def csr_values_f32(index, dst, in_degree, out_degree):
+    index, dst, in_degree, out_degree = map(_i32, (index, dst, in_degree, out_degree))
+    n = len(index) - 1
+    values = np.empty(max(len(dst), 1), np.float32)
+    lib().oracle_csr_values_f32(_p(index, C.c_int), _p(dst, C.c_int), _p(in_degree, C.c_int),
+                                _p(out_degree, C.c_int), n, _p(values, C.c_float))
+    return values[:len(dst)]
+
+
+def csr_values_f64(index, dst, in_degree, out_degree):
+    index, dst, in_degree, out_degree = map(_i32, (index, dst, in_degree, out_degree))
+    n = len(index) - 1
+    values = np.empty(max(len(dst), 1), np.float64)
+    lib().oracle_csr_values_f64(_p(index, C.c_int), _p(dst, C.c_int), _p(in_degree, C.c_int),
+                                _p(out_degree, C.c_int), n, _p(values, C.c_double))
+    return values[:len(dst)]
+
+
+def graphsum_forward_f64(x, index, dst, values):
+    """out[v] += coef * in[u] over edges u->v (cuda_gcn/src/cuda/cuda_kernel.cu:203-218)."""
+    x = _f32(x)
+    n, dim = x.shape
+    index, dst, values = _i32(index), _i32(dst), _f32(values)
+    out = np.empty((n, dim), np.float64)
+    lib().oracle_graphsum_forward_f64(_p(x, C.c_float), _p(out, C.c_double), _p(index, C.c_int),
+                                      _p(dst, C.c_int), _p(values, C.c_float), dim, n)
+    return out
+
+
+def graphsum_backward_f64(out_grad, index, dst, values):
+    """in_grad[u] += coef * out_grad[v] over edges u->v (cuda_gcn/src/cuda/cuda_kernel.cu:236-248)."""
+    out_grad = _f32(out_grad)
+    n, dim = out_grad.shape
+    index, dst, values = _i32(index), _i32(dst), _f32(values)
+    in_grad = np.empty((n, dim), np.float64)
+    lib().oracle_graphsum_backward_f64(_p(in_grad, C.c_double), _p(out_grad, C.c_float), _p(index, C.c_int),
+                                       _p(dst, C.c_int), _p(values, C.c_float), dim, n)
+    return in_grad
+
+
+def spmm_csr_f64(rowptr, col, val, x, with_abs=False):
+    """Y = A·X for CSR A, double accumulation.  with_abs also returns sum |val*x| per output."""
+    rowptr, col, val, x = _i32(rowptr), _i32(col), _f32(val), _f32(x)
+    n = len(rowptr) - 1
+    f = x.shape[1]
+    y = np.empty((n, f), np.float64)
+    a = np.empty((n, f), np.float64) if with_abs else None
+    lib().oracle_spmm_csr_f64(n, _p(rowptr, C.c_int), _p(col, C.c_int), _p(val, C.c_float), _p(x, C.c_float),
+                              f, _p(y, C.c_double), _p(a, C.c_double) if with_abs else None, f, f)
+    return (y, a) if with_abs else y
+
+
+def spmm_csr_f32(rowptr, col, val, x, threads=0, out=None):
+    """Y = A·X in float on `threads` host threads (0 = all): the timed CPU baseline."""
+    rowptr, col, val, x = _i32(rowptr), _i32(col), _f32(val), _f32(x)
+    n = len(rowptr) - 1
+    f = x.shape[1]
+    y = out if out is not None else np.empty((n, f), np.float32)
+    lib().oracle_spmm_csr_f32(n, _p(rowptr, C.c_int), _p(col, C.c_int), _p(val, C.c_float), _p(x, C.c_float),
+                              f, _p(y, C.c_float), f, f, int(threads))
+    return y
+
+
+def transpose_csr(n_rows, n_cols, rowptr, col, val):
+    rowptr, col, val = _i32(rowptr), _i32(col), _f32(val)
+    nnz = len(col)
+    t_rowptr = np.empty(n_cols + 1, np.int32)
+    t_col = np.empty(max(nnz, 1), np.int32)
+    t_val = np.empty(max(nnz, 1), np.float32)
+    lib().oracle_transpose_csr(n_rows, n_cols, _p(rowptr, C.c_int), _p(col, C.c_int), _p(val, C.c_float),
+                               _p(t_rowptr, C.c_int), _p(t_col, C.c_int), _p(t_val, C.c_float))
+    return t_rowptr, t_col[:nnz], t_val[:nnz]
+
+
+def _parts_args(parts_u, parts_v, out_degree, owner):
+    eoff = np.zeros(len(parts_u) + 1, np.int32)
+    eoff[1:] = np.cumsum([len(a) for a in parts_u])
+    eu = _i32(np.concatenate(parts_u)) if len(parts_u) else np.zeros(0, np.int32)
+    ev = _i32(np.concatenate(parts_v)) if len(parts_v) else np.zeros(0, np.int32)
+    return eoff, eu, ev, _i32(out_degree), _i32(owner)
+
+
+def pr_drone_cpu(global_v, parts_u, parts_v, out_degree, owner, eps=0.01, max_steps=200):
+    """DRONE's CPU job "pr" over a partition (float32).  Returns (pr[global_v], supersteps, messages)."""
+    eoff, eu, ev, od, ow = _parts_args(parts_u, parts_v, out_degree, owner)
+    out = np.empty(global_v, np.float32)
+    msgs = C.c_longlong(0)
+    steps = lib().oracle_pr_drone_cpu(len(parts_u), global_v, _p(eoff, C.c_int), _p(eu, C.c_int), _p(ev, C.c_int),
+                                      _p(od, C.c_int), _p(ow, C.c_int), C.c_float(eps), int(max_steps),
+                                      _p(out, C.c_float), C.byref(msgs))
+    return out, steps, msgs.value
+
+
+def pr_drone_cuda(global_v, parts_u, parts_v, out_degree, owner, eps=1e-6, max_steps=10000, dtype=np.float32):
+    """DRONE's GPU job "pr_cuda" over a partition.  Returns (pr, supersteps, sizes[steps,4])."""
+    eoff, eu, ev, od, ow = _parts_args(parts_u, parts_v, out_degree, owner)
+    out = np.empty(global_v, dtype)
+    sizes = np.zeros((max_steps + 1, 4), np.int64)
+    if dtype == np.float32:
+        steps = lib().oracle_pr_drone_cuda_f32(len(parts_u), global_v, _p(eoff, C.c_int), _p(eu, C.c_int),
+                                               _p(ev, C.c_int), _p(od, C.c_int), _p(ow, C.c_int), C.c_float(eps),
+                                               int(max_steps), _p(out, C.c_float), _p(sizes, C.c_longlong))
+    else:
+        steps = lib().oracle_pr_drone_cuda_f64(len(parts_u), global_v, _p(eoff, C.c_int), _p(eu, C.c_int),
+                                               _p(ev, C.c_int), _p(od, C.c_int), _p(ow, C.c_int), C.c_double(eps),
+                                               int(max_steps), _p(out, C.c_double), _p(sizes, C.c_longlong))
+    return out, steps, sizes[:steps]
+
+
+def pagerank_power_f64(rowptr, col, iterations=20, damping=0.85):
+    rowptr, col = _i32(rowptr), _i32(col)
+    n = len(rowptr) - 1
+    out = np.empty(n, np.float64)
+    lib().oracle_pagerank_power_f64(n, _p(rowptr, C.c_int), _p(col, C.c_int), int(iterations), C.c_double(damping),
+                                    _p(out, C.c_double))
+    return out

@@ -1,0 +1,52 @@
+"""The shared library loads without a GPU and exports every symbol include/drone_b200.h declares."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = []
+    for fn in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        if not fn.endswith(".h"):
+            continue
+        text = open(os.path.join(ROOT, "include", fn)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names += re.findall(r"\b(drone_[a-z0-9_]+|build_graph|addMasterRoute|addMirrorRoute|getLocalVertexSize|"
+                            r"getGlobalVertexSize|loadOutDegree|PR_PEVal|PR_IncEVal)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+    import drone_b200
+    lib = drone_b200.lib()
+    names = declared_symbols()
+    assert "drone_spmm" in names and "drone_plan_create" in names
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, "declared in include/ but not exported: %s" % missing
+
+
+def test_version_and_error_string():
+    import drone_b200
+    lib = drone_b200.lib()
+    assert lib.drone_version() >= 1000
+    # an invalid call fails with a code and a message, without touching a device
+    rc = lib.drone_plan_create(None, 1, 1, None, None, None, None, None, 3, None)
+    assert rc == -1
+    assert b"out is NULL" in lib.drone_last_error()
+    h = C.c_void_p(0)
+    rc = lib.drone_plan_create(C.byref(h), -5, 0, None, None, None, None, None, 3, None)
+    assert rc == -1 and b"negative" in lib.drone_last_error()
+    rc = lib.drone_spmm(None, 0, 32, None, 32, None, 32, None)
+    assert rc == -1 and b"plan is NULL" in lib.drone_last_error()
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from drone_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libdrone_b200.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.lib()

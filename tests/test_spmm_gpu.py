@@ -1,0 +1,222 @@
+"""Parity of the CUDA aggregation (through the C ABI) with the double-precision oracle, the
+committed golden vectors, and cuSPARSE called as the reference calls it."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import drone_b200 as db
+from drone_b200 import graphgen as gg
+from helpers import ROOT, REL_TOL, assert_close_to_oracle, graph_case
+
+import make_golden
+
+pytestmark = pytest.mark.gpu
+
+WIDTHS = [1, 2, 3, 4, 31, 32, 33, 41, 47, 64, 128, 256]
+
+
+def make_plan(dev, index, dst, in_deg, out_deg, **env):
+    old = {k: os.environ.get(k) for k in env}
+    for k, v in env.items():
+        os.environ[k] = str(v)
+    try:
+        return db.AggregationPlan(torch.as_tensor(index, device=dev), torch.as_tensor(dst, device=dev),
+                                  in_degree=torch.as_tensor(in_deg, device=dev),
+                                  out_degree=torch.as_tensor(out_deg, device=dev))
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+
+
+def check_both_orientations(plan, oracle, index, dst, val, x, dev):
+    xt = torch.as_tensor(x, device=dev)
+    fwd = plan.spmm(db.OP_AT, xt).cpu().numpy()
+    bwd = plan.spmm(db.OP_A, xt).cpu().numpy()
+    n = len(index) - 1
+    t = oracle.transpose_csr(n, n, index, dst, val)
+    w_f, a_f = oracle.spmm_csr_f64(*t, x, with_abs=True)
+    w_b, a_b = oracle.spmm_csr_f64(index, dst, val, x, with_abs=True)
+    assert_close_to_oracle(fwd, w_f, a_f)
+    assert_close_to_oracle(bwd, w_b, a_b)
+    # the hand-written definition of the layer (push / pull over edges) gives the same numbers
+    np.testing.assert_allclose(w_f, oracle.graphsum_forward_f64(x, index, dst, val), rtol=0, atol=1e-12)
+    return fwd, bwd
+
+
+def test_coefficients_bit_exact(cuda_device, oracle):
+    n, u, v = gg.rmat_graph(12, 16, seed=21, symmetrise=False, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    rng = np.random.default_rng(0)
+    in_deg = rng.integers(1, 3000000, n).astype(np.int32)     # large degrees: products beyond 2^24
+    out_deg = rng.integers(1, 3000000, n).astype(np.int32)
+    want = oracle.csr_values_f32(index, dst, in_deg, out_deg)
+    got = db.compute_csr_values(torch.as_tensor(index, device=cuda_device), torch.as_tensor(dst, device=cuda_device),
+                                torch.as_tensor(in_deg, device=cuda_device),
+                                torch.as_tensor(out_deg, device=cuda_device))
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_transpose_matches_oracle(cuda_device, oracle):
+    n, u, v = gg.rmat_graph(11, 16, seed=22, symmetrise=False, self_loops="drop")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    rp, co, va = [t.cpu().numpy() for t in plan.csr(db.OP_AT)]
+    t_rp, t_co, t_va = oracle.transpose_csr(n, n, index, dst, val)
+    assert np.array_equal(rp, t_rp) and np.array_equal(co, t_co) and np.array_equal(va, t_va)
+    rp, co, va = [t.cpu().numpy() for t in plan.csr(db.OP_A)]
+    assert np.array_equal(rp, index) and np.array_equal(co, dst) and np.array_equal(va, val)
+
+
+@pytest.mark.parametrize("name", sorted(gg.tiny_graphs()))
+def test_tiny_graphs(cuda_device, oracle, name):
+    n, u, v = gg.tiny_graphs()[name]
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u, v)
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    for f in (1, 3, 32):
+        x = gg.seeded_normal(7 + f, (n, f))
+        check_both_orientations(plan, oracle, index, dst, val, x, cuda_device)
+
+
+@pytest.mark.parametrize("f", WIDTHS)
+def test_widths_on_small_graph(cuda_device, oracle, f):
+    """N = 64 with empty rows, a self-loop-only row and one row that holds a third of all edges."""
+    rng = np.random.default_rng(100 + f)
+    n = 64
+    u = rng.integers(0, n, 400)
+    v = rng.integers(0, n, 400)
+    u = np.concatenate([u, np.full(200, 5), [9]])
+    v = np.concatenate([v, rng.integers(0, n, 200), [9]])
+    keep = ~np.isin(u, [3, 17, 40])                      # rows 3, 17, 40 stay empty in A
+    u, v = u[keep], v[keep]
+    key = np.unique(u.astype(np.int64) * n + v)
+    u, v = (key // n).astype(np.int32), (key % n).astype(np.int32)
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u, v)
+    x = gg.seeded_normal(f, (n, f))
+    for env in ({}, {"DRONE_SHORT_ROW_LIMIT": 4, "DRONE_CHUNK_NNZ": 8}):
+        plan = make_plan(cuda_device, index, dst, in_deg, out_deg, **env)
+        check_both_orientations(plan, oracle, index, dst, val, x, cuda_device)
+
+
+@pytest.mark.parametrize("f", [1, 3, 32, 41, 64])
+def test_rmat12(cuda_device, oracle, f):
+    n, u, v = gg.rmat_graph(12, 16, seed=31, symmetrise=True, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    x = gg.seeded_normal(50 + f, (n, f))
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    st = plan.stats()
+    assert st.n_chunks[db.OP_AT] > 0 and st.n_split_rows[db.OP_AT] > 0     # skewed enough to split rows
+    check_both_orientations(plan, oracle, index, dst, val, x, cuda_device)
+
+
+def test_many_partials_per_row(cuda_device, oracle):
+    """One row with thousands of nonzeros and tiny chunks: the wide (eight-warp) reduction runs."""
+    n = 3000
+    u = np.concatenate([np.zeros(n - 1, np.int64), np.arange(1, n)])
+    v = np.concatenate([np.arange(1, n), np.zeros(n - 1, np.int64)])
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.astype(np.int32), v.astype(np.int32))
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg, DRONE_SHORT_ROW_LIMIT=4, DRONE_CHUNK_NNZ=8)
+    assert plan.stats().n_partials[db.OP_A] > 64
+    for f in (1, 32, 41, 256):
+        x = gg.seeded_normal(f, (n, f))
+        check_both_orientations(plan, oracle, index, dst, val, x, cuda_device)
+
+
+def test_golden_vectors(cuda_device, oracle):
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "spmm_golden.npz"))
+    for name, scale, ef, seed, sym, loops, widths in make_golden.CASES:
+        n, index, dst, in_deg, out_deg = make_golden.case_inputs(scale, ef, seed, sym, loops)
+        plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+        for f in widths:
+            x = torch.as_tensor(gg.seeded_normal(1000 + f, (n, f)), device=cuda_device)
+            assert_close_to_oracle(plan.spmm(db.OP_AT, x).cpu().numpy(), gold["%s/fwd_F%d" % (name, f)])
+            assert_close_to_oracle(plan.spmm(db.OP_A, x).cpu().numpy(), gold["%s/bwd_F%d" % (name, f)])
+
+
+def test_bitwise_repeatable_and_padded_leading_dimension(cuda_device, oracle):
+    n, u, v = gg.rmat_graph(11, 16, seed=33, symmetrise=True, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    for f, ld in ((32, 32), (41, 41), (41, 48), (64, 80)):
+        xh = gg.seeded_normal(f, (n, f))
+        xp = torch.zeros((n, ld), device=cuda_device)
+        xp[:, :f] = torch.as_tensor(xh, device=cuda_device)
+        yp = torch.full((n, ld), 7.0, device=cuda_device)
+        y1 = plan.spmm(db.OP_AT, xp[:, :f], out=yp[:, :f]).clone()
+        y2 = plan.spmm(db.OP_AT, xp[:, :f].contiguous())
+        y3 = plan.spmm(db.OP_AT, xp[:, :f].contiguous())
+        assert torch.equal(y2, y3)                       # run-to-run bit equality
+        if ld % 4 == f % 4 == 0 or (f % 4 and ld % 4):   # same kernel variant => same bits
+            assert torch.equal(y1, y2)
+        assert (yp[:, f:] == 7.0).all()                  # padding columns untouched
+        t = oracle.transpose_csr(n, n, index, dst, val)
+        w, a = oracle.spmm_csr_f64(*t, xh, with_abs=True)
+        assert_close_to_oracle(y1.cpu().numpy(), w, a)
+
+
+def test_matches_cusparse_as_called_by_reference(cuda_device, oracle):
+    from baseline import cusparse_ref
+    n, u, v = gg.rmat_graph(13, 16, seed=34, symmetrise=True, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    rp, co, va = plan.csr(db.OP_AT)
+    for f in (32, 41, 64, 128):
+        x = torch.as_tensor(gg.seeded_normal(f, (n, f)), device=cuda_device)
+        y_ref = torch.empty_like(x)
+        ref = cusparse_ref.CusparseSpmm(rp, co, va, x, y_ref)
+        ref.run()
+        torch.cuda.synchronize()
+        y = plan.spmm(db.OP_AT, x)
+        scale = y_ref.abs().max().item()
+        assert (y - y_ref).abs().max().item() <= REL_TOL * scale
+        ref.close()
+
+
+def test_host_operand_entry_point(cuda_device, oracle):
+    n, u, v = gg.rmat_graph(11, 16, seed=35, symmetrise=True, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    f = 64
+    xh = torch.as_tensor(gg.seeded_normal(3, (n, f))).pin_memory()
+    yh = torch.empty((n, f)).pin_memory()
+    plan.spmm_host(db.OP_AT, xh, yh)
+    y_dev = plan.spmm(db.OP_AT, xh.to(cuda_device))
+    assert torch.equal(yh, y_dev.cpu())
+    xn = xh.numpy().copy()                               # pageable numpy operands work too
+    yn = np.empty_like(xn)
+    plan.spmm_host(db.OP_A, xn, yn)
+    assert np.array_equal(yn, plan.spmm(db.OP_A, xh.to(cuda_device)).cpu().numpy())
+
+
+def test_argument_errors(cuda_device, oracle):
+    n, u, v = gg.tiny_graphs()["path5"]
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u, v)
+    plan = db.AggregationPlan(torch.as_tensor(index, device=cuda_device), torch.as_tensor(dst, device=cuda_device),
+                              in_degree=torch.as_tensor(in_deg, device=cuda_device),
+                              out_degree=torch.as_tensor(out_deg, device=cuda_device), orientations=db.PLAN_AT)
+    x = torch.zeros((n, 8), device=cuda_device)
+    with pytest.raises(db.DroneError, match="not prepared"):
+        plan.spmm(db.OP_A, x)
+    lib = db.lib()
+    assert lib.drone_spmm(plan.handle, 1, 2048, x.data_ptr(), 2048, x.data_ptr(), 2048, None) == -1
+    assert b"outside 1..1024" in lib.drone_last_error()
+    assert lib.drone_spmm(plan.handle, 1, 8, x.data_ptr(), 8, x.data_ptr(), 8, None) == -1
+    assert b"alias" in lib.drone_last_error()
+
+
+def test_empty_graph(cuda_device):
+    index = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    dst = torch.zeros(0, dtype=torch.int32, device=cuda_device)
+    plan = db.AggregationPlan(index, dst, values=torch.zeros(0, device=cuda_device))
+    y = plan.spmm(db.OP_AT, torch.zeros((0, 16), device=cuda_device))
+    assert y.shape == (0, 16)
+    # vertices but no edges: output is all zeros, previous contents overwritten
+    index = torch.zeros(11, dtype=torch.int32, device=cuda_device)
+    plan = db.AggregationPlan(index, dst, values=torch.zeros(0, device=cuda_device))
+    out = torch.full((10, 5), 3.0, device=cuda_device)
+    plan.spmm(db.OP_A, torch.ones((10, 5), device=cuda_device), out=out)
+    assert (out == 0).all()
