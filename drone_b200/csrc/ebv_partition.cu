@@ -1,0 +1,144 @@
+// EBV vertex-cut partitioner on the host, single process.
+//
+// Restates the algorithm of the reference's MPI partitioner (EBV_mpi.cpp) as a
+// simulation of its P ranks in one address space, so that partitions in the
+// reference's format can be produced without MPI:
+//   * edges are dealt round-robin to P ranks (EBV_mpi.cpp:212-253, rank = index % P);
+//   * every rank sorts its share by deg(u)+deg(v) ascending, degrees counted over
+//     its own share only (:259-265);
+//   * in lock-step rounds of 10, 13, 16, ... up to 1000 edges per rank (:273,372)
+//     each rank scores every part for each of its edges from the state at the start
+//     of the round (:284-331):
+//         score[p] = -[u not in p] - [v not in p] - edges_p/edges_of_this_rank
+//                    - vertices_p / |V| * P   (+0.1 for the rank's own part)
+//     and sends the edge to the first part with the highest score (:50-61);
+//   * parts append what they receive in sender order and update their vertex sets
+//     and counters (:334-370);
+//   * a vertex held by several parts gets as master the replica number
+//     (id mod #replicas) in ascending part order (:567-581); the others are mirrors.
+// The only liberty taken: the per-rank sort is stable (the reference uses
+// std::sort, whose order among equal keys is unspecified), so the result is
+// deterministic.
+#include "common.cuh"
+
+#include <algorithm>
+#include <cstdint>
+#include <vector>
+
+namespace drone {
+
+struct EbvEdge {
+    int u, v, key;
+};
+
+static inline bool bit_get(const std::vector<uint64_t> &b, int i) { return (b[(size_t)i >> 6] >> (i & 63)) & 1ULL; }
+static inline void bit_set(std::vector<uint64_t> &b, int i) { b[(size_t)i >> 6] |= 1ULL << (i & 63); }
+
+}  // namespace drone
+
+using namespace drone;
+
+extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int *h_u, const int *h_v, int n_parts,
+                                   int keep_self_loops, int *h_out_u, int *h_out_v, long long *h_part_offset,
+                                   int *h_owner, int *h_replicas) {
+    DRONE_REQUIRE(n_vertices > 0 && n_edges >= 0, "drone_ebv_partition: bad sizes (V=%d, E=%lld)", n_vertices, n_edges);
+    DRONE_REQUIRE(n_parts >= 1 && n_parts <= 64, "drone_ebv_partition: n_parts=%d outside 1..64", n_parts);
+    DRONE_REQUIRE(n_edges == 0 || (h_u && h_v), "drone_ebv_partition: NULL edge list");
+    DRONE_REQUIRE(h_out_u && h_out_v && h_part_offset && h_owner && h_replicas, "drone_ebv_partition: NULL output");
+    const int P = n_parts;
+    const int max_batch = 1000;
+
+    // deal + per-rank degree + per-rank stable sort by degree sum
+    std::vector<std::vector<EbvEdge>> share(P);
+    for (int r = 0; r < P; ++r) share[r].reserve((size_t)(n_edges / P + 1));
+    for (long long i = 0; i < n_edges; ++i) {
+        DRONE_REQUIRE(h_u[i] >= 0 && h_u[i] < n_vertices && h_v[i] >= 0 && h_v[i] < n_vertices,
+                      "drone_ebv_partition: edge %lld (%d,%d) outside 0..%d", i, h_u[i], h_v[i], n_vertices - 1);
+        if (!keep_self_loops && h_u[i] == h_v[i]) continue;
+        share[(size_t)(i % P)].push_back({h_u[i], h_v[i], 0});
+    }
+    long long kept = 0;
+    {
+        std::vector<int> deg((size_t)n_vertices);
+        for (int r = 0; r < P; ++r) {
+            std::fill(deg.begin(), deg.end(), 0);
+            for (const EbvEdge &e : share[r]) { deg[e.u]++; deg[e.v]++; }
+            for (EbvEdge &e : share[r]) e.key = deg[e.u] + deg[e.v];
+            std::stable_sort(share[r].begin(), share[r].end(),
+                             [](const EbvEdge &a, const EbvEdge &b) { return a.key < b.key; });
+            kept += (long long)share[r].size();
+        }
+    }
+
+    std::vector<std::vector<uint64_t>> has(P, std::vector<uint64_t>(((size_t)n_vertices + 63) / 64, 0));
+    std::vector<long long> edge_count(P, 0), vertex_count(P, 0);
+    std::vector<std::vector<int>> part_u(P), part_v(P);
+    // assignment of this round: for each (sender, part) the edges in sender order
+    std::vector<std::vector<int>> sent((size_t)P * P);
+    std::vector<double> weight(P);
+
+    long long longest = 0;
+    for (int r = 0; r < P; ++r) longest = std::max<long long>(longest, (long long)share[r].size());
+    int batch = 10;
+    for (long long start = 0; start < longest; start += batch,
+                   batch = batch < max_batch ? std::min((int)(batch * 1.3), max_batch) : batch) {
+        for (auto &s : sent) s.clear();
+        for (int r = 0; r < P; ++r) {
+            const long long edges_r = (long long)share[r].size();
+            const long long end = std::min<long long>(start + batch, edges_r);
+            for (long long i = start; i < end; ++i) {
+                const EbvEdge &e = share[r][(size_t)i];
+                int best = -1;
+                double best_w = -100;
+                for (int p = 0; p < P; ++p) {
+                    double w = 0;
+                    if (!bit_get(has[p], e.u)) w -= 1;
+                    if (!bit_get(has[p], e.v)) w -= 1;
+                    w = w - 1.0 * edge_count[p] / (double)edges_r - 1.0 * vertex_count[p] / n_vertices * P;
+                    if (p == r) w += 0.1;
+                    if (best_w < w) { best_w = w; best = p; }
+                }
+                sent[(size_t)r * P + best].push_back(e.u);
+                sent[(size_t)r * P + best].push_back(e.v);
+            }
+        }
+        for (int p = 0; p < P; ++p)
+            for (int r = 0; r < P; ++r) {
+                const std::vector<int> &s = sent[(size_t)r * P + p];
+                for (size_t k = 0; k < s.size(); k += 2) {
+                    const int u = s[k], v = s[k + 1];
+                    part_u[p].push_back(u);
+                    part_v[p].push_back(v);
+                    if (!bit_get(has[p], u)) { bit_set(has[p], u); vertex_count[p]++; }
+                    if (!bit_get(has[p], v)) { bit_set(has[p], v); vertex_count[p]++; }
+                }
+                edge_count[p] += (long long)(s.size() / 2);
+            }
+    }
+
+    long long off = 0;
+    for (int p = 0; p < P; ++p) {
+        h_part_offset[p] = off;
+        std::copy(part_u[p].begin(), part_u[p].end(), h_out_u + off);
+        std::copy(part_v[p].begin(), part_v[p].end(), h_out_v + off);
+        off += (long long)part_u[p].size();
+    }
+    h_part_offset[P] = off;
+    if (off != kept) return set_error(DRONE_E_STATE, "drone_ebv_partition: %lld edges in, %lld out", kept, off);
+
+    for (int v = 0; v < n_vertices; ++v) {
+        int reps = 0;
+        for (int p = 0; p < P; ++p) reps += bit_get(has[p], v) ? 1 : 0;
+        h_replicas[v] = reps;
+        h_owner[v] = -1;
+        if (reps == 0) continue;
+        const int want = reps > 1 ? v % reps : 0;
+        int seen = 0;
+        for (int p = 0; p < P; ++p)
+            if (bit_get(has[p], v)) {
+                if (seen == want) { h_owner[v] = p; break; }
+                ++seen;
+            }
+    }
+    return DRONE_OK;
+}
