@@ -54,6 +54,20 @@ def _declare(lib):
         "drone_spmm_host": (i, [vp, i, i, vp, vp]),
         "drone_host_alloc": (i, [C.POINTER(vp), C.c_size_t]),
         "drone_host_free": (i, [vp]),
+        "drone_comm_unique_id": (i, [vp, C.c_size_t]),
+        "drone_comm_create": (i, [C.POINTER(vp), i, i, vp, C.c_size_t]),
+        "drone_comm_adopt": (i, [C.POINTER(vp), vp, i, i]),
+        "drone_comm_destroy": (i, [vp]),
+        "drone_comm_allreduce_sum": (i, [vp, vp, C.c_size_t, i, vp]),
+        "drone_xplan_create": (i, [C.POINTER(vp), i, i, i, vp, vp, vp, vp, i]),
+        "drone_xplan_destroy": (i, [vp]),
+        "drone_xplan_counts": (i, [vp, vp, vp, C.POINTER(i)]),
+        "drone_xplan_lists": (i, [vp, vp, vp]),
+        "drone_exchange_sum": (i, [vp, vp, vp, i, i, vp]),
+        "drone_exchange_sum_local": (i, [i, C.POINTER(vp), C.POINTER(vp), i, C.POINTER(i), vp]),
+        "drone_ebv_partition": (i, [i, ll, vp, vp, i, i, vp, vp, vp, vp, vp]),
+        "drone_graph_build_host": (i, [i, i, vp, vp, vp, vp, vp, vp, C.POINTER(i)]),
+        "drone_route_tables_host": (i, [i, vp, vp, vp, vp, i, i, vp, vp, i, vp, vp, vp]),
         "drone_rmat_edges": (i, [i, ll, C.c_ulonglong, C.c_double, C.c_double, C.c_double, ll, vp, vp, vp]),
         "drone_rmat_edges_host": (i, [i, ll, C.c_ulonglong, C.c_double, C.c_double, C.c_double, ll, vp, vp]),
     }

@@ -134,6 +134,64 @@ __global__ void fill_chunks_kernel(const int *__restrict__ rowptr, int n_rows, i
     }
 }
 
+// Per row: 1 if short, and its number of stream entries (a row without nonzeros gets one placeholder).
+__global__ void count_short_kernel(const int *__restrict__ rowptr, int n_rows, int short_limit,
+                                   int *__restrict__ is_short, int *__restrict__ n_entries) {
+    for (long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x; r <= n_rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        int s = 0, e = 0;
+        if (r < n_rows) {
+            const int deg = rowptr[r + 1] - rowptr[r];
+            if (deg <= short_limit) { s = 1; e = deg > 0 ? deg : 1; }
+        }
+        is_short[r] = s;
+        n_entries[r] = e;
+    }
+}
+
+__global__ void fill_short_kernel(const int *__restrict__ rowptr, const int *__restrict__ col,
+                                  const float *__restrict__ val, int n_rows, int short_limit,
+                                  const int *__restrict__ short_off, const int *__restrict__ entry_off,
+                                  int *__restrict__ s_rows, int *__restrict__ s_rowptr,
+                                  int *__restrict__ s_col, float *__restrict__ s_val) {
+    for (long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x; r < n_rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        const int b = rowptr[r], deg = rowptr[r + 1] - b;
+        if (deg > short_limit) continue;
+        const int si = short_off[r];
+        const int e0 = entry_off[r];
+        s_rows[si] = (int)r;
+        s_rowptr[si] = e0;
+        if (deg == 0) {
+            s_col[e0] = (int)(kLastInRow | kPlaceholder);
+            s_val[e0] = 0.f;
+        } else {
+            for (int j = 0; j < deg; ++j) {
+                unsigned c = (unsigned)col[b + j];
+                if (j == deg - 1) c |= kLastInRow;
+                s_col[e0 + j] = (int)c;
+                s_val[e0 + j] = val[b + j];
+            }
+        }
+    }
+}
+
+// s_range_row[i] = first short row whose stream offset is >= i * range_nnz
+__global__ void short_ranges_kernel(const int *__restrict__ s_rowptr, int n_short, int n_ranges, int range_nnz,
+                                    int *__restrict__ s_range_row) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i <= n_ranges;
+         i += (long long)gridDim.x * blockDim.x) {
+        if (i == n_ranges) { s_range_row[i] = n_short; continue; }
+        const long long target = i * (long long)range_nnz;
+        int lo = 0, hi = n_short;  // first index with s_rowptr[idx] >= target
+        while (lo < hi) {
+            const int mid = lo + ((hi - lo) >> 1);
+            if (s_rowptr[mid] < target) lo = mid + 1; else hi = mid;
+        }
+        s_range_row[i] = lo;
+    }
+}
+
 __global__ void max_nslots_kernel(const SplitRow *__restrict__ split, int n, int *out) {
     int m = 0;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
@@ -166,6 +224,11 @@ static void free_side(Side &s) {
     cudaFree(s.val);
     cudaFree(s.chunks);
     cudaFree(s.split);
+    cudaFree(s.s_rows);
+    cudaFree(s.s_rowptr);
+    cudaFree(s.s_col);
+    cudaFree(s.s_val);
+    cudaFree(s.s_range_row);
     s = Side();
 }
 
@@ -274,6 +337,37 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
         }
         DRONE_CUDA(cudaStreamSynchronize(st));
     }
+    // stream of the short rows
+    count_short_kernel<<<grid_for(n + 1), 256, 0, st>>>(s.rowptr, n, p->short_row_limit, cnt[0], cnt[1]);
+    DRONE_LAUNCH_CHECK("count_short_kernel");
+    for (int i = 0; i < 2; ++i) {
+        DRONE_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, cnt[i], off[i], n + 1, st));
+        count_launch();
+    }
+    int short_totals[2];
+    for (int i = 0; i < 2; ++i)
+        DRONE_CUDA(cudaMemcpyAsync(&short_totals[i], off[i] + n, sizeof(int), cudaMemcpyDeviceToHost, st));
+    DRONE_CUDA(cudaStreamSynchronize(st));
+    s.n_short_rows = short_totals[0];
+    s.n_short_entries = short_totals[1];
+    s.n_short_ranges = s.n_short_entries > 0 ? ceil_div(s.n_short_entries, kShortRangeNnz) : 0;
+    if (s.n_short_rows > 0) {
+        DRONE_CUDA(cudaMalloc(&s.s_rows, sizeof(int) * (size_t)s.n_short_rows));
+        DRONE_CUDA(cudaMalloc(&s.s_rowptr, sizeof(int) * (size_t)(s.n_short_rows + 1)));
+        DRONE_CUDA(cudaMalloc(&s.s_col, sizeof(int) * (size_t)s.n_short_entries));
+        DRONE_CUDA(cudaMalloc(&s.s_val, sizeof(float) * (size_t)s.n_short_entries));
+        DRONE_CUDA(cudaMalloc(&s.s_range_row, sizeof(int) * (size_t)(s.n_short_ranges + 1)));
+        fill_short_kernel<<<grid_for(n), 256, 0, st>>>(s.rowptr, s.col, s.val, n, p->short_row_limit, off[0], off[1],
+                                                      s.s_rows, s.s_rowptr, s.s_col, s.s_val);
+        DRONE_LAUNCH_CHECK("fill_short_kernel");
+        DRONE_CUDA(cudaMemcpyAsync(s.s_rowptr + s.n_short_rows, &s.n_short_entries, sizeof(int),
+                                   cudaMemcpyHostToDevice, st));
+        short_ranges_kernel<<<grid_for(s.n_short_ranges + 1), 256, 0, st>>>(s.s_rowptr, s.n_short_rows,
+                                                                           s.n_short_ranges, kShortRangeNnz,
+                                                                           s.s_range_row);
+        DRONE_LAUNCH_CHECK("short_ranges_kernel");
+        DRONE_CUDA(cudaStreamSynchronize(st));
+    }
     cudaFree(tmp);
     cudaFree(buf);
     s.ready = true;
@@ -356,6 +450,7 @@ int drone_plan_create(drone_plan **out, int n_rows, int nnz, const int *d_index,
     DRONE_REQUIRE(out != nullptr, "drone_plan_create: out is NULL");
     *out = nullptr;
     DRONE_REQUIRE(n_rows >= 0 && nnz >= 0, "drone_plan_create: negative size (n_rows=%d, nnz=%d)", n_rows, nnz);
+    DRONE_REQUIRE(n_rows < (1 << 30), "drone_plan_create: n_rows=%d is above the 2^30-1 limit of the column encoding", n_rows);
     DRONE_REQUIRE(d_index != nullptr, "drone_plan_create: d_index is NULL");
     DRONE_REQUIRE(nnz == 0 || d_dst != nullptr, "drone_plan_create: d_dst is NULL with nnz=%d", nnz);
     DRONE_REQUIRE(nnz == 0 || d_values != nullptr || (d_in_degree && d_out_degree),

@@ -5,6 +5,11 @@
 
 namespace drone {
 
+constexpr int kShortRangeNnz = 64;          // stream entries per lane group (plus at most one more row)
+constexpr unsigned kLastInRow = 0x80000000u; // flag on s_col: last entry of its row
+constexpr unsigned kPlaceholder = 0x40000000u; // flag on s_col: row has no nonzeros, entry carries no data
+constexpr unsigned kColMask = 0x3fffffffu;
+
 // One chunk of a long row: nonzeros [k0, k0+len) of `row`.  slot >= 0 means the
 // chunk's sum goes to partial-sum slot `slot` (the row has several chunks);
 // slot < 0 means the chunk is the whole row and its sum goes straight to Y.
@@ -32,6 +37,18 @@ struct Side {
     float *val = nullptr;      // [nnz]
     Chunk *chunks = nullptr;   // [n_chunks]
     SplitRow *split = nullptr; // [n_split_rows]
+    // Short rows (at most short_row_limit nonzeros) as one contiguous stream: their nonzeros copied
+    // in row order, bit 31 of the column marking the last nonzero of a row.  A row without nonzeros
+    // contributes one placeholder entry (bit 30) so that it is still written.  The stream is cut into
+    // ranges of about kShortRangeNnz entries at row boundaries; range i starts at row s_range_row[i].
+    int *s_rows = nullptr;      // [n_short_rows] row id of each short row
+    int *s_rowptr = nullptr;    // [n_short_rows + 1] start of each short row in the stream
+    int *s_col = nullptr;       // [n_short_entries] column | flags
+    float *s_val = nullptr;     // [n_short_entries]
+    int *s_range_row = nullptr; // [n_short_ranges + 1]
+    int n_short_rows = 0;
+    int n_short_entries = 0;
+    int n_short_ranges = 0;
     int n_long_rows = 0;
     int n_chunks = 0;
     int n_split_rows = 0;

@@ -1,8 +1,11 @@
 // Sparse aggregation kernels:  Y[r,:] = sum_k val[k] * X[col[k],:]  over CSR rows.
 //
 // The work of one call is split three ways, all decided when the plan was built:
-//   1. short rows (at most short_row_limit nonzeros): one lane group per row,
-//      32/G rows per warp, nonzeros added in CSR order into one accumulator;
+//   1. short rows (at most short_row_limit nonzeros) are stored once more as one
+//      contiguous stream with end-of-row flags; a lane group walks about 64
+//      entries of it (whole rows), adding a row's nonzeros in CSR order into one
+//      accumulator and writing the row at its last entry, so the per-row cost
+//      is one store and no warp is spent on a row of two nonzeros;
 //   2. long rows: cut into chunks of chunk_nnz nonzeros, one warp per chunk with
 //      its 32/G lane groups taking interleaved nonzeros; a row that is a single
 //      chunk is written directly, otherwise the chunk sum goes to a partial slot;
@@ -16,6 +19,47 @@
 #include "plan.cuh"
 
 namespace drone {
+
+// L2 cache policies.  Rows of X are gathered many times and should stay resident; the CSR
+// streams, the chunk list and the output pass through once and should be the first to go.
+__device__ __forceinline__ unsigned long long l2_policy_keep() {
+    unsigned long long p;
+    asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ unsigned long long l2_policy_stream() {
+    unsigned long long p;
+    asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ float4 ld_keep(const float4 *ptr, unsigned long long pol) {
+    float4 v;
+    asm("ld.global.nc.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+        : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(ptr), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ float ld_keep(const float *ptr, unsigned long long pol) {
+    float v;
+    asm("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(ptr), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ int ld_stream(const int *ptr, unsigned long long pol) {
+    int v;
+    asm("ld.global.nc.L1::no_allocate.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(ptr), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ float ld_stream(const float *ptr, unsigned long long pol) {
+    float v;
+    asm("ld.global.nc.L1::no_allocate.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(ptr), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ void st_stream(float4 *ptr, const float4 &v, unsigned long long pol) {
+    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1,%2,%3,%4}, %5;"
+                 :: "l"(ptr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void st_stream(float *ptr, const float &v, unsigned long long pol) {
+    asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" :: "l"(ptr), "f"(v), "l"(pol) : "memory");
+}
 
 template <int VEC> struct Vec;
 template <> struct Vec<4> {
@@ -48,47 +92,59 @@ template <> struct Vec<1> {
 template <int A, int B> struct MinOf { static constexpr int value = A < B ? A : B; };
 
 // ---------------------------------------------------------------------------
-// 1. short rows: one lane group per row
+// 1. short rows: one lane group walks a range of the short-row stream
+//    (about kShortRangeNnz entries, whole rows only) and writes each row when
+//    its last entry has been added.  Entries of a row are added in CSR order
+//    into one accumulator.
 // ---------------------------------------------------------------------------
-template <int G, int VPL, int VEC, int U>
+template <int G, int VPL, int VEC, int U, bool EXACT>
 __global__ void __launch_bounds__(256)
-spmm_short_rows_kernel(const int *__restrict__ rowptr, const int *__restrict__ col,
-                       const float *__restrict__ val, const float *__restrict__ X, long long ldx,
-                       float *__restrict__ Y, long long ldy, int n_rows, int nvec, int short_limit) {
+spmm_short_stream_kernel(const int *__restrict__ s_range_row, int n_ranges, const int *__restrict__ s_rowptr,
+                         const int *__restrict__ s_rows, const int *__restrict__ s_col,
+                         const float *__restrict__ s_val, const float *__restrict__ X, long long ldv,
+                         float *__restrict__ Y, long long ldy, int nvec) {
     using V = typename Vec<VEC>::type;
     constexpr int RPW = 32 / G;
     constexpr int UU = MinOf<U, G>::value;
     const int lane = threadIdx.x & 31;
     const int gl = lane & (G - 1);
     const int gi = lane / G;
-    const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-    const long long row = warp * RPW + gi;
-    int s = 0, deg = 0;
-    const bool in_range = row < n_rows;
-    if (in_range) {
-        s = rowptr[row];
-        deg = rowptr[row + 1] - s;
+    const long long range = ((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5) * RPW + gi;
+    int ri = 0, k = 0, kend = 0;
+    if (range < n_ranges) {
+        ri = s_range_row[range];
+        const int ri_end = s_range_row[range + 1];
+        k = s_rowptr[ri];
+        kend = s_rowptr[ri_end];
     }
-    const bool mine = in_range && deg <= short_limit;
-    if (!mine) deg = 0;
-    int maxdeg = deg;
+    int maxlen = kend - k;
 #pragma unroll
-    for (int o = G; o < 32; o <<= 1) maxdeg = max(maxdeg, __shfl_xor_sync(0xffffffffu, maxdeg, o));
+    for (int o = G; o < 32; o <<= 1) maxlen = max(maxlen, __shfl_xor_sync(0xffffffffu, maxlen, o));
 
+    const V *xb = reinterpret_cast<const V *>(X) + gl;
+    const unsigned long long pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
     V acc[VPL];
 #pragma unroll
     for (int p = 0; p < VPL; ++p) acc[p] = Vec<VEC>::zero();
 
-    for (int base = 0; base < maxdeg; base += G) {
-        int c = 0;
-        float v = 0.f;
-        if (base + gl < deg) {
-            c = __ldcs(col + s + base + gl);
-            v = __ldcs(val + s + base + gl);
+    unsigned c_next = 0;
+    float v_next = 0.f;
+    if (k + gl < kend) {
+        c_next = (unsigned)ld_stream(s_col + k + gl, pol_stream);
+        v_next = ld_stream(s_val + k + gl, pol_stream);
+    }
+    for (int base = 0; base < maxlen; base += G) {
+        const unsigned c = c_next;
+        const float v = v_next;
+        c_next = 0;
+        v_next = 0.f;
+        if (k + base + G + gl < kend) {   // next batch, requested before this batch's gathers
+            c_next = (unsigned)ld_stream(s_col + k + base + G + gl, pol_stream);
+            v_next = ld_stream(s_val + k + base + G + gl, pol_stream);
         }
-        const int lim = min(G, maxdeg - base);
+        const int lim = min(G, maxlen - base);
         for (int j = 0; j < lim; j += UU) {
-            int cc[UU];
+            unsigned cc[UU];
             float vv[UU];
             V x[UU][VPL];
 #pragma unroll
@@ -98,37 +154,38 @@ spmm_short_rows_kernel(const int *__restrict__ rowptr, const int *__restrict__ c
             }
 #pragma unroll
             for (int u = 0; u < UU; ++u) {
-                const bool live = base + j + u < deg;
-                const V *xr = reinterpret_cast<const V *>(X + (long long)cc[u] * ldx);
+                const bool live = (k + base + j + u < kend) && !(cc[u] & kPlaceholder);
+                const V *xr = xb + (long long)(cc[u] & kColMask) * ldv;
 #pragma unroll
-                for (int p = 0; p < VPL; ++p) {
-                    const int vi = gl + p * G;
-                    x[u][p] = (live && vi < nvec) ? __ldg(xr + vi) : Vec<VEC>::zero();
-                }
+                for (int p = 0; p < VPL; ++p)
+                    x[u][p] = (live && (EXACT || gl + p * G < nvec)) ? ld_keep(xr + p * G, pol_keep) : Vec<VEC>::zero();
             }
 #pragma unroll
-            for (int u = 0; u < UU; ++u)
+            for (int u = 0; u < UU; ++u) {
 #pragma unroll
                 for (int p = 0; p < VPL; ++p) Vec<VEC>::fma(acc[p], vv[u], x[u][p]);
-        }
-    }
-    if (mine) {
-        V *yr = reinterpret_cast<V *>(Y + row * ldy);
+                if ((cc[u] & kLastInRow) && (k + base + j + u < kend)) {
+                    V *yr = reinterpret_cast<V *>(Y + (long long)s_rows[ri] * ldy) + gl;
 #pragma unroll
-        for (int p = 0; p < VPL; ++p) {
-            const int vi = gl + p * G;
-            if (vi < nvec) __stcs(yr + vi, acc[p]);
+                    for (int p = 0; p < VPL; ++p) {
+                        if (EXACT || gl + p * G < nvec) st_stream(yr + p * G, acc[p], pol_stream);
+                        acc[p] = Vec<VEC>::zero();
+                    }
+                    ++ri;
+                }
+            }
         }
     }
 }
 
 // ---------------------------------------------------------------------------
-// 2. chunks of long rows: one warp per chunk
+// 2. chunks of long rows: one warp per chunk.  The warp loads 32 (col, val)
+//    pairs at a time; its 32/G lane groups take interleaved entries.
 // ---------------------------------------------------------------------------
-template <int G, int VPL, int VEC, int U>
+template <int G, int VPL, int VEC, int U, bool EXACT>
 __global__ void __launch_bounds__(256)
 spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__restrict__ col,
-                   const float *__restrict__ val, const float *__restrict__ X, long long ldx,
+                   const float *__restrict__ val, const float *__restrict__ X, long long ldv,
                    float *__restrict__ Y, long long ldy, float *__restrict__ partials, int nvec) {
     using V = typename Vec<VEC>::type;
     constexpr int RPW = 32 / G;
@@ -140,19 +197,58 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
     if (warp >= n_chunks) return;
     const int4 raw = __ldg(reinterpret_cast<const int4 *>(chunks) + warp);
     const int row = raw.x, k0 = raw.y, len = raw.z, slot = raw.w;
+    const V *xb = reinterpret_cast<const V *>(X) + gl;
+    const unsigned long long pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
 
     V acc[VPL];
 #pragma unroll
     for (int p = 0; p < VPL; ++p) acc[p] = Vec<VEC>::zero();
 
-    for (int base = 0; base < len; base += 32) {
-        int c = 0;
-        float v = 0.f;
-        if (base + lane < len) {
-            c = __ldcs(col + k0 + base + lane);
-            v = __ldcs(val + k0 + base + lane);
+    // (col, val) of the next batch are requested before the gathers of the current one are issued, so the
+    // dependent chain col -> X row costs one memory latency per batch instead of two
+    int c = 0;
+    float v = 0.f;
+    if (lane < len) {
+        c = ld_stream(col + k0 + lane, pol_stream);
+        v = ld_stream(val + k0 + lane, pol_stream);
+    }
+    int base = 0;
+    // full batches of 32 entries: no bounds checks
+    for (; base + 32 <= len; base += 32) {
+        int c_next = 0;
+        float v_next = 0.f;
+        if (base + 32 + lane < len) {
+            c_next = ld_stream(col + k0 + base + 32 + lane, pol_stream);
+            v_next = ld_stream(val + k0 + base + 32 + lane, pol_stream);
         }
-        const int cnt = min(32, len - base);
+#pragma unroll
+        for (int t = 0; t < G; t += UU) {
+            int cc[UU];
+            float vv[UU];
+            V x[UU][VPL];
+#pragma unroll
+            for (int u = 0; u < UU; ++u) {
+                cc[u] = __shfl_sync(0xffffffffu, c, (t + u) * RPW + gi);
+                vv[u] = __shfl_sync(0xffffffffu, v, (t + u) * RPW + gi);
+            }
+#pragma unroll
+            for (int u = 0; u < UU; ++u) {
+                const V *xr = xb + (long long)cc[u] * ldv;
+#pragma unroll
+                for (int p = 0; p < VPL; ++p)
+                    x[u][p] = (EXACT || gl + p * G < nvec) ? ld_keep(xr + p * G, pol_keep) : Vec<VEC>::zero();
+            }
+#pragma unroll
+            for (int u = 0; u < UU; ++u)
+#pragma unroll
+                for (int p = 0; p < VPL; ++p) Vec<VEC>::fma(acc[p], vv[u], x[u][p]);
+        }
+        c = c_next;
+        v = v_next;
+    }
+    // last, partial batch (entries beyond the chunk were loaded as zeros)
+    if (base < len) {
+        const int cnt = len - base;
         const int steps = (cnt + RPW - 1) / RPW;  // <= G
         for (int t = 0; t < steps; t += UU) {
             int cc[UU];
@@ -168,12 +264,10 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
 #pragma unroll
             for (int u = 0; u < UU; ++u) {
                 const bool live = (t + u) * RPW + gi < cnt;
-                const V *xr = reinterpret_cast<const V *>(X + (long long)cc[u] * ldx);
+                const V *xr = xb + (long long)cc[u] * ldv;
 #pragma unroll
-                for (int p = 0; p < VPL; ++p) {
-                    const int vi = gl + p * G;
-                    x[u][p] = (live && vi < nvec) ? __ldg(xr + vi) : Vec<VEC>::zero();
-                }
+                for (int p = 0; p < VPL; ++p)
+                    x[u][p] = (live && (EXACT || gl + p * G < nvec)) ? ld_keep(xr + p * G, pol_keep) : Vec<VEC>::zero();
             }
 #pragma unroll
             for (int u = 0; u < UU; ++u)
@@ -188,15 +282,13 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
         for (int p = 0; p < VPL; ++p) Vec<VEC>::add(acc[p], Vec<VEC>::shfl_xor(acc[p], o));
 
     if (gi == 0) {
-        V *out = slot < 0 ? reinterpret_cast<V *>(Y + (long long)row * ldy)
-                          : reinterpret_cast<V *>(partials + (long long)slot * nvec * VEC);
+        V *out = (slot < 0 ? reinterpret_cast<V *>(Y + (long long)row * ldy)
+                           : reinterpret_cast<V *>(partials + (long long)slot * nvec * VEC)) + gl;
 #pragma unroll
-        for (int p = 0; p < VPL; ++p) {
-            const int vi = gl + p * G;
-            if (vi < nvec) {
-                if (slot < 0) __stcs(out + vi, acc[p]); else out[vi] = acc[p];
+        for (int p = 0; p < VPL; ++p)
+            if (EXACT || gl + p * G < nvec) {
+                if (slot < 0) st_stream(out + p * G, acc[p], pol_stream); else out[p * G] = acc[p];
             }
-        }
     }
 }
 
@@ -281,32 +373,30 @@ struct SpmmArgs {
     const Side *side;
     int n_rows;
     int nvec;
-    int short_limit;
     const float *X;
-    long long ldx;
+    long long ldv;   // leading dimension of X in vectors
     float *Y;
-    long long ldy;
+    long long ldy;   // leading dimension of Y in floats
     float *partials;
     cudaStream_t st;
 };
 
 static const int kWideSlots = 64;  // split rows above this many slots get eight warps
 
-template <int G, int VPL, int VEC, int U>
+template <int G, int VPL, int VEC, int U, bool EXACT>
 static int launch_all(const SpmmArgs &a) {
     constexpr int RPW = 32 / G;
     const Side &s = *a.side;
-    if (a.n_rows > 0) {
-        const int rows_per_block = 8 * RPW;
-        const int grid = ceil_div(a.n_rows, rows_per_block);
-        spmm_short_rows_kernel<G, VPL, VEC, U><<<grid, 256, 0, a.st>>>(
-            s.rowptr, s.col, s.val, a.X, a.ldx, a.Y, a.ldy, a.n_rows, a.nvec, a.short_limit);
-        DRONE_LAUNCH_CHECK("spmm_short_rows_kernel");
+    if (s.n_short_ranges > 0) {
+        const int grid = ceil_div(s.n_short_ranges, 8 * RPW);
+        spmm_short_stream_kernel<G, VPL, VEC, U, EXACT><<<grid, 256, 0, a.st>>>(
+            s.s_range_row, s.n_short_ranges, s.s_rowptr, s.s_rows, s.s_col, s.s_val, a.X, a.ldv, a.Y, a.ldy, a.nvec);
+        DRONE_LAUNCH_CHECK("spmm_short_stream_kernel");
     }
     if (s.n_chunks > 0) {
         const int grid = ceil_div(s.n_chunks, 8);
-        spmm_chunks_kernel<G, VPL, VEC, U><<<grid, 256, 0, a.st>>>(
-            s.chunks, s.n_chunks, s.col, s.val, a.X, a.ldx, a.Y, a.ldy, a.partials, a.nvec);
+        spmm_chunks_kernel<G, VPL, VEC, 2 * U, EXACT><<<grid, 256, 0, a.st>>>(
+            s.chunks, s.n_chunks, s.col, s.val, a.X, a.ldv, a.Y, a.ldy, a.partials, a.nvec);
         DRONE_LAUNCH_CHECK("spmm_chunks_kernel");
     }
     if (s.n_split_rows > 0) {
@@ -323,22 +413,27 @@ static int launch_all(const SpmmArgs &a) {
     return DRONE_OK;
 }
 
+template <int G, int VPL, int VEC, int U>
+static int launch_exact(const SpmmArgs &a) {
+    return a.nvec == G * VPL ? launch_all<G, VPL, VEC, U, true>(a) : launch_all<G, VPL, VEC, U, false>(a);
+}
+
 template <int VEC>
 static int dispatch_width(const SpmmArgs &a) {
     const int nv = a.nvec;
-    if (nv <= 1) return launch_all<1, 1, VEC, 4>(a);
-    if (nv <= 2) return launch_all<2, 1, VEC, 4>(a);
-    if (nv <= 4) return launch_all<4, 1, VEC, 4>(a);
-    if (nv <= 8) return launch_all<8, 1, VEC, 4>(a);
-    if (nv <= 16) return launch_all<16, 1, VEC, 4>(a);
-    if (nv <= 32) return launch_all<32, 1, VEC, 4>(a);
-    if (nv <= 64) return launch_all<32, 2, VEC, 4>(a);
-    if (nv <= 96) return launch_all<32, 3, VEC, 2>(a);
-    if (nv <= 128) return launch_all<32, 4, VEC, 2>(a);
-    if (nv <= 256) return launch_all<32, 8, VEC, 1>(a);
+    if (nv <= 1) return launch_exact<1, 1, VEC, 4>(a);
+    if (nv <= 2) return launch_exact<2, 1, VEC, 4>(a);
+    if (nv <= 4) return launch_exact<4, 1, VEC, 4>(a);
+    if (nv <= 8) return launch_exact<8, 1, VEC, 4>(a);
+    if (nv <= 16) return launch_exact<16, 1, VEC, 4>(a);
+    if (nv <= 32) return launch_exact<32, 1, VEC, 4>(a);
+    if (nv <= 64) return launch_exact<32, 2, VEC, 2>(a);
+    if (nv <= 96) return launch_exact<32, 3, VEC, 2>(a);
+    if (nv <= 128) return launch_exact<32, 4, VEC, 1>(a);
+    if (nv <= 256) return launch_exact<32, 8, VEC, 1>(a);
     if (VEC == 1) {
-        if (nv <= 512) return launch_all<32, 16, 1, 1>(a);
-        if (nv <= 1024) return launch_all<32, 32, 1, 1>(a);
+        if (nv <= 512) return launch_exact<32, 16, 1, 1>(a);
+        if (nv <= 1024) return launch_exact<32, 32, 1, 1>(a);
     }
     return set_error(DRONE_E_INVALID, "drone_spmm: feature width %d is above 1024", nv * VEC);
 }
@@ -366,9 +461,7 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
     SpmmArgs a;
     a.side = &s;
     a.n_rows = p->n_rows;
-    a.short_limit = p->short_row_limit;
     a.X = X;
-    a.ldx = ldx;
     a.Y = Y;
     a.ldy = ldy;
     a.partials = p->scratch;
@@ -377,9 +470,11 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
                       ((reinterpret_cast<uintptr_t>(X) & 15) == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     if (vec4) {
         a.nvec = F / 4;
+        a.ldv = ldx / 4;
         return dispatch_width<4>(a);
     }
     a.nvec = F;
+    a.ldv = ldx;
     return dispatch_width<1>(a);
 }
 

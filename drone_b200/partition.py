@@ -1,0 +1,206 @@
+"""EBV partitions in the reference's layout: per part an edge list (G.<p>), the master rows
+(Master.<p>: vertex, ranks holding its mirrors) and the mirror rows (Mirror.<p>: vertex, rank
+of its master), plus the per-rank local graph and routing tables built from them.
+
+Everything here is host-side numpy over the C ABI; nothing needs a GPU.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import _lib
+from ._lib import check
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _vp(a):
+    return C.c_void_p(a.ctypes.data) if a is not None and a.size else C.c_void_p(0)
+
+
+class Partition:
+    """Result of the EBV vertex cut of a directed edge list over n_parts parts."""
+
+    def __init__(self, n_vertices, n_parts, part_u, part_v, owner, replicas):
+        self.n_vertices = n_vertices
+        self.n_parts = n_parts
+        self.part_u = part_u            # list of int32 arrays (global ids), G.<p> order
+        self.part_v = part_v
+        self.owner = owner              # [V] part holding the master copy (-1: vertex has no edge)
+        self.replicas = replicas        # [V] number of parts holding the vertex
+        self._present = None
+
+    # ----- statistics the reference prints (EBV_mpi.cpp:379-401) -----
+    def replication_factor(self):
+        return float(self.replicas.sum()) / self.n_vertices
+
+    def edge_imbalance(self):
+        sizes = np.array([len(u) for u in self.part_u], dtype=np.float64)
+        return float(sizes.max() * self.n_parts / max(sizes.sum(), 1))
+
+    def present(self, p):
+        if self._present is None:
+            self._present = []
+            for q in range(self.n_parts):
+                m = np.zeros(self.n_vertices, dtype=bool)
+                m[self.part_u[q]] = True
+                m[self.part_v[q]] = True
+                self._present.append(m)
+        return self._present[p]
+
+    def master_rows(self, p):
+        """(master_vertex, mirror_number, mirror_workers): the content of Master.<p>."""
+        mine = np.nonzero((self.owner == p) & (self.replicas > 1))[0].astype(np.int32)
+        holders = np.stack([self.present(q)[mine] for q in range(self.n_parts)], axis=1) if len(mine) else \
+            np.zeros((0, self.n_parts), bool)
+        holders[:, p] = False
+        number = holders.sum(axis=1).astype(np.int32)
+        workers = np.nonzero(holders)[1].astype(np.int32)    # row-major: per vertex, ascending rank
+        return mine, number, workers
+
+    def mirror_rows(self, p):
+        """(mirror_vertex, master_worker): the content of Mirror.<p>."""
+        mine = np.nonzero(self.present(p) & (self.replicas > 1) & (self.owner != p))[0].astype(np.int32)
+        return mine, self.owner[mine].astype(np.int32)
+
+    def write_files(self, directory):
+        """G.<p>, Master.<p>, Mirror.<p> in the reference's text formats (EBV_mpi.cpp:342,602-603,631-632)."""
+        os.makedirs(directory, exist_ok=True)
+        for p in range(self.n_parts):
+            np.savetxt(os.path.join(directory, "G.%d" % p), np.stack([self.part_u[p], self.part_v[p]], 1), fmt="%d")
+            mv, num, wk = self.master_rows(p)
+            with open(os.path.join(directory, "Master.%d" % p), "w") as f:
+                pos = 0
+                for v, k in zip(mv.tolist(), num.tolist()):
+                    f.write("%d %s \n" % (v, " ".join(str(w) for w in wk[pos:pos + k].tolist())))
+                    pos += k
+            mr, ow = self.mirror_rows(p)
+            with open(os.path.join(directory, "Mirror.%d" % p), "w") as f:
+                for v, o in zip(mr.tolist(), ow.tolist()):
+                    f.write("%d %d \n" % (v, o))
+
+    def local_graph(self, p):
+        return LocalGraph(self, p)
+
+
+def read_partition_files(directory, n_vertices, n_parts):
+    """Parse G./Master./Mirror. files (as cuda_gcn/src/common/parser.cu:59-131 does) back into a Partition."""
+    part_u, part_v = [], []
+    owner = np.full(n_vertices, -1, np.int32)
+    replicas = np.zeros(n_vertices, np.int32)
+    for p in range(n_parts):
+        e = np.loadtxt(os.path.join(directory, "G.%d" % p), dtype=np.int32, ndmin=2)
+        part_u.append(_i32(e[:, 0]) if e.size else np.zeros(0, np.int32))
+        part_v.append(_i32(e[:, 1]) if e.size else np.zeros(0, np.int32))
+        seen = np.zeros(n_vertices, bool)
+        seen[part_u[-1]] = True
+        seen[part_v[-1]] = True
+        replicas += seen
+        owner[seen & (owner < 0)] = p                 # single-replica vertices: the part that has them
+    for p in range(n_parts):
+        with open(os.path.join(directory, "Master.%d" % p)) as f:
+            for line in f:
+                t = line.split()
+                if t:
+                    owner[int(t[0])] = p
+    return Partition(n_vertices, n_parts, part_u, part_v, owner, replicas)
+
+
+def ebv_partition(n_vertices, u, v, n_parts, keep_self_loops=True):
+    """EBV vertex cut (restating EBV_mpi.cpp; see drone_ebv_partition in include/drone_b200.h)."""
+    u, v = _i32(u), _i32(v)
+    e = len(u)
+    out_u = np.empty(max(e, 1), np.int32)
+    out_v = np.empty(max(e, 1), np.int32)
+    off = np.zeros(n_parts + 1, np.int64)
+    owner = np.empty(n_vertices, np.int32)
+    replicas = np.empty(n_vertices, np.int32)
+    check(_lib.lib().drone_ebv_partition(n_vertices, e, _vp(u), _vp(v), n_parts, int(bool(keep_self_loops)),
+                                         _vp(out_u), _vp(out_v), _vp(off), _vp(owner), _vp(replicas)))
+    part_u = [out_u[off[p]:off[p + 1]].copy() for p in range(n_parts)]
+    part_v = [out_v[off[p]:off[p + 1]].copy() for p in range(n_parts)]
+    return Partition(n_vertices, n_parts, part_u, part_v, owner, replicas)
+
+
+class LocalGraph:
+    """One rank's view: local numbering, CSR by source, routing tables (host numpy arrays) —
+    the content of struct Graph (cuda_gcn/src/cuda/graph.h:17-41) before it is copied to the device."""
+
+    def __init__(self, part, p):
+        lib = _lib.lib()
+        self.rank, self.n_parts, self.global_v = p, part.n_parts, part.n_vertices
+        u, v = part.part_u[p], part.part_v[p]
+        e = len(u)
+        cap = min(part.n_vertices, 2 * e) + 1
+        g2l = np.empty(part.n_vertices, np.int32)
+        l2g = np.empty(cap, np.int32)
+        index = np.empty(cap + 1, np.int32)
+        dst = np.empty(max(e, 1), np.int32)
+        n = C.c_int(0)
+        check(lib.drone_graph_build_host(part.n_vertices, e, _vp(u), _vp(v), _vp(g2l), _vp(l2g), _vp(index), _vp(dst),
+                                         C.byref(n)))
+        self.n_local = n.value
+        self.g2l = g2l
+        self.l2g = l2g[:self.n_local].copy()
+        self.index = index[:self.n_local + 1].copy()
+        self.dst = dst[:e].copy()
+        mv, num, wk = part.master_rows(p)
+        mr, ow = part.mirror_rows(p)
+        self.master_size, self.mirror_worker_size, self.mirror_size = len(mv), len(wk), len(mr)
+        self.master_worker_index = np.empty(self.n_local + 1, np.int32)
+        self.master2workers = np.empty(max(len(wk), 1), np.int32)
+        self.mirror2worker = np.empty(max(self.n_local, 1), np.int32)
+        check(lib.drone_route_tables_host(self.n_local, _vp(g2l), _vp(mv), _vp(num), _vp(wk), len(mv), len(wk),
+                                          _vp(mr), _vp(ow), len(mr), _vp(self.master_worker_index),
+                                          _vp(self.master2workers), _vp(self.mirror2worker)))
+        self.master2workers = self.master2workers[:len(wk)]
+        self.mirror2worker = self.mirror2worker[:self.n_local]
+
+    def local_degrees(self, global_in_degree, global_out_degree):
+        """Global degrees indexed by local id (setDegree, cuda_gcn/src/common/parser.cu:25-35)."""
+        return _i32(global_in_degree[self.l2g]), _i32(global_out_degree[self.l2g])
+
+
+class ExchangePlan:
+    """Static routing plan of one rank (drone_xplan)."""
+
+    def __init__(self, local_graph, max_features):
+        g = local_graph
+        self.rank, self.n_parts, self.n_local = g.rank, g.n_parts, g.n_local
+        self._keep = g
+        self._h = C.c_void_p(0)
+        check(_lib.lib().drone_xplan_create(C.byref(self._h), g.rank, g.n_parts, g.n_local, _vp(g.l2g),
+                                            _vp(g.mirror2worker), _vp(g.master_worker_index), _vp(g.master2workers),
+                                            int(max_features)))
+
+    @property
+    def handle(self):
+        return self._h
+
+    def counts(self):
+        up = np.zeros(self.n_parts, np.int32)
+        down = np.zeros(self.n_parts, np.int32)
+        nm = C.c_int(0)
+        check(_lib.lib().drone_xplan_counts(self._h, _vp(up), _vp(down), C.byref(nm)))
+        return up, down, nm.value
+
+    def lists(self):
+        up, down, _ = self.counts()
+        ur = np.empty(max(int(up.sum()), 1), np.int32)
+        dr = np.empty(max(int(down.sum()), 1), np.int32)
+        check(_lib.lib().drone_xplan_lists(self._h, _vp(ur), _vp(dr)))
+        return ur[:int(up.sum())], dr[:int(down.sum())]
+
+    def close(self):
+        if self._h.value:
+            _lib.lib().drone_xplan_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -134,6 +134,123 @@ int drone_spmm_host(drone_plan *plan, int orientation, int F,
 int drone_host_alloc(void **out, size_t bytes);
 int drone_host_free(void *ptr);
 
+/* ------------------------------------------------------------------------- */
+/* EBV vertex-cut exchange                                                     */
+/* ------------------------------------------------------------------------- */
+
+typedef struct drone_comm drone_comm;     /* one NCCL communicator + this process's rank */
+typedef struct drone_xplan drone_xplan;   /* static routing plan of one rank */
+
+#define DRONE_UNIQUE_ID_BYTES 128
+
+/*
+ * Communicator bootstrap without MPI: rank 0 calls drone_comm_unique_id and
+ * hands the 128 bytes to the other ranks by any means (file, socket,
+ * torch.distributed); every rank then calls drone_comm_create with its device
+ * current.  Replaces ncclGetUniqueId + MPI_Bcast + ncclCommInitRank in
+ * build_graph, cuda_gcn/src/cuda/graph.cu:39-52 (DRONE/src/cuda/graph.cu:31-37,
+ * 122-128 passes the id through the file ./nccl.id).
+ * drone_comm_adopt wraps a communicator the caller already owns (the
+ * reference's Comm.comm, cuda_gcn/src/cuda/graph.h:43-46); it is not destroyed
+ * with the handle.
+ */
+int drone_comm_unique_id(void *id_out, size_t id_bytes);
+int drone_comm_create(drone_comm **out, int rank, int nranks, const void *id, size_t id_bytes);
+int drone_comm_adopt(drone_comm **out, void *nccl_comm, int rank, int nranks);
+int drone_comm_destroy(drone_comm *comm);
+
+/* In-place sum over ranks of `count` floats (is_double = 0) or doubles (1).
+ * Replaces ncclAllReduce(globalDiff), DRONE/src/cuda/algorithm/pr.cu:365. */
+int drone_comm_allreduce_sum(drone_comm *comm, void *d_buf, size_t count, int is_double, void *stream);
+
+/*
+ * Routing plan of one rank, from the reference's routing tables (host arrays,
+ * indexed by local vertex id):
+ *   h_local2global[n_local]          Graph.Local2Global
+ *   h_mirror2worker[n_local]         Graph.Mirror2Worker: -1, or the rank owning the master copy
+ *   h_master_worker_index[n_local+1] Graph.MasterWorkerIndex  } CSR: ranks that hold a mirror
+ *   h_master2workers[...]            Graph.Master2Workers     } of each local master
+ * (cuda_gcn/src/cuda/graph.h:21-26, filled by addMasterRoute / addMirrorRoute,
+ * cuda_gcn/src/cuda/graph.cu:281-367).  Needs no GPU; device copies are made on
+ * first use.  max_features bounds F of later exchanges (it sizes the buffers).
+ * Replaces buffer_init / generateLen / calSendRecvLen / buffer_initIdx,
+ * cuda_gcn/src/cuda/cuda_communicate.cu:7-74,117-124.
+ */
+int drone_xplan_create(drone_xplan **out, int rank, int nranks, int n_local,
+                       const int *h_local2global, const int *h_mirror2worker,
+                       const int *h_master_worker_index, const int *h_master2workers,
+                       int max_features);
+int drone_xplan_destroy(drone_xplan *plan);
+
+/* Rows sent up (mirror -> master) and down (master -> mirror) per peer rank
+ * (arrays of nranks ints, either may be NULL), and the number of local master
+ * rows that receive contributions. */
+int drone_xplan_counts(const drone_xplan *plan, int *up_rows_per_peer, int *down_rows_per_peer,
+                       int *n_master_rows);
+/* The row lists themselves (local row ids, grouped by peer in rank order, ascending
+ * global id inside a group); sizes are the sums of drone_xplan_counts. */
+int drone_xplan_lists(const drone_xplan *plan, int *up_rows, int *down_rows);
+
+/*
+ * d_rows is [n_local, F] row-major with leading dimension ld.  On return every
+ * replica row of a vertex holds the sum of that vertex's rows over all ranks;
+ * rows of unreplicated vertices are untouched.  The master adds its mirrors'
+ * rows to its own in ascending rank order, so results are bit-reproducible.
+ * Collective over the communicator; asynchronous on `stream`.
+ * Replaces GraphSum_sync_value_nccl and GraphSum_sync_grad_nccl,
+ * cuda_gcn/src/cuda/cuda_communicate.cu:374-448 and :502-556 (pack kernels
+ * :126-207, sendID_Value :296-372, apply_sum :239-249, apply_assign :264-274).
+ */
+int drone_exchange_sum(drone_xplan *plan, drone_comm *comm, float *d_rows, int F, int ld, void *stream);
+
+/*
+ * The same exchange among n_parts plans held by ONE process on ONE device
+ * (plans[p] is rank p of n_parts, d_rows[p] its rows): messages become
+ * device-to-device copies.  For running all parts of a partition on a single
+ * GPU; no counterpart in the reference.
+ */
+int drone_exchange_sum_local(int n_parts, drone_xplan **plans, float **d_rows, int F, const int *ld,
+                             void *stream);
+
+/*
+ * EBV vertex-cut partitioner (host, single process).  Input: directed edge
+ * list in global ids.  Output: the edges grouped by part in the order the
+ * reference writes them to G.<p> (h_out_u/h_out_v hold all kept edges,
+ * h_part_offset[n_parts+1] delimits the parts), h_replicas[v] = number of parts
+ * holding v, h_owner[v] = part of v's master copy (-1 if v has no edge).
+ * keep_self_loops = 1 keeps edges u==u (the variant used for GCN inputs).
+ * Restates EBV_mpi.cpp:212-374 (deal, local-degree sort, batched scoring) and
+ * :549-581 (master = replica number id mod #replicas), as a simulation of its
+ * n_parts MPI ranks.
+ */
+int drone_ebv_partition(int n_vertices, long long n_edges, const int *h_u, const int *h_v,
+                        int n_parts, int keep_self_loops,
+                        int *h_out_u, int *h_out_v, long long *h_part_offset,
+                        int *h_owner, int *h_replicas);
+
+/*
+ * One rank's local graph from the edge list of its G.<p> file (host arrays in,
+ * host arrays out): local ids in first-seen order, CSR by source vertex with
+ * destinations in edge-list order.  h_g2l[global_v] gets -1 for absent
+ * vertices; h_l2g / h_index need room for min(global_v, 2*n_edges) (+1)
+ * entries.  The host half of build_graph, cuda_gcn/src/cuda/graph.cu:54-103
+ * (twin: DRONE/src/cuda/graph.cu).
+ */
+int drone_graph_build_host(int global_v, int n_edges, const int *h_u, const int *h_v,
+                           int *h_g2l, int *h_l2g, int *h_index, int *h_dst, int *n_local_out);
+
+/*
+ * Routing tables by local id from the rows of Master.<p> (master_vertex[i] has
+ * mirror_number[i] mirrors on the ranks listed consecutively in mirror_workers)
+ * and Mirror.<p> (mirror_vertex[i]'s master lives on master_worker[i]).
+ * Same tables as addMasterRoute / addMirrorRoute, cuda_gcn/src/cuda/graph.cu:281-367.
+ */
+int drone_route_tables_host(int n_local, const int *h_g2l,
+                            const int *master_vertex, const int *mirror_number, const int *mirror_workers,
+                            int master_size, int mirror_worker_size,
+                            const int *mirror_vertex, const int *master_worker, int mirror_size,
+                            int *h_master_worker_index, int *h_master2workers, int *h_mirror2worker);
+
 /*
  * Seeded R-MAT edge list (quadrant probabilities a, b, c, 1-a-b-c; `scale` bits
  * per endpoint).  Edge number e depends only on (seed, e): the device and host
