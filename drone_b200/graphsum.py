@@ -1,0 +1,119 @@
+"""Host-side mirror of the reference's GraphSum layer over the C ABI.
+
+GraphSum keeps the constructor arguments, the forward(training)/backward() interface and the
+side effects of CUDAGraphSum (cuda_gcn/src/cuda/cuda_module.cuh:83-84, cuda_module.cu:149-389):
+forward overwrites out.data with A^T · in.data and then makes every replica row hold the global
+sum; backward overwrites in.grad with A · out.grad and syncs it the same way.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import OP_A, OP_AT, check
+from .plan import AggregationPlan, _stream_ptr
+from .partition import ExchangePlan
+
+
+class Variable:
+    """data/grad pair of a layer boundary (CUDAVariable, cuda_gcn/src/cuda/cuda_variable.cuh:17-30)."""
+
+    def __init__(self, n_rows, dim, device, requires_grad=True):
+        self.data = torch.zeros((n_rows, dim), dtype=torch.float32, device=device)
+        self.grad = torch.zeros((n_rows, dim), dtype=torch.float32, device=device) if requires_grad else None
+        self.size = n_rows * dim
+
+
+class Comm:
+    """One NCCL communicator owned by the library (Comm{ncclComm_t, stream}, cuda_gcn/src/cuda/graph.h:43-46).
+    The unique id travels through torch.distributed when it is initialised, otherwise through `id_bytes`."""
+
+    def __init__(self, rank, nranks, id_bytes=None):
+        lib = _lib.lib()
+        self.rank, self.nranks = rank, nranks
+        if id_bytes is None:
+            import torch.distributed as dist
+            box = [None]
+            if rank == 0:
+                buf = C.create_string_buffer(128)
+                check(lib.drone_comm_unique_id(buf, 128))
+                box[0] = buf.raw
+            dist.broadcast_object_list(box, src=0)
+            id_bytes = box[0]
+        self._h = C.c_void_p(0)
+        check(lib.drone_comm_create(C.byref(self._h), rank, nranks, id_bytes, len(id_bytes)))
+
+    @staticmethod
+    def unique_id():
+        buf = C.create_string_buffer(128)
+        check(_lib.lib().drone_comm_unique_id(buf, 128))
+        return buf.raw
+
+    @property
+    def handle(self):
+        return self._h
+
+    def allreduce_sum(self, t, stream=None):
+        check(_lib.lib().drone_comm_allreduce_sum(self._h, C.c_void_p(t.data_ptr()), t.numel(),
+                                                  int(t.dtype == torch.float64), _stream_ptr(stream)))
+
+    def close(self):
+        if self._h.value:
+            _lib.lib().drone_comm_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+
+class DeviceGraph:
+    """A rank's local graph on its GPU: CSR by source, global degrees by local id, routing plan."""
+
+    def __init__(self, local_graph, global_in_degree, global_out_degree, device, max_features):
+        g = local_graph
+        self.host = g
+        self.n_local = g.n_local
+        self.device = device
+        self.index = torch.as_tensor(g.index, device=device)
+        self.dst = torch.as_tensor(g.dst, device=device)
+        ind, outd = g.local_degrees(np.asarray(global_in_degree), np.asarray(global_out_degree))
+        self.in_degree = torch.as_tensor(ind, device=device)
+        self.out_degree = torch.as_tensor(outd, device=device)
+        self.mirror2worker = torch.as_tensor(g.mirror2worker, device=device)
+        self.xplan = ExchangePlan(g, max_features)
+        self.plan = AggregationPlan(self.index, self.dst, in_degree=self.in_degree, out_degree=self.out_degree)
+
+
+def exchange_sum(xplan, comm, rows, stream=None):
+    """Mirror -> master sum, master -> mirror assign on a [n_local, F] tensor (in place)."""
+    f = rows.shape[1]
+    ld = rows.stride(0) if rows.shape[0] > 1 else max(f, rows.stride(0))
+    check(_lib.lib().drone_exchange_sum(xplan.handle, comm.handle, C.c_void_p(rows.data_ptr()), f, int(ld),
+                                        _stream_ptr(stream)))
+
+
+def exchange_sum_local(xplans, rows_list, stream=None):
+    """The same exchange among all parts held on one device."""
+    n = len(xplans)
+    f = rows_list[0].shape[1]
+    plans = (C.c_void_p * n)(*[x.handle for x in xplans])
+    ptrs = (C.c_void_p * n)(*[C.c_void_p(r.data_ptr()) for r in rows_list])
+    lds = (C.c_int * n)(*[int(r.stride(0)) if r.shape[0] > 1 else f for r in rows_list])
+    check(_lib.lib().drone_exchange_sum_local(n, plans, ptrs, f, lds, _stream_ptr(stream)))
+
+
+class GraphSum:
+    """Drop-in shape of CUDAGraphSum: GraphSum(in, out, graph, comm, dim, worker_id, worker_num, name, layer)."""
+
+    def __init__(self, in_var, out_var, graph, comm, dim, worker_id=0, worker_num=1, name="graphSum", layer=0):
+        self.inp, self.out, self.graph, self.comm = in_var, out_var, graph, comm
+        self.dim, self.worker_id, self.worker_num = dim, worker_id, worker_num
+        self.ModuleName, self.layer = name, layer
+
+    def forward(self, training=True):
+        self.graph.plan.spmm(OP_AT, self.inp.data, out=self.out.data)
+        if self.worker_num > 1:
+            exchange_sum(self.graph.xplan, self.comm, self.out.data)
+
+    def backward(self):
+        self.graph.plan.spmm(OP_A, self.out.grad, out=self.inp.grad)
+        if self.worker_num > 1:
+            exchange_sum(self.graph.xplan, self.comm, self.inp.grad)

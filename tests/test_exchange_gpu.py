@@ -1,0 +1,104 @@
+"""The exchange kernels on real devices: all parts on one GPU (device-to-device copies), and, when the
+box has at least two GPUs, one process per GPU over NCCL through the GraphSum module."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import drone_b200 as db
+from drone_b200 import graphgen as gg
+from drone_b200 import graphsum as gs
+from drone_b200 import partition as pt
+from helpers import assert_close_to_oracle
+from test_exchange_cpu import setup_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("parts,f", [(2, 32), (4, 41), (8, 64)])
+def test_all_parts_on_one_gpu(cuda_device, oracle, parts, f):
+    n, part, in_deg, out_deg, x, want_fwd, want_bwd = setup_case(oracle, parts, scale=11, seed=8, f=f, sym=True)
+    graphs = [gs.DeviceGraph(part.local_graph(p), in_deg, out_deg, cuda_device, max_features=64) for p in range(parts)]
+    for op, want in ((db.OP_AT, want_fwd), (db.OP_A, want_bwd)):
+        rows = [g.plan.spmm(op, torch.as_tensor(x[g.host.l2g], device=cuda_device)) for g in graphs]
+        before = [r.clone() for r in rows]
+        gs.exchange_sum_local([g.xplan for g in graphs], rows)
+        torch.cuda.synchronize()
+        scale = np.abs(want).max()
+        for p, g in enumerate(graphs):
+            assert_close_to_oracle(rows[p].cpu().numpy(), want[g.host.l2g])
+            # rows of unreplicated vertices are not touched by the exchange
+            single = torch.as_tensor(part.replicas[g.host.l2g] == 1, device=cuda_device)
+            assert torch.equal(rows[p][single], before[p][single])
+        # every replica of a vertex holds the same bits
+        glob = {}
+        for p, g in enumerate(graphs):
+            host = rows[p].cpu().numpy()
+            for loc in np.nonzero(part.replicas[g.host.l2g] > 1)[0][:300]:
+                key = int(g.host.l2g[loc])
+                if key in glob:
+                    assert np.array_equal(glob[key], host[loc])
+                glob[key] = host[loc]
+        assert scale > 0
+
+
+def test_exchange_is_repeatable_and_checks_arguments(cuda_device, oracle):
+    n, part, in_deg, out_deg, x, want_fwd, _ = setup_case(oracle, 3, scale=10, seed=9, f=16)
+    graphs = [gs.DeviceGraph(part.local_graph(p), in_deg, out_deg, cuda_device, max_features=16) for p in range(3)]
+    outs = []
+    for _ in range(2):
+        rows = [g.plan.spmm(db.OP_AT, torch.as_tensor(x[g.host.l2g], device=cuda_device)) for g in graphs]
+        gs.exchange_sum_local([g.xplan for g in graphs], rows)
+        outs.append([r.clone() for r in rows])
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    wide = [torch.zeros((g.n_local, 32), device=cuda_device) for g in graphs]
+    with pytest.raises(db.DroneError, match="max_features|F="):
+        gs.exchange_sum_local([g.xplan for g in graphs], wide)
+
+
+def _nccl_rank(rank, world, port, ok):
+    import torch.distributed as dist
+    from oracle import oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        f = 32
+        n, part, in_deg, out_deg, x, want_fwd, want_bwd = setup_case(oracle, world, scale=11, seed=10, f=f, sym=True)
+        comm = gs.Comm(rank, world)
+        g = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, dev, max_features=f)
+        a, b = gs.Variable(g.n_local, f, dev), gs.Variable(g.n_local, f, dev)
+        layer = gs.GraphSum(a, b, g, comm, f, rank, world, "graphSum_test", 0)
+        a.data.copy_(torch.as_tensor(x[g.host.l2g]))
+        layer.forward(True)
+        b.grad.copy_(torch.as_tensor(x[g.host.l2g]))
+        layer.backward()
+        torch.cuda.synchronize()
+        assert_close_to_oracle(b.data.cpu().numpy(), want_fwd[g.host.l2g])
+        assert_close_to_oracle(a.grad.cpu().numpy(), want_bwd[g.host.l2g])
+        ok[rank] = 1
+        dist.barrier()
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_graphsum_over_nccl_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ok = ctx.Array("i", [0, 0])
+    port = 29600 + os.getpid() % 2000
+    procs = [ctx.Process(target=_nccl_rank, args=(r, 2, port, ok)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    assert all(p.exitcode == 0 for p in procs)
+    assert list(ok) == [1, 1]

@@ -1,0 +1,119 @@
+"""EBV partitioner and routing tables (host code, no GPU)."""
+import numpy as np
+import pytest
+
+from drone_b200 import graphgen as gg
+from drone_b200 import partition as pt
+from oracle import ebv_oracle
+
+
+def small_graph(scale=9, seed=3, sym=True):
+    n, u, v = gg.rmat_graph(scale, 8, seed=seed, symmetrise=sym, self_loops="add")
+    return n, u.numpy(), v.numpy()
+
+
+@pytest.mark.parametrize("parts", [1, 2, 3, 8])
+def test_vertex_cut_invariants(parts):
+    n, u, v = small_graph()
+    p = pt.ebv_partition(n, u, v, parts)
+    # every edge lives in exactly one part
+    all_edges = np.concatenate([pu.astype(np.int64) * n + pv for pu, pv in zip(p.part_u, p.part_v)])
+    assert len(all_edges) == len(u)
+    assert np.array_equal(np.sort(all_edges), np.sort(u.astype(np.int64) * n + v))
+    # replica counts and owners agree with where the edges went
+    present = np.stack([p.present(q) for q in range(parts)])
+    assert np.array_equal(present.sum(0), p.replicas)
+    has_edge = p.replicas > 0
+    assert (p.owner[has_edge] >= 0).all() and (p.owner[~has_edge] == -1).all()
+    assert present[p.owner[has_edge], np.nonzero(has_edge)[0]].all()       # the owner holds the vertex
+    # master rule of the reference: replica number (id mod #replicas), parts ascending
+    for x in np.nonzero(p.replicas > 1)[0][:200]:
+        holders = np.nonzero(present[:, x])[0]
+        assert p.owner[x] == holders[x % len(holders)]
+    # Master.<p> and Mirror.<p> are mutually consistent
+    mirrors_seen = {}
+    for q in range(parts):
+        mv, num, wk = p.master_rows(q)
+        assert num.sum() == len(wk) and (num >= 1).all()
+        pos = 0
+        for x, k in zip(mv.tolist(), num.tolist()):
+            for w in wk[pos:pos + k].tolist():
+                mirrors_seen[(x, w)] = q
+            pos += k
+    count = 0
+    for q in range(parts):
+        mr, ow = p.mirror_rows(q)
+        for x, o in zip(mr.tolist(), ow.tolist()):
+            assert mirrors_seen[(x, q)] == o
+            count += 1
+    assert count == len(mirrors_seen) == int((p.replicas[p.replicas > 1] - 1).sum())
+    if parts > 1:
+        assert p.edge_imbalance() < 1.3
+        assert 1.0 <= p.replication_factor() <= parts
+
+
+def test_matches_python_restatement():
+    n, u, v = small_graph(scale=7, seed=11, sym=False)
+    for parts, keep in ((2, True), (4, True), (3, False)):
+        p = pt.ebv_partition(n, u, v, parts, keep_self_loops=keep)
+        ref_parts, ref_owner, ref_rep = ebv_oracle.ebv_partition(n, list(zip(u.tolist(), v.tolist())), parts, keep)
+        for q in range(parts):
+            assert list(zip(p.part_u[q].tolist(), p.part_v[q].tolist())) == ref_parts[q]
+        assert p.owner.tolist() == ref_owner and p.replicas.tolist() == ref_rep
+
+
+def test_self_loops_dropped_like_root_partitioner():
+    n, u, v = small_graph(scale=7, seed=12)
+    p = pt.ebv_partition(n, u, v, 2, keep_self_loops=False)
+    assert sum(len(x) for x in p.part_u) == int((u != v).sum())
+    assert all((pu != pv).all() for pu, pv in zip(p.part_u, p.part_v))
+
+
+def test_file_round_trip(tmp_path):
+    n, u, v = small_graph(scale=8, seed=13)
+    p = pt.ebv_partition(n, u, v, 3)
+    p.write_files(str(tmp_path))
+    first = open(tmp_path / "G.0").readline().split()
+    assert len(first) == 2                                        # "u v" per line
+    q = pt.read_partition_files(str(tmp_path), n, 3)
+    for a, b in zip(p.part_u + p.part_v, q.part_u + q.part_v):
+        assert np.array_equal(a, b)
+    assert np.array_equal(p.replicas, q.replicas)
+    rep = p.replicas > 1
+    assert np.array_equal(p.owner[rep], q.owner[rep])
+    for k in range(3):
+        for a, b in zip(p.master_rows(k) + p.mirror_rows(k), q.master_rows(k) + q.mirror_rows(k)):
+            assert np.array_equal(a, b)
+
+
+def test_local_graph_follows_reference_numbering(oracle):
+    n, u, v = small_graph(scale=8, seed=14)
+    p = pt.ebv_partition(n, u, v, 2)
+    for k in range(2):
+        g = p.local_graph(k)
+        nloc, g2l, l2g, index, dst = oracle.build_graph(n, p.part_u[k], p.part_v[k])
+        assert g.n_local == nloc
+        assert np.array_equal(g.g2l, g2l) and np.array_equal(g.l2g, l2g)
+        assert np.array_equal(g.index, index) and np.array_equal(g.dst, dst)
+        # routing tables by local id
+        mr, ow = p.mirror_rows(k)
+        want = np.full(nloc, -1, np.int32)
+        want[g2l[mr]] = ow
+        assert np.array_equal(g.mirror2worker, want)
+        mv, num, wk = p.master_rows(k)
+        deg = np.zeros(nloc, np.int64)
+        deg[g2l[mv]] = num
+        assert np.array_equal(np.diff(g.master_worker_index), deg)
+        pos = 0
+        for x, c in zip(mv.tolist(), num.tolist()):
+            lo = g.master_worker_index[g2l[x]]
+            assert g.master2workers[lo:lo + c].tolist() == wk[pos:pos + c].tolist()
+            pos += c
+
+
+def test_bad_input_is_an_error():
+    import drone_b200 as db
+    with pytest.raises(db.DroneError, match="outside"):
+        pt.ebv_partition(4, np.array([0, 9], np.int32), np.array([1, 2], np.int32), 2)
+    with pytest.raises(db.DroneError, match="n_parts"):
+        pt.ebv_partition(4, np.array([0], np.int32), np.array([1], np.int32), 0)
