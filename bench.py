@@ -51,11 +51,15 @@ def parse_args():
 
 def workload_config(args):
     if args.workload == "custom":
-        return dict(scale=args.scale, edge_factor=args.edge_factor, features=args.features,
-                    symmetrise=args.symmetrise, seed=20261199)
-    cfg = dict(WORKLOADS[args.workload])
-    if args.features:
-        cfg["features"] = args.features
+        cfg = dict(scale=args.scale, edge_factor=args.edge_factor, features=args.features,
+                   symmetrise=args.symmetrise, seed=20261199)
+    else:
+        cfg = dict(WORKLOADS[args.workload])
+        if args.features:
+            cfg["features"] = args.features
+    # weak scaling: the graph doubles with the GPU count, so every EBV part keeps the single-GPU edge count
+    n = max(args.gpus, 1)
+    cfg["scale"] += max(n.bit_length() - 1, 0)
     return cfg
 
 
@@ -177,7 +181,7 @@ def run_reference(args, cfg):
     line = {
         "impl": "reference", "metric": "spmm_nnzF_per_s", "value": value, "unit": "nnz*F/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_descr(args, cfg, n, nnz),
         "cpu_baseline": {"value": value, "unit": "nnz*F/s", "cores": threads, "kind": "port",
                          "sample": "whole workload, one CSR SpMM per step, all host threads (OpenMP row-parallel)"},
@@ -197,12 +201,11 @@ def workload_descr(args, cfg, n, nnz):
 def run_ours(args, cfg):
     import drone_b200 as db
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the aggregation path has no CPU fallback")
     if world > 1:
-        raise SystemExit("bench.py: multi-GPU path not wired yet")
+        return run_ours_multi(args, cfg)
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     lib = db.lib()
@@ -266,7 +269,7 @@ def run_ours(args, cfg):
 
     line = {
         "metric": "spmm_nnzF_per_s", "value": value, "unit": "nnz*F/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_descr(args, cfg, n, nnz),
         "ms_per_step_median": float(np.median(per_step)), "ms_per_step_min": float(per_step.min()),
@@ -314,6 +317,165 @@ def run_ours(args, cfg):
                                 "sample": "whole workload, best of %d runs of the oracle's OpenMP float CSR SpMM"
                                           % len(times), "ms": 1e3 * best}
     print(json.dumps(line), flush=True)
+
+
+def run_ours_multi(args, cfg):
+    """One process per GPU: R-MAT graph EBV-partitioned into WORLD_SIZE parts, every step is the local
+    aggregation Y_p = A_p^T X_p followed by the mirror/master exchange over NCCL."""
+    import torch.distributed as dist
+    import drone_b200 as db
+    from drone_b200 import graphgen as gg
+    from drone_b200 import graphsum as gs
+    from drone_b200 import partition as pt
+
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ["RANK"])
+    local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=device)
+    lib = db.lib()
+    f = cfg["features"]
+    n = 1 << cfg["scale"]
+
+    # rank 0 builds and partitions the graph; everybody receives the parts
+    t_setup = time.perf_counter()
+    meta = torch.zeros(2 + world + 1, dtype=torch.int64, device=device)
+    if rank == 0:
+        _, u, v = gg.rmat_graph(cfg["scale"], cfg["edge_factor"], seed=cfg["seed"], device=device,
+                                symmetrise=cfg["symmetrise"], self_loops="add")
+        in_deg, out_deg = gg.degrees(u, v, n)
+        part = pt.ebv_partition(n, u.cpu().numpy(), v.cpu().numpy(), world, keep_self_loops=True)
+        del u, v
+        sizes = [len(x) for x in part.part_u]
+        meta[0], meta[1] = sum(sizes), n
+        meta[2:2 + world + 1] = torch.tensor(np.concatenate([[0], np.cumsum(sizes)]))
+    dist.broadcast(meta, 0)
+    total_e = int(meta[0])
+    offs = meta[2:].cpu().numpy()
+    if rank == 0:
+        eu = torch.as_tensor(np.concatenate(part.part_u), device=device)
+        ev = torch.as_tensor(np.concatenate(part.part_v), device=device)
+        owner = torch.as_tensor(part.owner, device=device)
+        reps = torch.as_tensor(part.replicas, device=device)
+    else:
+        eu = torch.empty(total_e, dtype=torch.int32, device=device)
+        ev = torch.empty(total_e, dtype=torch.int32, device=device)
+        owner = torch.empty(n, dtype=torch.int32, device=device)
+        reps = torch.empty(n, dtype=torch.int32, device=device)
+        in_deg = torch.empty(n, dtype=torch.int32, device=device)
+        out_deg = torch.empty(n, dtype=torch.int32, device=device)
+    for t in (eu, ev, owner, reps, in_deg, out_deg):
+        dist.broadcast(t, 0)
+    if rank != 0:
+        eu_h, ev_h = eu.cpu().numpy(), ev.cpu().numpy()
+        part = pt.Partition(n, world, [eu_h[offs[p]:offs[p + 1]] for p in range(world)],
+                            [ev_h[offs[p]:offs[p + 1]] for p in range(world)], owner.cpu().numpy(),
+                            reps.cpu().numpy())
+    del eu, ev, owner, reps
+    graph = gs.DeviceGraph(part.local_graph(rank), in_deg.cpu().numpy(), out_deg.cpu().numpy(), device, max_features=f)
+    comm = gs.Comm(rank, world)
+    nnz_local = graph.dst.numel()
+    nnz_total = total_e
+    up, down, _ = graph.xplan.counts()
+    sync_bytes = int(up.sum() + down.sum()) * f * 4
+    setup_s = time.perf_counter() - t_setup
+
+    nbuf = 3
+    gen = torch.Generator(device=device)
+    gen.manual_seed(cfg["seed"] + rank)
+    xs = [torch.randn((graph.n_local, f), device=device, generator=gen) for _ in range(nbuf)]
+    ys = [torch.empty((graph.n_local, f), device=device) for _ in range(nbuf)]
+
+    def step(i):
+        graph.plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
+        gs.exchange_sum(graph.xplan, comm, ys[i % nbuf])
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(index=local_rank)
+    sampler.start()
+    launches0 = lib.drone_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    launches = lib.drone_kernel_launch_count() - launches0
+    clocks = sampler.finish()
+    t_ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+    ms = float(t_ms) / args.steps
+
+    # local aggregation alone (for the roofline of the kernel) and exchange alone
+    e0.record()
+    for i in range(args.steps):
+        graph.plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
+    e1.record()
+    torch.cuda.synchronize()
+    spmm_ms = e0.elapsed_time(e1) / args.steps
+    dist.barrier()
+    e0.record()
+    for i in range(args.steps):
+        gs.exchange_sum(graph.xplan, comm, ys[i % nbuf])
+    e1.record()
+    torch.cuda.synchronize()
+    xchg = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device)
+    dist.all_reduce(xchg, op=dist.ReduceOp.MAX)
+
+    # end to end: host operands in, host result out, every step
+    xh = torch.empty((graph.n_local, f), dtype=torch.float32).pin_memory()
+    yh = torch.empty((graph.n_local, f), dtype=torch.float32).pin_memory()
+    xh.copy_(xs[0])
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        xs[0].copy_(xh, non_blocking=True)
+        step(0)
+        yh.copy_(ys[0], non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_t = torch.tensor([(time.perf_counter() - t0) / args.e2e_steps], device=device, dtype=torch.float64)
+    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    stats = torch.tensor([graph.n_local, nnz_local, sync_bytes, launches], device=device, dtype=torch.int64)
+    gathered = [torch.zeros_like(stats) for _ in range(world)]
+    dist.all_gather(gathered, stats)
+
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+        else:
+            peak, peak_src = 6650.0, "fallback"
+        b_alg = algorithmic_bytes(graph.n_local, nnz_local, f)
+        achieved = b_alg / (spmm_ms * 1e-3) / 1e9
+        g = torch.stack(gathered).cpu().numpy()
+        line = {
+            "metric": "spmm_nnzF_per_s", "value": nnz_total * f / (ms * 1e-3), "unit": "nnz*F/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict(workload_descr(args, cfg, n, nnz_total), parts=world, partitioner="EBV",
+                           replication_factor=float(g[:, 0].sum()) / n,
+                           edge_imbalance=float(g[:, 1].max() * world / g[:, 1].sum())),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src, "algorithmic_bytes": b_alg,
+                         "kernel": "rank 0's local drone_spmm call, timed alone", "ms": spmm_ms},
+            "exchange": {"ms": float(xchg), "mirror_sync_bytes_per_step_all_ranks": int(g[:, 2].sum()),
+                         "mirror_sync_bytes_per_step_rank0": sync_bytes, "collective": "grouped ncclSend/ncclRecv x2"},
+            "e2e": {"value": nnz_total * f / float(e2e_t), "unit": "nnz*F/s", "h2d_bytes_per_step": int(g[:, 0].sum()) * f * 4,
+                    "d2h_bytes_per_step": int(g[:, 0].sum()) * f * 4, "ms_per_step": 1e3 * float(e2e_t),
+                    "steps": args.e2e_steps},
+            "gpu_launches": int(g[:, 3].sum()), "clocks": clocks, "setup_s": setup_s,
+        }
+        print(json.dumps(line), flush=True)
+    comm.close()
+    dist.destroy_process_group()
 
 
 def main():

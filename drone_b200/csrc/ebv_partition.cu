@@ -22,13 +22,61 @@
 #include "common.cuh"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
+#include <functional>
+#include <thread>
 #include <vector>
 
 namespace drone {
 
 struct EbvEdge {
     int u, v, key;
+};
+
+// Runs job(i) for i in [0, n) on up to `threads` host threads, repeatedly, with the workers kept alive
+// between calls (the partitioner has tens of thousands of short parallel phases).
+class PhasePool {
+public:
+    explicit PhasePool(int threads) : n_threads_(threads > 1 ? threads : 1) {
+        for (int t = 1; t < n_threads_; ++t) workers_.emplace_back([this, t] { loop(t); });
+    }
+    ~PhasePool() {
+        stop_.store(true);
+        generation_.fetch_add(1);
+        for (auto &w : workers_) w.join();
+    }
+    void run(int n, const std::function<void(int)> &job) {
+        job_ = &job;
+        n_items_ = n;
+        next_.store(0);
+        pending_.store(n_threads_ - 1);
+        generation_.fetch_add(1);
+        work();
+        while (pending_.load(std::memory_order_acquire) != 0) std::this_thread::yield();
+    }
+
+private:
+    void work() {
+        for (int i = next_.fetch_add(1); i < n_items_; i = next_.fetch_add(1)) (*job_)(i);
+    }
+    void loop(int) {
+        unsigned long long seen = 0;
+        for (;;) {
+            while (generation_.load(std::memory_order_acquire) == seen) std::this_thread::yield();
+            seen = generation_.load();
+            if (stop_.load()) return;
+            work();
+            pending_.fetch_sub(1, std::memory_order_release);
+        }
+    }
+    int n_threads_;
+    std::vector<std::thread> workers_;
+    const std::function<void(int)> *job_ = nullptr;
+    int n_items_ = 0;
+    std::atomic<int> next_{0}, pending_{0};
+    std::atomic<unsigned long long> generation_{0};
+    std::atomic<bool> stop_{false};
 };
 
 static inline bool bit_get(const std::vector<uint64_t> &b, int i) { return (b[(size_t)i >> 6] >> (i & 63)) & 1ULL; }
@@ -57,25 +105,24 @@ extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int 
         if (!keep_self_loops && h_u[i] == h_v[i]) continue;
         share[(size_t)(i % P)].push_back({h_u[i], h_v[i], 0});
     }
+    int hw = (int)std::thread::hardware_concurrency();
+    if (hw < 1) hw = 1;
+    PhasePool pool(std::min(P, hw));
     long long kept = 0;
-    {
-        std::vector<int> deg((size_t)n_vertices);
-        for (int r = 0; r < P; ++r) {
-            std::fill(deg.begin(), deg.end(), 0);
-            for (const EbvEdge &e : share[r]) { deg[e.u]++; deg[e.v]++; }
-            for (EbvEdge &e : share[r]) e.key = deg[e.u] + deg[e.v];
-            std::stable_sort(share[r].begin(), share[r].end(),
-                             [](const EbvEdge &a, const EbvEdge &b) { return a.key < b.key; });
-            kept += (long long)share[r].size();
-        }
-    }
+    pool.run(P, [&](int r) {
+        std::vector<int> deg((size_t)n_vertices, 0);
+        for (const EbvEdge &e : share[r]) { deg[e.u]++; deg[e.v]++; }
+        for (EbvEdge &e : share[r]) e.key = deg[e.u] + deg[e.v];
+        std::stable_sort(share[r].begin(), share[r].end(),
+                         [](const EbvEdge &a, const EbvEdge &b) { return a.key < b.key; });
+    });
+    for (int r = 0; r < P; ++r) kept += (long long)share[r].size();
 
     std::vector<std::vector<uint64_t>> has(P, std::vector<uint64_t>(((size_t)n_vertices + 63) / 64, 0));
     std::vector<long long> edge_count(P, 0), vertex_count(P, 0);
     std::vector<std::vector<int>> part_u(P), part_v(P);
     // assignment of this round: for each (sender, part) the edges in sender order
     std::vector<std::vector<int>> sent((size_t)P * P);
-    std::vector<double> weight(P);
 
     long long longest = 0;
     for (int r = 0; r < P; ++r) longest = std::max<long long>(longest, (long long)share[r].size());
@@ -83,7 +130,8 @@ extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int 
     for (long long start = 0; start < longest; start += batch,
                    batch = batch < max_batch ? std::min((int)(batch * 1.3), max_batch) : batch) {
         for (auto &s : sent) s.clear();
-        for (int r = 0; r < P; ++r) {
+        // scoring: every simulated rank reads the state left by the previous round only
+        pool.run(P, [&](int r) {
             const long long edges_r = (long long)share[r].size();
             const long long end = std::min<long long>(start + batch, edges_r);
             for (long long i = start; i < end; ++i) {
@@ -101,8 +149,9 @@ extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int 
                 sent[(size_t)r * P + best].push_back(e.u);
                 sent[(size_t)r * P + best].push_back(e.v);
             }
-        }
-        for (int p = 0; p < P; ++p)
+        });
+        // hand-over: every part appends what it was sent, in sender order, and updates its own state
+        pool.run(P, [&](int p) {
             for (int r = 0; r < P; ++r) {
                 const std::vector<int> &s = sent[(size_t)r * P + p];
                 for (size_t k = 0; k < s.size(); k += 2) {
@@ -114,6 +163,7 @@ extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int 
                 }
                 edge_count[p] += (long long)(s.size() / 2);
             }
+        });
     }
 
     long long off = 0;

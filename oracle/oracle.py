@@ -53,7 +53,9 @@ def _f32(a):
 
 
 def max_threads():
-    return int(lib().oracle_max_threads())
+    """Host threads the timed CPU product may use: every core, whatever OMP_NUM_THREADS says
+    (launchers such as torchrun pin it to 1)."""
+    return max(int(os.cpu_count() or 1), int(lib().oracle_max_threads()))
 
 
 def build_graph(global_v, u, v):
