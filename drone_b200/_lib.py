@@ -22,6 +22,18 @@ class DroneError(RuntimeError):
         self.code = code
 
 
+class PRResponse(C.Structure):
+    _fields_ = [("Mirror2MasterSendSize", C.c_int), ("Mirror2MasterRecvSize", C.c_int),
+                ("Master2MirrorSendSize", C.c_int), ("Master2MirrorRecvSize", C.c_int),
+                ("VisitedSize", C.c_int), ("LocalVertexSize", C.c_int),
+                ("CalTime", C.c_float), ("SendTime", C.c_float)]
+
+    def is_empty(self):
+        """IsEmpty of the Go bridge, DRONE/src/tools/cuda_convert.go:47-52."""
+        return (self.Mirror2MasterSendSize == 0 and self.Mirror2MasterRecvSize == 0 and
+                self.Master2MirrorSendSize == 0 and self.Master2MirrorRecvSize == 0)
+
+
 class PlanStats(C.Structure):
     _fields_ = [
         ("n_rows", C.c_int),
@@ -65,6 +77,15 @@ def _declare(lib):
         "drone_xplan_lists": (i, [vp, vp, vp]),
         "drone_exchange_sum": (i, [vp, vp, vp, i, i, vp]),
         "drone_exchange_sum_local": (i, [i, C.POINTER(vp), C.POINTER(vp), i, C.POINTER(i), vp]),
+        "drone_pr_create": (i, [C.POINTER(vp), i, i, i, vp, vp, vp, vp, vp, vp, i, C.c_double]),
+        "drone_pr_destroy": (i, [vp]),
+        "drone_pr_peval": (i, [vp, C.POINTER(PRResponse), vp]),
+        "drone_pr_inceval": (i, [vp, C.POINTER(PRResponse), vp]),
+        "drone_pr_power_iterate": (i, [vp, i, C.c_double, vp]),
+        "drone_pr_step_local": (i, [i, C.POINTER(vp), i, C.POINTER(PRResponse), vp]),
+        "drone_pr_power_iterate_local": (i, [i, C.POINTER(vp), i, C.c_double, vp]),
+        "drone_pr_values": (i, [vp, vp, vp]),
+        "drone_pr_set_isolated_count": (i, [vp, ll]),
         "drone_ebv_partition": (i, [i, ll, vp, vp, i, i, vp, vp, vp, vp, vp]),
         "drone_graph_build_host": (i, [i, i, vp, vp, vp, vp, vp, vp, C.POINTER(i)]),
         "drone_route_tables_host": (i, [i, vp, vp, vp, vp, i, i, vp, vp, i, vp, vp, vp]),

@@ -12,41 +12,10 @@
 //     gather mirror rows -> all-to-all-v -> add at masters in ascending peer
 //     order (and gather the totals) -> all-to-all-v -> scatter into mirror rows.
 // The additions have a fixed order, so results are bit-reproducible.
-#include "common.cuh"
+#include "exchange.cuh"
 
-#include <nccl.h>
 #include <algorithm>
 #include <new>
-#include <vector>
-
-struct drone_comm {
-    ncclComm_t comm = nullptr;
-    int rank = 0, nranks = 1;
-    bool owned = false;
-};
-
-struct drone_xplan {
-    int rank = 0, nranks = 1, n_local = 0, max_features = 0;
-    // host lists, grouped by peer (offsets have nranks+1 entries)
-    std::vector<int> up_rows, up_off;        // my mirror rows, by owner, ascending global id
-    std::vector<int> down_rows, down_off;    // my master rows, by mirroring peer, ascending global id
-    // master rows that have at least one mirror, with the positions of their
-    // contributions in the received buffer (CSR: m_off / m_pos), peers ascending
-    std::vector<int> m_rows, m_off, m_pos;
-    // device copies
-    int device = -1;
-    int *d_up_rows = nullptr, *d_down_rows = nullptr, *d_m_rows = nullptr, *d_m_off = nullptr, *d_m_pos = nullptr;
-    float *d_send = nullptr, *d_recv = nullptr;   // each max(up, down) * max_features floats
-    size_t buf_floats = 0;
-};
-
-#define DRONE_NCCL(call)                                                                 \
-    do {                                                                                 \
-        ncclResult_t r__ = (call);                                                       \
-        if (r__ != ncclSuccess)                                                          \
-            return drone::set_error(DRONE_E_NCCL, "%s failed at %s:%d: %s", #call,       \
-                                    __FILE__, __LINE__, ncclGetErrorString(r__));        \
-    } while (0)
 
 namespace drone {
 
@@ -100,7 +69,7 @@ static int upload(T **dst, const std::vector<T> &src) {
     return DRONE_OK;
 }
 
-static int ensure_device(drone_xplan *x) {
+int xplan_ensure_device(drone_xplan *x) {
     int dev = -1;
     DRONE_CUDA(cudaGetDevice(&dev));
     if (x->device == dev) return DRONE_OK;
@@ -309,7 +278,7 @@ int drone_exchange_sum(drone_xplan *x, drone_comm *c, float *d_rows, int F, int 
     DRONE_REQUIRE(ld >= F, "drone_exchange_sum: ld=%d below F=%d", ld, F);
     if (x->nranks == 1) return DRONE_OK;
     DRONE_REQUIRE(d_rows != nullptr || x->n_local == 0, "drone_exchange_sum: rows is NULL");
-    int rc = ensure_device(x);
+    int rc = xplan_ensure_device(x);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     const int n_up = (int)x->up_rows.size(), n_down = (int)x->down_rows.size(), n_m = (int)x->m_rows.size();
@@ -348,7 +317,7 @@ int drone_exchange_sum_local(int n_parts, drone_xplan **plans, float **d_rows, i
         DRONE_REQUIRE(plans[p] && plans[p]->nranks == n_parts && plans[p]->rank == p,
                       "drone_exchange_sum_local: plan %d is not rank %d of %d", p, p, n_parts);
         DRONE_REQUIRE(F >= 1 && F <= plans[p]->max_features && ld[p] >= F, "drone_exchange_sum_local: F=%d, ld=%d", F, ld[p]);
-        const int rc = ensure_device(plans[p]);
+        const int rc = xplan_ensure_device(plans[p]);
         if (rc) return rc;
     }
     for (int phase = 0; phase < 2; ++phase) {

@@ -212,6 +212,63 @@ int drone_exchange_sum(drone_xplan *plan, drone_comm *comm, float *d_rows, int F
 int drone_exchange_sum_local(int n_parts, drone_xplan **plans, float **d_rows, int F, const int *ld,
                              void *stream);
 
+/* ------------------------------------------------------------------------- */
+/* PageRank (the sparse aggregation at feature width 1)                        */
+/* ------------------------------------------------------------------------- */
+
+typedef struct drone_pr drone_pr;
+
+/* Same fields, order and types as struct Response, DRONE/src/cuda/algorithm/common.h:23-27;
+ * the Go worker stops when the four exchange sizes are all zero
+ * (DRONE/src/tools/cuda_convert.go:47-52). */
+typedef struct drone_pr_response {
+    int Mirror2MasterSendSize, Mirror2MasterRecvSize, Master2MirrorSendSize, Master2MirrorRecvSize;
+    int VisitedSize, LocalVertexSize;
+    float CalTime, SendTime;
+} drone_pr_response;
+
+/*
+ * PageRank state of one rank over its local graph (device CSR by source as in
+ * drone_plan_create), the GLOBAL out-degree of every local vertex
+ * (loadOutDegree / setOutDegree, DRONE/src/cuda/algorithm/pr.cu:490-515) and
+ * Graph.Mirror2Worker on the device.  The exchange plan and communicator are
+ * borrowed and must outlive the handle; comm may be NULL for a single rank.
+ * use_double = 0 computes in float like the reference, 1 in double.
+ * eps is the push threshold (1e-6 in DRONE/src/cuda/algorithm/pr.cu:11,
+ * 0.01 in the CPU job DRONE/src/algorithm/PageRank.go:10).
+ * Owns what struct PRValues holds (DRONE/src/cuda/algorithm/pr.h:7-16); all
+ * buffers are allocated here once, none per superstep.
+ */
+int drone_pr_create(drone_pr **out, int n_local, int global_v, int nnz,
+                    const int *d_index, const int *d_dst, const int *d_out_degree,
+                    const int *d_mirror2worker, drone_xplan *xplan, drone_comm *comm,
+                    int use_double, double eps);
+int drone_pr_destroy(drone_pr *pr);
+
+/* First superstep (pr = 1, push pr/outDegree, exchange).  Replaces PR_PEVal,
+ * DRONE/src/cuda/algorithm/pr.cu:375-428.  Collective; synchronous. */
+int drone_pr_peval(drone_pr *pr, drone_pr_response *res, void *stream);
+/* Later supersteps.  Replaces PR_IncEVal, DRONE/src/cuda/algorithm/pr.cu:450-488. */
+int drone_pr_inceval(drone_pr *pr, drone_pr_response *res, void *stream);
+
+/* Synchronous power iteration: pr = 1/|V|, then `iterations` times
+ * pr' = (1-d)/|V| + d * (sum over in-edges of pr[u]/outDegree[u] + dangling/|V|),
+ * with the same boundary exchange.  Collective; asynchronous on `stream`. */
+int drone_pr_power_iterate(drone_pr *pr, int iterations, double damping, void *stream);
+
+/* Number of vertex ids in 0..|V|-1 that occur in no part (no edge at all).  The power iteration counts
+ * them as dangling vertices so that the result is the PageRank of the whole id range; the delta
+ * schedule ignores them, as the reference does.  Must be the same on every rank.  Default 0. */
+int drone_pr_set_isolated_count(drone_pr *pr, long long n_isolated);
+
+/* The same procedures over n_parts handles held by one process on one device
+ * (prs[p] built with part p's exchange plan, comm NULL); res has n_parts entries. */
+int drone_pr_step_local(int n_parts, drone_pr **prs, int is_peval, drone_pr_response *res, void *stream);
+int drone_pr_power_iterate_local(int n_parts, drone_pr **prs, int iterations, double damping, void *stream);
+
+/* Current values by local id into h_out (n_local floats or doubles); synchronises. */
+int drone_pr_values(drone_pr *pr, void *h_out, void *stream);
+
 /*
  * EBV vertex-cut partitioner (host, single process).  Input: directed edge
  * list in global ids.  Output: the edges grouped by part in the order the
