@@ -64,6 +64,7 @@ def _declare(lib):
         "drone_plan_get_csr": (i, [vp, i, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "drone_spmm": (i, [vp, i, i, vp, i, vp, i, vp]),
         "drone_spmm_host": (i, [vp, i, i, vp, vp]),
+        "drone_spmm_static_scratch": (i, [vp, i, i, vp, i, vp, i, vp]),
         "drone_host_alloc": (i, [C.POINTER(vp), C.c_size_t]),
         "drone_host_free": (i, [vp]),
         "drone_comm_unique_id": (i, [vp, C.c_size_t]),

@@ -18,6 +18,8 @@
 // cache hints so that L2 capacity is left to the gathered rows of X.
 #include "plan.cuh"
 
+#include <mutex>
+
 namespace drone {
 
 // L2 cache policies.  Rows of X are gathered many times and should stay resident; the CSR
@@ -535,3 +537,94 @@ int drone_spmm_host(drone_plan *p, int orientation, int F, const float *h_X, flo
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Aggregation without any allocation.
+//
+// Some callers hand every byte of device memory to their own pool when they start, or run on a
+// thread that must never wait on the driver's allocator; for them a library call that may reach
+// cudaMalloc is unusable.  drone_spmm can reach it (the partial sums of split rows live in a buffer
+// that grows on demand).  The entry point below does the same work with the partial sums in a
+// fixed array that is part of the library image: DRONE_STATIC_SCRATCH_BYTES on every GPU that loads
+// the library, until the process exits.
+// ---------------------------------------------------------------------------
+namespace drone {
+
+constexpr size_t kStaticScratchFloats = DRONE_STATIC_SCRATCH_BYTES / sizeof(float);
+
+// Partial sums of split rows, [n_partials, F] floats.  In host code this name is only a handle for
+// cudaGetSymbolAddress; kernels receive the device address obtained from it.
+static __device__ __align__(256) float g_static_partials[kStaticScratchFloats];
+
+static const int kMaxDevices = 64;
+static float *g_static_partials_addr[kMaxDevices];   // device address of the array on each device, once known
+static std::mutex g_static_partials_mutex;
+
+// Device address of g_static_partials on the CURRENT device (looked up once per device).
+static int static_partials_address(int device, float **out) {
+    if (device < 0 || device >= kMaxDevices)
+        return set_error(DRONE_E_INVALID, "drone_spmm_static_scratch: device ordinal %d is outside 0..%d", device,
+                         kMaxDevices - 1);
+    std::lock_guard<std::mutex> lock(g_static_partials_mutex);
+    if (!g_static_partials_addr[device]) {
+        float *addr = nullptr;
+        const cudaError_t err = cudaGetSymbolAddress((void **)&addr, g_static_partials);
+        if (err != cudaSuccess || !addr)
+            return set_error(DRONE_E_CUDA, "drone_spmm_static_scratch: cudaGetSymbolAddress failed on device %d: %s", device,
+                             cudaGetErrorString(err));
+        g_static_partials_addr[device] = addr;
+    }
+    *out = g_static_partials_addr[device];
+    return DRONE_OK;
+}
+
+}  // namespace drone
+
+extern "C" int drone_spmm_static_scratch(drone_plan *p, int orientation, int F, const float *d_X, int ldx, float *d_Y,
+                                         int ldy, void *stream) {
+    DRONE_REQUIRE(p != nullptr, "drone_spmm_static_scratch: plan is NULL");
+    DRONE_REQUIRE(orientation == DRONE_OP_A || orientation == DRONE_OP_AT, "drone_spmm_static_scratch: orientation=%d",
+                  orientation);
+    const drone::Side &s = p->side[orientation];
+    DRONE_REQUIRE(s.ready, "drone_spmm_static_scratch: orientation %d was not prepared by drone_plan_create", orientation);
+    DRONE_REQUIRE(F >= 1 && F <= 1024, "drone_spmm_static_scratch: feature width F=%d outside 1..1024", F);
+    DRONE_REQUIRE(ldx >= F && ldy >= F, "drone_spmm_static_scratch: leading dimensions (ldx=%d, ldy=%d) below F=%d", ldx,
+                  ldy, F);
+    if (p->n_rows == 0) return DRONE_OK;
+    DRONE_REQUIRE(d_X && d_Y, "drone_spmm_static_scratch: NULL operand");
+    DRONE_REQUIRE(d_X != d_Y, "drone_spmm_static_scratch: X and Y must not alias");
+    const size_t need = (size_t)s.n_partials * (size_t)F;
+    if (need > drone::kStaticScratchFloats)
+        return drone::set_error(DRONE_E_TOO_LARGE,
+                                "drone_spmm_static_scratch: this plan needs %zu bytes of partial sums at F=%d, the built-in "
+                                "scratch holds %zu; use drone_spmm",
+                                need * sizeof(float), F, (size_t)DRONE_STATIC_SCRATCH_BYTES);
+    int dev = -1;
+    DRONE_CUDA(cudaGetDevice(&dev));
+    if (dev != p->device) DRONE_CUDA(cudaSetDevice(p->device));
+    float *partials = nullptr;
+    int rc = drone::static_partials_address(p->device, &partials);
+    if (rc == DRONE_OK) {
+        drone::SpmmArgs a;
+        a.side = &s;
+        a.n_rows = p->n_rows;
+        a.X = d_X;
+        a.Y = d_Y;
+        a.ldy = ldy;
+        a.partials = partials;
+        a.st = (cudaStream_t)stream;
+        const bool vec4 = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) &&
+                          ((reinterpret_cast<uintptr_t>(d_X) & 15) == 0) && ((reinterpret_cast<uintptr_t>(d_Y) & 15) == 0);
+        if (vec4) {
+            a.nvec = F / 4;
+            a.ldv = ldx / 4;
+            rc = drone::dispatch_width<4>(a);
+        } else {
+            a.nvec = F;
+            a.ldv = ldx;
+            rc = drone::dispatch_width<1>(a);
+        }
+    }
+    if (dev != p->device) cudaSetDevice(dev);
+    return rc;
+}

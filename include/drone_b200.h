@@ -130,6 +130,35 @@ int drone_spmm(drone_plan *plan, int orientation, int F,
 int drone_spmm_host(drone_plan *plan, int orientation, int F,
                     const float *h_X, float *h_Y);
 
+/*
+ * drone_spmm for callers that cannot allocate device memory: programs that give
+ * all of it to their own pool at start-up, so that an allocation made behind
+ * their back fails or fragments the pool, and threads that must never block on
+ * the driver's allocator.  drone_spmm grows a per-plan buffer for the partial
+ * sums of split rows with cudaMalloc when it needs to; this entry point keeps
+ * those partial sums in an array built into the library instead
+ * (DRONE_STATIC_SCRATCH_BYTES, resident on every GPU that loads the library
+ * until the process exits) and calls no cudaMalloc, cudaFree or any other
+ * allocating routine.  Inputs, outputs, arguments and results are those of
+ * drone_spmm: the same kernels run in the same order, so the output is
+ * bit-identical.
+ * Limits and rules:
+ *  - a call whose plan needs more than DRONE_STATIC_SCRATCH_BYTES of partial
+ *    sums (n_partials[orientation] * F * 4 bytes, see drone_plan_get_stats)
+ *    fails with DRONE_E_TOO_LARGE and launches nothing;
+ *  - the first call on a device looks up the array's device address; make that
+ *    first call before any stream capture;
+ *  - all calls on a device share the one array: two calls whose kernels may
+ *    overlap on the GPU (different streams, or different plans on different
+ *    streams) race on it; order them on one stream or with events.  Nothing
+ *    in the array has to be zero beforehand: every slot a call reads was
+ *    written earlier in the same call.
+ * It has no counterpart in the reference.
+ */
+#define DRONE_STATIC_SCRATCH_BYTES (16u << 20)
+int drone_spmm_static_scratch(drone_plan *plan, int orientation, int F,
+                              const float *d_X, int ldx, float *d_Y, int ldy, void *stream);
+
 /* Pinned host memory for drone_spmm_host operands. */
 int drone_host_alloc(void **out, size_t bytes);
 int drone_host_free(void *ptr);
