@@ -32,6 +32,11 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the kernels of ONE drone_spmm call, from an ncu capture of this
+# program on the named workload (profiles/spmm_c2_f64.md gives the command and the per-kernel split).
+NCU_DRAM_BYTES_PER_CALL = {"c2": 1.511e9}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -82,7 +87,7 @@ def algorithmic_bytes(n, nnz, f):
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
 
-    def __init__(self, index=0, period=0.05):
+    def __init__(self, index=0, period=0.004):
         super().__init__(daemon=True)
         self.period = period
         self.samples = []
@@ -248,10 +253,7 @@ def run_ours(args, cfg):
     else:
         peak, peak_src = 6650.0, "fallback"
     achieved = b_alg / (ms * 1e-3) / 1e9
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
-        traffic = json.load(open(tpath)).get(args.workload)
+    traffic = NCU_DRAM_BYTES_PER_CALL.get(args.workload) if cfg == dict(WORKLOADS.get(args.workload, {})) else None
 
     # end to end: host operands through the C ABI, copies inside the timed region
     xh = torch.empty((n, f), dtype=torch.float32).pin_memory()
@@ -275,7 +277,7 @@ def run_ours(args, cfg):
         "ms_per_step_median": float(np.median(per_step)), "ms_per_step_min": float(per_step.min()),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes": b_alg,
-                     "kernel": "one drone_spmm call = spmm_short_rows + spmm_chunks + spmm_reduce_partials"},
+                     "kernel": "one drone_spmm call = spmm_short_stream + spmm_chunks + spmm_reduce_partials"},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         "plan": {"short_row_limit": st.short_row_limit, "chunk_nnz": st.chunk_nnz,
                  "long_rows": st.n_long_rows[1], "chunks": st.n_chunks[1], "split_rows": st.n_split_rows[1],
