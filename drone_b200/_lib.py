@@ -87,6 +87,7 @@ def _declare(lib):
         "drone_pr_power_iterate_local": (i, [i, C.POINTER(vp), i, C.c_double, vp]),
         "drone_pr_values": (i, [vp, vp, vp]),
         "drone_pr_set_isolated_count": (i, [vp, ll]),
+        "drone_pr_device_arrays": (i, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "drone_ebv_partition": (i, [i, ll, vp, vp, i, i, vp, vp, vp, vp, vp]),
         "drone_graph_build_host": (i, [i, i, vp, vp, vp, vp, vp, vp, C.POINTER(i)]),
         "drone_route_tables_host": (i, [i, vp, vp, vp, vp, i, i, vp, vp, i, vp, vp, vp]),

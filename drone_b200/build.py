@@ -77,5 +77,34 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
+COMPAT = os.path.join(PKG, "compat")
+COMPAT_LIBS = {
+    "libdrone_pr_compat.so": ["pr_compat.cu"],
+    "libdrone_gcn_compat.so": ["graphsum_module.cu"],
+}
+
+
+def build_compat(force=False):
+    """The reference-shaped shims (exact symbol / class names of the reference) as separate libraries
+    linked against libdrone_b200.so."""
+    build_library(force=force)
+    nvcc = nvcc_path()
+    out = []
+    for name, srcs in COMPAT_LIBS.items():
+        target = os.path.join(LIBDIR, name)
+        deps = [os.path.join(COMPAT, s) for s in srcs] + glob.glob(os.path.join(COMPAT, "*.h")) + \
+            glob.glob(os.path.join(COMPAT, "*.cuh")) + [LIB]
+        if force or _stale(target, deps):
+            cmd = [nvcc, *NVCC_FLAGS, "-shared", "-o", target, *[os.path.join(COMPAT, s) for s in srcs],
+                   "-L" + LIBDIR, "-ldrone_b200", "-lnccl", "-Xlinker", "-rpath=$ORIGIN"]
+            r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            if r.returncode != 0:
+                sys.stderr.write(r.stdout)
+                raise RuntimeError("build of %s failed" % name)
+        out.append(target)
+    return out
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print("\n".join(build_compat(force="--force" in sys.argv)))

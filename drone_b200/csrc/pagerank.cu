@@ -807,6 +807,17 @@ int drone_pr_set_isolated_count(drone_pr *p, long long n_isolated) {
     return DRONE_OK;
 }
 
+int drone_pr_device_arrays(drone_pr *p, void **d_pr, void **d_acc, void **d_diff, int **d_active,
+                           int **d_update_by_message) {
+    DRONE_REQUIRE(p != nullptr, "drone_pr_device_arrays: handle is NULL");
+    if (d_pr) *d_pr = p->pr;
+    if (d_acc) *d_acc = p->acc;
+    if (d_diff) *d_diff = p->diff;
+    if (d_active) *d_active = p->active;
+    if (d_update_by_message) *d_update_by_message = p->ubm;
+    return DRONE_OK;
+}
+
 int drone_pr_values(drone_pr *p, void *h_out, void *stream) {
     DRONE_REQUIRE(p && (h_out || p->n_local == 0), "drone_pr_values: NULL argument");
     if (p->n_local == 0) return DRONE_OK;

@@ -295,6 +295,12 @@ int drone_pr_set_isolated_count(drone_pr *pr, long long n_isolated);
 int drone_pr_step_local(int n_parts, drone_pr **prs, int is_peval, drone_pr_response *res, void *stream);
 int drone_pr_power_iterate_local(int n_parts, drone_pr **prs, int iterations, double damping, void *stream);
 
+/* Device arrays of the state, indexed by local id (float or double as chosen at creation): what
+ * PRValues.prValue / accValue / diffValue and Graph.active / updateByMessage point to in the reference
+ * (DRONE/src/cuda/algorithm/pr.h:7-16, DRONE/src/cuda/graph.h:33-35).  Owned by the handle. */
+int drone_pr_device_arrays(drone_pr *pr, void **d_pr, void **d_acc, void **d_diff, int **d_active,
+                           int **d_update_by_message);
+
 /* Current values by local id into h_out (n_local floats or doubles); synchronises. */
 int drone_pr_values(drone_pr *pr, void *h_out, void *stream);
 

@@ -50,3 +50,20 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libdrone_b200.so")
     with pytest.raises(RuntimeError, match="no fallback"):
         _lib.lib()
+
+
+def test_reference_shaped_shims_export_the_reference_symbols():
+    import drone_b200
+    drone_b200.lib()
+    libdir = os.path.join(ROOT, "drone_b200", "lib")
+    pr = C.CDLL(os.path.join(libdir, "libdrone_pr_compat.so"))
+    header = open(os.path.join(ROOT, "drone_b200", "compat", "drone_pr_compat.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    names = re.findall(r"\b(build_graph|getLocalVertexSize|getGlobalVertexSize|addMasterRoute|addMirrorRoute|"
+                       r"loadOutDegree|PR_PEVal|PR_IncEVal)\s*\(", header)
+    assert len(set(names)) == 8
+    for n in set(names):
+        assert hasattr(pr, n), n
+    gcn = C.CDLL(os.path.join(libdir, "libdrone_gcn_compat.so"))
+    for n in ("create", "forward", "backward", "destroy"):
+        assert hasattr(gcn, "drone_compat_graphsum_" + n)
