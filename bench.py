@@ -528,14 +528,14 @@ def run_ours_multi(args, cfg):
     dist.barrier()
     torch.cuda.synchronize()
     launches = lib.drone_kernel_launch_count() - launches0
-    sampler.in_timed_region = False
-    for i in range(max(10, int(400.0 / max(e0.elapsed_time(e1) / args.steps, 0.05)))):   # same count on every rank
-        step(i)
-    torch.cuda.synchronize()
-    clocks = sampler.finish()
     t_ms = torch.tensor([e0.elapsed_time(e1)], device=device)
     dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
     ms = float(t_ms) / args.steps
+    sampler.in_timed_region = False
+    for i in range(max(10, min(2000, int(400.0 / max(ms, 0.05))))):   # from the reduced time: same count on every rank
+        step(i)
+    torch.cuda.synchronize()
+    clocks = sampler.finish()
 
     # local aggregation alone (for the roofline of the kernel) and exchange alone
     e0.record()
