@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cusparse", action="store_true")
     ap.add_argument("--no-gcn", action="store_true")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="transport of the mirror/master exchange on several GPUs")
     return ap.parse_args()
 
 
@@ -495,6 +497,8 @@ def run_ours_multi(args, cfg):
     del eu, ev, owner, reps
     graph = gs.DeviceGraph(part.local_graph(rank), in_deg.cpu().numpy(), out_deg.cpu().numpy(), device, max_features=f)
     comm = gs.Comm(rank, world)
+    if args.exchange == "p2p":
+        graph.xplan.enable_p2p(comm)
     nnz_local = graph.dst.numel()
     nnz_total = total_e
     up, down, _ = graph.xplan.counts()
@@ -591,7 +595,8 @@ def run_ours_multi(args, cfg):
                          "traffic": None, "peak_source": peak_src, "algorithmic_bytes": b_alg,
                          "kernel": "rank 0's local drone_spmm call, timed alone", "ms": spmm_ms},
             "exchange": {"ms": float(xchg), "mirror_sync_bytes_per_step_all_ranks": int(g[:, 2].sum()),
-                         "mirror_sync_bytes_per_step_rank0": sync_bytes, "collective": "grouped ncclSend/ncclRecv x2"},
+                         "mirror_sync_bytes_per_step_rank0": sync_bytes, "collective": "peer-memory stores + epoch flags (3 fused kernels)" if args.exchange == "p2p"
+                         else "grouped ncclSend/ncclRecv x2"},
             "e2e": {"value": nnz_total * f / float(e2e_t), "unit": "nnz*F/s", "h2d_bytes_per_step": int(g[:, 0].sum()) * f * 4,
                     "d2h_bytes_per_step": int(g[:, 0].sum()) * f * 4, "ms_per_step": 1e3 * float(e2e_t),
                     "steps": args.e2e_steps},

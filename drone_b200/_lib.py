@@ -74,6 +74,7 @@ def _declare(lib):
         "drone_comm_allreduce_sum": (i, [vp, vp, C.c_size_t, i, vp]),
         "drone_xplan_create": (i, [C.POINTER(vp), i, i, i, vp, vp, vp, vp, i]),
         "drone_xplan_destroy": (i, [vp]),
+        "drone_xplan_enable_p2p": (i, [vp, vp, vp]),
         "drone_xplan_counts": (i, [vp, vp, vp, C.POINTER(i)]),
         "drone_xplan_lists": (i, [vp, vp, vp]),
         "drone_exchange_sum": (i, [vp, vp, vp, i, i, vp]),

@@ -19,6 +19,9 @@
 
 namespace drone {
 
+int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t st);
+void xplan_p2p_release(drone_xplan *x);
+
 // buf[i, 0:F] = rows[list[i], 0:F]
 __global__ void gather_rows_kernel(const float *__restrict__ rows, long long ld, const int *__restrict__ list,
                                    int n_list, int F, float *__restrict__ buf) {
@@ -244,6 +247,7 @@ int drone_xplan_destroy(drone_xplan *x) {
         int prev = -1;
         cudaGetDevice(&prev);
         cudaSetDevice(x->device);
+        xplan_p2p_release(x);
         cudaFree(x->d_up_rows); cudaFree(x->d_down_rows); cudaFree(x->d_m_rows); cudaFree(x->d_m_off);
         cudaFree(x->d_m_pos); cudaFree(x->d_send); cudaFree(x->d_recv);
         if (prev >= 0) cudaSetDevice(prev);
@@ -281,6 +285,7 @@ int drone_exchange_sum(drone_xplan *x, drone_comm *c, float *d_rows, int F, int 
     int rc = xplan_ensure_device(x);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    if (x->p2p) return exchange_sum_p2p(x, d_rows, F, ld, st);
     const int n_up = (int)x->up_rows.size(), n_down = (int)x->down_rows.size(), n_m = (int)x->m_rows.size();
     // mirrors -> masters
     if (n_up) {

@@ -25,6 +25,27 @@ struct drone_xplan {
     int *d_up_rows = nullptr, *d_down_rows = nullptr, *d_m_rows = nullptr, *d_m_off = nullptr, *d_m_pos = nullptr;
     float *d_send = nullptr, *d_recv = nullptr;   // each max(up, down) * max_features floats
     size_t buf_floats = 0;
+    struct drone_p2p *p2p = nullptr;              // peer-memory transport, when enabled
+};
+
+// Peer-memory transport of one rank (one process per GPU on one NVLink domain).  Every rank owns a segment
+//   [ flags: 2 x nranks epochs | up-receive: n_down rows x max_features | down-receive: n_up rows x max_features ]
+// that its peers map through CUDA IPC.  Senders store rows straight into the receiver's segment and then publish
+// the call's epoch in the receiver's flag word; receivers poll their own flags with a bounded wait.
+struct drone_p2p {
+    unsigned epoch = 0;
+    char *segment = nullptr;            // my segment (cudaMalloc)
+    size_t segment_bytes = 0;
+    std::vector<char *> peer_segment;   // peers' segments mapped into this process (NULL for self / unused)
+    // device tables, all indexed as documented in exchange_p2p.cu
+    float **d_peer_up_recv = nullptr, **d_peer_down_recv = nullptr;   // [nranks] bases inside peers' segments
+    unsigned **d_peer_flag_up = nullptr, **d_peer_flag_down = nullptr;   // [nranks] address of "my" word in the peer's flags
+    int *d_up_peer = nullptr, *d_up_dest_row = nullptr;       // [n_up]   per mirror row: owner, row in owner's up-receive
+    int *d_down_peer = nullptr, *d_down_dest_row = nullptr;   // [n_down] per (master, mirror) pair: peer, row in its down-receive
+    int *d_need_up = nullptr, *d_need_down = nullptr;         // [nranks] 1 where a flag from that peer is expected
+    int *h_error = nullptr;             // pinned, mapped: set by a kernel whose wait ran out
+    int *d_host_error = nullptr;        // device alias of h_error (written only when a wait runs out)
+    int *d_error = nullptr;             // the same word in device memory: what the kernels poll
 };
 
 #define DRONE_NCCL(call)                                                                 \

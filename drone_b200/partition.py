@@ -194,6 +194,10 @@ class ExchangePlan:
         check(_lib.lib().drone_xplan_lists(self._h, _vp(ur), _vp(dr)))
         return ur[:int(up.sum())], dr[:int(down.sum())]
 
+    def enable_p2p(self, comm, stream_ptr=None):
+        """Switch later exchanges on this plan to the peer-memory transport (collective over `comm`)."""
+        check(_lib.lib().drone_xplan_enable_p2p(self._h, comm.handle, C.c_void_p(stream_ptr or 0)))
+
     def close(self):
         if self._h.value:
             _lib.lib().drone_xplan_destroy(self._h)

@@ -233,6 +233,20 @@ int drone_xplan_lists(const drone_xplan *plan, int *up_rows, int *down_rows);
 int drone_exchange_sum(drone_xplan *plan, drone_comm *comm, float *d_rows, int F, int ld, void *stream);
 
 /*
+ * Switch a plan to the peer-memory transport (one process per GPU, all GPUs in one NVLink domain): later
+ * drone_exchange_sum calls on this plan fuse packing, transfer and unpacking into three kernels that store rows
+ * directly into the receiving GPU's memory (CUDA IPC mappings of one buffer per rank) and order themselves with
+ * epoch flags in that memory; waits are bounded (about two seconds), after which the call sequence reports
+ * DRONE_E_STATE instead of hanging.  Results are bit-identical to the NCCL transport.  Collective over `comm`
+ * (it exchanges the IPC handles with one ncclAllGather) and synchronous.  Every rank must enable it, with plans
+ * created for the same max_features, and all ranks must then issue the same sequence of exchanges.
+ * Before destroying a plan, make sure no peer is still inside an exchange (e.g. a barrier).
+ * The reference has no counterpart (it always goes through grouped ncclSend/ncclRecv,
+ * cuda_gcn/src/cuda/cuda_communicate.cu:296-372).
+ */
+int drone_xplan_enable_p2p(drone_xplan *plan, drone_comm *comm, void *stream);
+
+/*
  * The same exchange among n_parts plans held by ONE process on ONE device
  * (plans[p] is rank p of n_parts, d_rows[p] its rows): messages become
  * device-to-device copies.  For running all parts of a partition on a single

@@ -81,11 +81,74 @@ def _nccl_rank(rank, world, port, ok):
         torch.cuda.synchronize()
         assert_close_to_oracle(b.data.cpu().numpy(), want_fwd[g.host.l2g])
         assert_close_to_oracle(a.grad.cpu().numpy(), want_bwd[g.host.l2g])
+        # the peer-memory transport gives the same bits, call after call, without host synchronisation in between
+        nccl_fwd, nccl_bwd = b.data.clone(), a.grad.clone()
+        g.xplan.enable_p2p(comm)
+        for _ in range(5):
+            layer.forward(True)
+            layer.backward()
+        torch.cuda.synchronize()
+        assert torch.equal(b.data, nccl_fwd) and torch.equal(a.grad, nccl_bwd)
+        narrow = torch.as_tensor(x[g.host.l2g][:, :5].copy(), device=dev)      # a width below max_features
+        ref = g.plan.spmm(db.OP_AT, narrow)
+        gs.exchange_sum(g.xplan, comm, ref)
+        torch.cuda.synchronize()
+        assert_close_to_oracle(ref.cpu().numpy(), want_fwd[g.host.l2g][:, :5])
+        dist.barrier()
         ok[rank] = 1
         dist.barrier()
         comm.close()
     finally:
         dist.destroy_process_group()
+
+
+def _lonely_rank(rank, world, port, ok):
+    """Rank 0 starts an exchange that rank 1 never joins: its bounded wait must run out and be reported."""
+    import time
+    import torch.distributed as dist
+    from oracle import oracle
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n, part, in_deg, out_deg, x, _, _ = setup_case(oracle, world, scale=9, seed=12, f=8, sym=True)
+        comm = gs.Comm(rank, world)
+        g = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, dev, max_features=8)
+        g.xplan.enable_p2p(comm)
+        rows = torch.ones((g.n_local, 8), device=dev)
+        gs.exchange_sum(g.xplan, comm, rows)            # both ranks: fine
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            t0 = time.time()
+            gs.exchange_sum(g.xplan, comm, rows)        # alone: the kernels give up after their wait limit
+            torch.cuda.synchronize()
+            assert time.time() - t0 < 30
+            with pytest.raises(db.DroneError, match="gave up waiting for rank 1"):
+                gs.exchange_sum(g.xplan, comm, rows)
+            assert float(torch.ones(4, device=dev).sum()) == 4.0    # the context is still usable
+        ok[rank] = 1
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_wait_runs_out_instead_of_hanging():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ok = ctx.Array("i", [0, 0])
+    port = 29900 + os.getpid() % 2000
+    procs = [ctx.Process(target=_lonely_rank, args=(r, 2, port, ok)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    assert all(p.exitcode == 0 for p in procs)
+    assert list(ok) == [1, 1]
 
 
 def test_graphsum_over_nccl_two_gpus():
