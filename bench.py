@@ -337,6 +337,11 @@ def run_ours(args, cfg):
             line["gcn_epoch"] = gcn_epoch_timing(device)
         except Exception as e:
             line["gcn_epoch"] = {"error": repr(e)}
+        torch.cuda.empty_cache()
+        try:
+            line["pagerank"] = pagerank_timing(device)
+        except Exception as e:
+            line["pagerank"] = {"error": repr(e)}
 
     if not args.no_cpu_baseline:
         from oracle import oracle
@@ -438,6 +443,75 @@ def gcn_epoch_timing(device, epochs=5):
     except Exception as e:
         out["ms_cusparse_aggregation"] = None
         out["cusparse_error"] = repr(e)
+    return out
+
+
+def pagerank_timing(device):
+    """PageRank, the path at feature width 1.
+    (a) R-MAT scale 16, edge factor 16, self-loops and duplicates removed, EBV into 2 parts (both held on this GPU):
+        20 synchronous iterations, damping 0.85, start 1/|V|, in double; checked against the double oracle, and timed
+        next to the restatement of DRONE's CPU job "pr" (float, eps 0.01, at most 200 supersteps) on one host core.
+    (b) R-MAT scale 22 directed, one part, float: time per iteration of the propagation."""
+    import types
+    import drone_b200 as db
+    from drone_b200 import graphgen as gg, graphsum as gs, pagerank as prk, partition as pt
+    from oracle import oracle
+    out = {}
+    n, u, v = gg.rmat_graph(16, 16, seed=20261125, device=device, symmetrise=False, self_loops="drop")
+    uh, vh = u.cpu().numpy(), v.cpu().numpy()
+    in_deg = np.bincount(vh, minlength=n).astype(np.int32)
+    out_deg = np.bincount(uh, minlength=n).astype(np.int32)
+    part = pt.ebv_partition(n, uh, vh, 2, keep_self_loops=False)
+    graphs = [gs.DeviceGraph(part.local_graph(p), in_deg, out_deg, device, max_features=1) for p in range(2)]
+    n_iso = int((part.replicas == 0).sum())
+    prs = [prk.PageRank(g, n, use_double=True, eps=0.0, n_isolated=n_iso) for g in graphs]
+    prk.power_iterate_local(prs, 20, 0.85)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    prk.power_iterate_local(prs, 20, 0.85)
+    e1.record()
+    torch.cuda.synchronize()
+    got = prk.gather_global(prs, graphs, n)
+    index, dst = gg.csr_by_source(u, v, n)
+    want = oracle.pagerank_power_f64(index.cpu().numpy(), dst.cpu().numpy(), 20, 0.85)
+    touched = part.replicas > 0
+    t0 = time.perf_counter()
+    _, cpu_steps, cpu_msgs = oracle.pr_drone_cpu(n, part.part_u, part.part_v, out_deg, part.owner, eps=0.01, max_steps=200)
+    cpu_s = time.perf_counter() - t0
+    out["rmat16_2parts"] = {
+        "vertices": n, "edges": int(len(uh)), "iterations": 20, "ms_total_gpu": e0.elapsed_time(e1),
+        "max_rel_err_vs_double_oracle": float(np.max(np.abs(got[touched] - want[touched]) / want[touched])),
+        "replication_factor": part.replication_factor(),
+        "cpu_pr_job_restatement": {"seconds": cpu_s, "supersteps": cpu_steps, "messages": int(cpu_msgs), "cores": 1,
+                                   "note": "C restatement of DRONE's Go job (the Go binary cannot be built here)"}}
+    for p_ in prs:
+        p_.close()
+    del graphs, prs
+
+    n, u, v = gg.rmat_graph(22, 16, seed=20261131, device=device, symmetrise=False, self_loops="drop")
+    index, dst = gg.csr_by_source(u, v, n)
+    _, outd = gg.degrees(u, v, n)
+    del u, v
+    host = types.SimpleNamespace(rank=0, n_parts=1, n_local=n, l2g=np.arange(n, dtype=np.int32),
+                                 mirror2worker=np.full(n, -1, np.int32), master_worker_index=np.zeros(n + 1, np.int32),
+                                 master2workers=np.zeros(0, np.int32))
+    g = types.SimpleNamespace(host=host, n_local=n, device=device, index=index, dst=dst, out_degree=outd,
+                              mirror2worker=torch.full((n,), -1, dtype=torch.int32, device=device),
+                              xplan=pt.ExchangePlan(host, 1))
+    pr1 = prk.PageRank(g, n, use_double=False, eps=0.0)
+    pr1.power_iterate(3, 0.85)
+    torch.cuda.synchronize()
+    e0.record()
+    pr1.power_iterate(20, 0.85)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_it = e0.elapsed_time(e1) / 20
+    nnz = int(dst.numel())
+    b_alg = 4 * nnz + 4 * (n + 1) + 8 * n + 8 * n       # columns, row pointers, published pairs, state in/out
+    out["rmat22_1part_float"] = {"vertices": n, "edges": nnz, "ms_per_iteration": ms_it,
+                                 "edges_per_s": nnz / (ms_it * 1e-3), "algorithmic_GBps": b_alg / (ms_it * 1e-3) / 1e9}
+    pr1.close()
     return out
 
 

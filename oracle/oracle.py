@@ -23,6 +23,51 @@ def build(force=False):
     return _SO
 
 
+_REF_SO = os.path.join(_HERE, "_ref", "libref_graphsum.so")
+REFERENCE_ROOT = os.environ.get("DRONE_REFERENCE_ROOT", "/root/reference")
+
+
+def build_ref(force=False):
+    """Compile the reference's own GraphSum layer from its sources where they lie (`make ref`), into oracle/_ref/.
+    Returns the library path, or None when the reference tree is not on this machine."""
+    if not os.path.isdir(os.path.join(REFERENCE_ROOT, "cuda_gcn", "src")):
+        return _REF_SO if os.path.exists(_REF_SO) else None
+    deps = [os.path.join(_HERE, f) for f in ("ref_driver.cu", "Makefile", "ref_shim/mpi.h", "ref_shim/utils_override.h")]
+    if force or not os.path.exists(_REF_SO) or any(os.path.getmtime(d) > os.path.getmtime(_REF_SO) for d in deps):
+        subprocess.run(["make", "-C", _HERE, "ref", "REFERENCE=" + REFERENCE_ROOT] + (["-B"] if force else []),
+                       check=True, stdout=subprocess.DEVNULL)
+    return _REF_SO
+
+
+def reference_available():
+    return os.path.exists(_REF_SO)
+
+
+def reference_graphsum(global_v, u, v, global_in_degree, global_out_degree, x, out_grad):
+    """Run the REFERENCE's CUDAGraphSum (cuSPARSE) forward and backward on one worker, on cuda:0.
+    x, out_grad: [global_v, dim] float32 by global id.  Returns (l2g, out_data, in_grad, values): results by the
+    reference's local id (l2g maps them to global ids), values in the reference's CSR order."""
+    ref = C.CDLL(_REF_SO)
+    u, v = _i32(u), _i32(v)
+    ind, outd = _i32(global_in_degree), _i32(global_out_degree)
+    x, out_grad = _f32(x), _f32(out_grad)
+    dim = x.shape[1]
+    cap = min(global_v, 2 * len(u)) + 1
+    out_data = np.zeros((cap, dim), np.float32)
+    in_grad = np.zeros((cap, dim), np.float32)
+    values = np.zeros(max(len(u), 1), np.float32)
+    l2g = np.zeros(cap, np.int32)
+    n = C.c_int(0)
+    rc = ref.ref_graphsum_run(int(global_v), len(u), _p(u, C.c_int), _p(v, C.c_int), _p(ind, C.c_int),
+                              _p(outd, C.c_int), dim, _p(x, C.c_float), _p(out_grad, C.c_float),
+                              _p(out_data, C.c_float), _p(in_grad, C.c_float), _p(values, C.c_float),
+                              _p(l2g, C.c_int), C.byref(n))
+    if rc != 0:
+        raise RuntimeError("reference GraphSum run failed (%d)" % rc)
+    n = n.value
+    return l2g[:n].copy(), out_data[:n].copy(), in_grad[:n].copy(), values[:len(u)].copy()
+
+
 _lib = None
 
 

@@ -1,0 +1,70 @@
+// Drives the REFERENCE's own GraphSum layer (class CUDAGraphSum over cuSPARSE, cuda_gcn/src/cuda/cuda_module.cu:149-389)
+// on one worker: builds the reference's Graph with its build_graph / addMasterRoute / addMirrorRoute, its Degree,
+// Buffer and CUDAVariable objects, runs forward() and backward(), and copies the results out.
+// Compiled together with the reference sources, where they lie, by `make ref` into oracle/_ref/ (never committed).
+// TEST INFRASTRUCTURE: validates the oracle and the CUDA library against the reference itself on a GPU box.
+#include <cstdio>
+#include <vector>
+
+#include "cuda_module.cuh"
+
+extern "C" int ref_graphsum_run(int global_v, int n_edges, int *u, int *v, const int *global_in_degree,
+                                const int *global_out_degree, int dim, const float *h_in_data,
+                                const float *h_out_grad, float *h_out_data, float *h_in_grad, float *h_values,
+                                int *h_local2global, int *n_local_out) {
+    Comm *comm = new Comm();
+    Graph *g = build_graph(global_v, n_edges, u, v, 0, 1, comm);
+    int none = 0;
+    addMasterRoute(g, &none, &none, &none, 0, 0);
+    addMirrorRoute(g, &none, &none, 0);
+    const int n = getLocalVertexSize(g);
+    *n_local_out = n;
+    std::vector<int> l2g(n), ind(n), outd(n);
+    cudaMemcpy(l2g.data(), g->Local2Global, sizeof(int) * n, cudaMemcpyDeviceToHost);
+    for (int i = 0; i < n; ++i) {
+        h_local2global[i] = l2g[i];
+        ind[i] = global_in_degree[l2g[i]];      // what loadInOutDegree / setDegree do (common/parser.cu:25-50)
+        outd[i] = global_out_degree[l2g[i]];
+    }
+    Degree *degree = new Degree();
+    cudaMalloc(&degree->inDegree, sizeof(int) * n);
+    cudaMalloc(&degree->outDegree, sizeof(int) * n);
+    cudaMemcpy(degree->inDegree, ind.data(), sizeof(int) * n, cudaMemcpyHostToDevice);
+    cudaMemcpy(degree->outDegree, outd.data(), sizeof(int) * n, cudaMemcpyHostToDevice);
+
+    CUDAVariable *in = new CUDAVariable(n * dim, true, false);
+    CUDAVariable *out = new CUDAVariable(n * dim, true, false);
+    Buffer *buffer = new Buffer();
+    buffer->maxDim = dim;
+    buffer_init(buffer, g, 0, 1);
+    // local rows are in the reference's first-seen order; the caller passes operands by GLOBAL id
+    std::vector<float> tmp((size_t)n * dim);
+    for (int i = 0; i < n; ++i)
+        for (int j = 0; j < dim; ++j) tmp[(size_t)i * dim + j] = h_in_data[(size_t)l2g[i] * dim + j];
+    cudaMemcpy(in->data, tmp.data(), sizeof(float) * tmp.size(), cudaMemcpyHostToDevice);
+    for (int i = 0; i < n; ++i)
+        for (int j = 0; j < dim; ++j) tmp[(size_t)i * dim + j] = h_out_grad[(size_t)l2g[i] * dim + j];
+    cudaMemcpy(out->grad, tmp.data(), sizeof(float) * tmp.size(), cudaMemcpyHostToDevice);
+
+    CUDAGraphSum *layer = new CUDAGraphSum(in, out, g, comm, degree, buffer, dim, 0, 1, "graphSum_ref", 0);
+    // forward and backward each end in an exchange that, with one worker, launches over zero rows; the launch errors
+    // are cleared here and the reference's exit() on them is caught (see ref_shim/utils_override.h)
+    try {
+        layer->forward(true);
+    } catch (const DroneRefExit &) {
+    }
+    cudaDeviceSynchronize();
+    cudaGetLastError();
+    try {
+        layer->backward();
+    } catch (const DroneRefExit &) {
+    }
+    cudaGetLastError();
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    cudaMemcpy(h_out_data, out->data, sizeof(float) * (size_t)n * dim, cudaMemcpyDeviceToHost);   // by LOCAL id
+    cudaMemcpy(h_in_grad, in->grad, sizeof(float) * (size_t)n * dim, cudaMemcpyDeviceToHost);
+    cudaMemcpy(h_values, g->edgeLen, sizeof(float) * n_edges, cudaMemcpyDeviceToHost);           // CSR order
+    // the reference's destructor deletes an uninitialised pointer when batch_type != SEMI_BATCH: the layer is leaked
+    cudaGetLastError();
+    return 0;
+}
