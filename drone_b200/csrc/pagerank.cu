@@ -106,11 +106,11 @@ __global__ void pr_init_kernel(R *pr, R *acc, R *diff, Pair<R> *push, int *activ
 // scalars[0] (globalDiff) += sum of block sums, in block order.
 template <typename R>
 __global__ void pr_fold_block_sums_kernel(const R *block_sums, int n_blocks, R *scalars, int slot) {
-    if (threadIdx.x == 0 && blockIdx.x == 0) {
-        R s = 0;
-        for (int i = 0; i < n_blocks; ++i) s += block_sums[i];
-        scalars[slot] += s;
-    }
+    if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+    R s = 0;                                          // lane l adds blocks l, l+32, ...; then a fixed tree
+    for (int i = threadIdx.x; i < n_blocks; i += 32) s += block_sums[i];
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+    if (threadIdx.x == 0) scalars[slot] += s;
 }
 
 // globalAcc += globalDiff; globalDiff = 0   (pr_process_messages, pr.cu:435-438)
@@ -162,32 +162,52 @@ __global__ void pr_increment_kernel(R *pr, R *acc, R *diff, Pair<R> *push, int *
 
 // ---- pull along in-edges: diff[v] = sum of published deltas, active[v] = any in-neighbour pushed ----
 
-// rows with at most short_limit in-edges: eight lanes per row
+// Short rows through the plan's short-row stream (columns with an end-of-row flag, ranges of whole rows): one warp
+// per range, one lane per entry, so the column reads are coalesced and 32 gathers are in flight per warp; the sums of
+// the rows inside a batch come from a segmented scan (fixed tree order), rows that continue into the next batch
+// carry their partial sum over.
 template <typename R>
-__global__ void pr_pull_short_kernel(const int *__restrict__ rowptr, const int *__restrict__ col,
-                                     const Pair<R> *__restrict__ push, int n, int short_limit, R *diff, int *active) {
-    const int lane = threadIdx.x & 31, gl = lane & 7;
-    const long long row = ((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 3);
-    int s = 0, e = 0;
-    if (row < n) {
-        s = rowptr[row];
-        e = rowptr[row + 1];
-        if (e - s > short_limit) e = s;
-    }
-    R sum = 0, flag = 0;
-    for (int k = s + gl; k < e; k += 8) {
-        const Pair<R> p = push[col[k]];
-        sum += p.val;
-        flag += p.flag;
-    }
+__global__ void pr_pull_stream_kernel(const int *__restrict__ s_range_row, int n_ranges, const int *__restrict__ s_rowptr,
+                                      const int *__restrict__ s_rows, const int *__restrict__ s_col,
+                                      const Pair<R> *__restrict__ push, R *diff, int *active) {
+    const int lane = threadIdx.x & 31;
+    const long long range = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    if (range >= n_ranges) return;
+    int ri = s_range_row[range];
+    const int k0 = s_rowptr[ri], k1 = s_rowptr[s_range_row[range + 1]];
+    R carry_v = 0, carry_f = 0;
+    unsigned c_next = (k0 + lane < k1) ? (unsigned)s_col[k0 + lane] : 0u;
+    for (int base = k0; base < k1; base += 32) {
+        const unsigned c = c_next;
+        const bool live = base + lane < k1;
+        c_next = (base + 32 + lane < k1) ? (unsigned)s_col[base + 32 + lane] : 0u;
+        R v = 0, f = 0;
+        if (live && !(c & kPlaceholder)) {
+            const Pair<R> p = push[c & kColMask];
+            v = p.val;
+            f = p.flag;
+        }
+        const bool end = live && (c & kLastInRow);
+        const unsigned ends = __ballot_sync(0xffffffffu, end);
+        const unsigned heads = (ends << 1) | 1u;                       // lane starts a row if the lane before ended one
+        const int start = 31 - __clz(heads & (0xffffffffu >> (31 - lane)));
 #pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
-        sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        flag += __shfl_xor_sync(0xffffffffu, flag, o);
-    }
-    if (row < n && gl == 0 && (rowptr[row + 1] - rowptr[row]) <= short_limit) {
-        diff[row] = sum;
-        active[row] = flag > 0 ? 1 : 0;
+        for (int d = 1; d < 32; d <<= 1) {
+            const R tv = __shfl_up_sync(0xffffffffu, v, d);
+            const R tf = __shfl_up_sync(0xffffffffu, f, d);
+            if (lane - d >= start) { v += tv; f += tf; }
+        }
+        if (start == 0) { v += carry_v; f += carry_f; }                // the row open at the start of this batch
+        if (end) {
+            const int row = s_rows[ri + __popc(ends & ((1u << lane) - 1u))];
+            diff[row] = v;
+            active[row] = f > 0 ? 1 : 0;
+        }
+        const R last_v = __shfl_sync(0xffffffffu, v, 31), last_f = __shfl_sync(0xffffffffu, f, 31);
+        const bool open = !(ends >> 31);
+        carry_v = open ? last_v : (R)0;
+        carry_f = open ? last_f : (R)0;
+        ri += __popc(ends);
     }
 }
 
@@ -199,7 +219,16 @@ __global__ void pr_pull_chunks_kernel(const Chunk *__restrict__ chunks, int n_ch
     if (warp >= n_chunks) return;
     const Chunk ch = chunks[warp];
     R sum = 0, flag = 0;
-    for (int k = lane; k < ch.len; k += 32) {
+    int k = lane;
+    for (; k + 96 < ch.len; k += 128) {          // four independent gathers in flight per lane
+        const int c0 = col[ch.k0 + k], c1 = col[ch.k0 + k + 32], c2 = col[ch.k0 + k + 64], c3 = col[ch.k0 + k + 96];
+        const Pair<R> p0 = push[c0], p1 = push[c1], p2 = push[c2], p3 = push[c3];
+        sum += p0.val; flag += p0.flag;
+        sum += p1.val; flag += p1.flag;
+        sum += p2.val; flag += p2.flag;
+        sum += p3.val; flag += p3.flag;
+    }
+    for (; k < ch.len; k += 32) {
         const Pair<R> p = push[col[ch.k0 + k]];
         sum += p.val;
         flag += p.flag;
@@ -362,13 +391,33 @@ __global__ void pr_power_isolated_kernel(R *scalars, long long n_isolated) {
     if (threadIdx.x == 0 && blockIdx.x == 0) scalars[2] += (R)n_isolated * scalars[3];
 }
 
-// pr' = (1-d)/V + d * (sum over in-edges + dangling/V); the isolated vertices' value follows the same rule
+// pr' = (1-d)/V + d * (sum over in-edges + dangling/V); the isolated vertices' value follows the same rule.
+// The same pass publishes pr'/outDegree and collects the dangling mass for the next iteration.
 template <typename R>
-__global__ void pr_power_apply_kernel(R *pr, const R *diff, int n, int global_v, R damping, R *scalars) {
+__global__ void pr_power_apply_kernel(R *pr, const R *diff, Pair<R> *push, const int *__restrict__ out_degree,
+                                      const int *__restrict__ mirror2worker, int n, int global_v, R damping, R *scalars,
+                                      R *block_sums) {
     const R dang = scalars[2];
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
-        pr[i] = ((R)1 - damping) / global_v + damping * (diff[i] + dang / global_v);
-    if (blockIdx.x == 0 && threadIdx.x == 0) scalars[3] = ((R)1 - damping) / global_v + damping * (dang / global_v);
+    const R base = ((R)1 - damping) / global_v;
+    R dangling = 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const R now = base + damping * (diff[i] + dang / global_v);
+        pr[i] = now;
+        Pair<R> p;
+        p.val = 0;
+        p.flag = 0;
+        const int od = out_degree[i];
+        if (od == 0) {
+            if (mirror2worker[i] == -1) dangling += now;
+        } else {
+            p.val = now / od;
+            p.flag = 1;
+        }
+        push[i] = p;
+    }
+    const R tot = block_sum<R>(dangling);
+    if (threadIdx.x == 0) block_sums[blockIdx.x] = tot;
+    if (blockIdx.x == 0 && threadIdx.x == 0) scalars[3] = base + damping * (dang / global_v);
 }
 
 template <typename R>
@@ -466,10 +515,12 @@ template <typename R>
 static int pull(drone_pr *p, cudaStream_t st) {
     const Side &s = p->plan->side[DRONE_OP_AT];
     const int n = p->n_local;
-    if (n > 0) {
-        pr_pull_short_kernel<R><<<ceil_div((long long)n * 8, 256), 256, 0, st>>>(
-            s.rowptr, s.col, (const Pair<R> *)p->push, n, p->plan->short_row_limit, (R *)p->diff, p->active);
-        DRONE_LAUNCH_CHECK("pr_pull_short_kernel");
+    (void)n;
+    if (s.n_short_ranges > 0) {
+        pr_pull_stream_kernel<R><<<ceil_div(s.n_short_ranges, 8), 256, 0, st>>>(
+            s.s_range_row, s.n_short_ranges, s.s_rowptr, s.s_rows, s.s_col, (const Pair<R> *)p->push, (R *)p->diff,
+            p->active);
+        DRONE_LAUNCH_CHECK("pr_pull_stream_kernel");
     }
     if (s.n_chunks > 0) {
         pr_pull_chunks_kernel<R><<<ceil_div(s.n_chunks, 8), 256, 0, st>>>(s.chunks, s.n_chunks, s.col,
@@ -603,13 +654,14 @@ static int power_iterations(std::vector<drone_pr *> &parts, int iterations, doub
         DRONE_LAUNCH_CHECK("pr_set_scalar_kernel");
         p->started = false;
     }
+    for (drone_pr *p : parts) {
+        pr_power_prepare_kernel<R><<<grid1d(p->n_local, kReduceBlocks), 256, 0, st>>>(
+            (const R *)p->pr, (Pair<R> *)p->push, p->out_degree, p->mirror2worker, p->n_local, (R *)p->block_sums);
+        DRONE_LAUNCH_CHECK("pr_power_prepare_kernel");
+    }
     for (int it = 0; it < iterations; ++it) {
         for (drone_pr *p : parts) {
-            const int n = p->n_local;
-            const int grid = grid1d(n, kReduceBlocks);
-            pr_power_prepare_kernel<R><<<grid, 256, 0, st>>>((const R *)p->pr, (Pair<R> *)p->push, p->out_degree,
-                                                             p->mirror2worker, n, (R *)p->block_sums);
-            DRONE_LAUNCH_CHECK("pr_power_prepare_kernel");
+            const int grid = grid1d(p->n_local, kReduceBlocks);
             DRONE_CUDA(cudaMemsetAsync((char *)p->scalars + 2 * sizeof(R), 0, sizeof(R), st));
             pr_fold_block_sums_kernel<R><<<1, 32, 0, st>>>((const R *)p->block_sums, grid, (R *)p->scalars, 2);
             DRONE_LAUNCH_CHECK("pr_fold_block_sums_kernel");
@@ -622,8 +674,10 @@ static int power_iterations(std::vector<drone_pr *> &parts, int iterations, doub
         if ((rc = exchange<R>(parts, tr, st))) return rc;
         if ((rc = tr.allreduce(parts, 2, sizeof(R) == 8, st))) return rc;
         for (drone_pr *p : parts) {
-            pr_power_apply_kernel<R><<<grid1d(p->n_local), 256, 0, st>>>((R *)p->pr, (const R *)p->diff, p->n_local,
-                                                                        p->global_v, (R)damping, (R *)p->scalars);
+            // new values, and what they publish for the next iteration, in one pass
+            pr_power_apply_kernel<R><<<grid1d(p->n_local, kReduceBlocks), 256, 0, st>>>(
+                (R *)p->pr, (const R *)p->diff, (Pair<R> *)p->push, p->out_degree, p->mirror2worker, p->n_local,
+                p->global_v, (R)damping, (R *)p->scalars, (R *)p->block_sums);
             DRONE_LAUNCH_CHECK("pr_power_apply_kernel");
         }
     }
