@@ -200,6 +200,19 @@ __global__ void max_nslots_kernel(const SplitRow *__restrict__ split, int n, int
     atomicMax(out, m);
 }
 
+// Copies the split rows with more than kWideSlots slots to `wide` (the order does not matter: every row is summed
+// on its own); counter[0] ends as their number.  With wide == NULL only counts.
+__global__ void select_wide_kernel(const SplitRow *__restrict__ split, int n, SplitRow *wide, int *counter) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        const SplitRow r = split[i];
+        if (r.nslots > kWideSlots) {
+            const int at = atomicAdd(counter, 1);
+            if (wide) wide[at] = r;
+        }
+    }
+}
+
 static inline int grid_for(long long n, int block = 256, int cap = 148 * 32) {
     long long g = (n + block - 1) / block;
     if (g < 1) g = 1;
@@ -224,6 +237,7 @@ static void free_side(Side &s) {
     cudaFree(s.val);
     cudaFree(s.chunks);
     cudaFree(s.split);
+    cudaFree(s.wide);
     cudaFree(s.s_rows);
     cudaFree(s.s_rowptr);
     cudaFree(s.s_col);
@@ -334,6 +348,18 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
             max_nslots_kernel<<<grid_for(s.n_split_rows), 256, 0, st>>>(s.split, s.n_split_rows, d_max);
             DRONE_LAUNCH_CHECK("max_nslots_kernel");
             DRONE_CUDA(cudaMemcpyAsync(&s.max_nslots, d_max, sizeof(int), cudaMemcpyDeviceToHost, st));
+            int *d_count = cnt[1];
+            DRONE_CUDA(cudaMemsetAsync(d_count, 0, sizeof(int), st));
+            select_wide_kernel<<<grid_for(s.n_split_rows), 256, 0, st>>>(s.split, s.n_split_rows, nullptr, d_count);
+            DRONE_LAUNCH_CHECK("select_wide_kernel");
+            DRONE_CUDA(cudaMemcpyAsync(&s.n_wide_rows, d_count, sizeof(int), cudaMemcpyDeviceToHost, st));
+            DRONE_CUDA(cudaStreamSynchronize(st));
+            if (s.n_wide_rows > 0) {
+                DRONE_CUDA(cudaMalloc(&s.wide, sizeof(SplitRow) * (size_t)s.n_wide_rows));
+                DRONE_CUDA(cudaMemsetAsync(d_count, 0, sizeof(int), st));
+                select_wide_kernel<<<grid_for(s.n_split_rows), 256, 0, st>>>(s.split, s.n_split_rows, s.wide, d_count);
+                DRONE_LAUNCH_CHECK("select_wide_kernel");
+            }
         }
         DRONE_CUDA(cudaStreamSynchronize(st));
     }
@@ -405,6 +431,12 @@ static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_ind
     }
     DRONE_CUDA(cudaStreamSynchronize(st));
 
+    const char *overlap = getenv("DRONE_SPMM_OVERLAP");   // "0" keeps every kernel of a call on the caller's stream
+    if (!(overlap && overlap[0] == '0')) {
+        DRONE_CUDA(cudaStreamCreateWithFlags(&p->side_stream, cudaStreamNonBlocking));
+        DRONE_CUDA(cudaEventCreateWithFlags(&p->fork_event, cudaEventDisableTiming));
+        DRONE_CUDA(cudaEventCreateWithFlags(&p->join_event, cudaEventDisableTiming));
+    }
     if (orientations & DRONE_PLAN_AT) {
         int rc = build_transpose(p, st);
         if (rc) return rc;
@@ -480,6 +512,9 @@ int drone_plan_destroy(drone_plan *p) {
     cudaFree(p->stage_x);
     cudaFree(p->stage_y);
     if (p->own_stream) cudaStreamDestroy(p->own_stream);
+    if (p->side_stream) cudaStreamDestroy(p->side_stream);
+    if (p->fork_event) cudaEventDestroy(p->fork_event);
+    if (p->join_event) cudaEventDestroy(p->join_event);
     if (prev >= 0) cudaSetDevice(prev);
     delete p;
     return DRONE_OK;

@@ -5,6 +5,7 @@
 
 namespace drone {
 
+constexpr int kWideSlots = 64;              // split rows above this many partial slots are reduced by a whole block
 constexpr int kShortRangeNnz = 64;          // stream entries per lane group (plus at most one more row)
 constexpr unsigned kLastInRow = 0x80000000u; // flag on s_col: last entry of its row
 constexpr unsigned kPlaceholder = 0x40000000u; // flag on s_col: row has no nonzeros, entry carries no data
@@ -37,6 +38,8 @@ struct Side {
     float *val = nullptr;      // [nnz]
     Chunk *chunks = nullptr;   // [n_chunks]
     SplitRow *split = nullptr; // [n_split_rows]
+    SplitRow *wide = nullptr;  // [n_wide_rows] the split rows with more than kWideSlots slots (any order)
+    int n_wide_rows = 0;
     // Short rows (at most short_row_limit nonzeros) as one contiguous stream: their nonzeros copied
     // in row order, bit 31 of the column marking the last nonzero of a row.  A row without nonzeros
     // contributes one placeholder entry (bit 30) so that it is still written.  The stream is cut into
@@ -72,4 +75,7 @@ struct drone_plan {
     float *stage_x = nullptr, *stage_y = nullptr;
     size_t stage_bytes = 0;
     cudaStream_t own_stream = nullptr;
+    // second stream and fork/join events: the short-row kernel runs beside the chunk kernels of the same call
+    cudaStream_t side_stream = nullptr;
+    cudaEvent_t fork_event = nullptr, join_event = nullptr;
 };

@@ -300,34 +300,36 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
 }
 
 // ---------------------------------------------------------------------------
-// 3. split rows: add the partial slots of a row in slot order
-//    One block per row; lane groups of all its warps take interleaved slots.
-//    Rows are filtered by slot count so that rows with few slots run with one
-//    warp per block and rows with many slots with eight.
+// 3. split rows: add the partial slots of a row in slot order.
+//    WIDE = false: one warp per split row (eight rows per block), its lane groups take interleaved slots; rows
+//    with more than max_slots slots are left to the wide launch.
+//    WIDE = true: one block per entry of the plan's list of wide rows, all eight warps share the row and their
+//    sums are added in warp order through shared memory.
 // ---------------------------------------------------------------------------
-template <int G, int VPL, int VEC>
+template <int G, int VPL, int VEC, bool WIDE>
 __global__ void __launch_bounds__(256)
 spmm_reduce_partials_kernel(const SplitRow *__restrict__ split, int n_split,
                             const float *__restrict__ partials, float *__restrict__ Y, long long ldy,
-                            int nvec, int min_slots, int max_slots) {
+                            int nvec, int max_slots) {
     using V = typename Vec<VEC>::type;
     constexpr int RPW = 32 / G;
-    extern __shared__ float smem[];  // [warps][nvec*VEC] when blockDim.x > 32
+    extern __shared__ float smem[];  // [8][nvec*VEC] for the wide launch
     const int lane = threadIdx.x & 31;
     const int w = threadIdx.x >> 5;
-    const int nw = blockDim.x >> 5;
     const int gl = lane & (G - 1);
     const int gi = lane / G;
-    if ((int)blockIdx.x >= n_split) return;
-    const int4 raw = __ldg(reinterpret_cast<const int4 *>(split) + blockIdx.x);
+    const long long entry = WIDE ? (long long)blockIdx.x : (long long)blockIdx.x * 8 + w;
+    if (entry >= n_split) return;
+    const int4 raw = __ldg(reinterpret_cast<const int4 *>(split) + entry);
     const int row = raw.x, slot0 = raw.y, nslots = raw.z;
-    if (nslots < min_slots || nslots > max_slots) return;
+    if (!WIDE && nslots > max_slots) return;
 
     V acc[VPL];
 #pragma unroll
     for (int p = 0; p < VPL; ++p) acc[p] = Vec<VEC>::zero();
-    const int stride = nw * RPW;
-    for (int sidx = w * RPW + gi; sidx < nslots; sidx += stride) {
+    const int first = WIDE ? w * RPW + gi : gi;
+    const int stride = WIDE ? 8 * RPW : RPW;
+    for (int sidx = first; sidx < nslots; sidx += stride) {
         const V *pr = reinterpret_cast<const V *>(partials + (long long)(slot0 + sidx) * nvec * VEC);
 #pragma unroll
         for (int p = 0; p < VPL; ++p) {
@@ -341,7 +343,7 @@ spmm_reduce_partials_kernel(const SplitRow *__restrict__ split, int n_split,
         for (int p = 0; p < VPL; ++p) Vec<VEC>::add(acc[p], Vec<VEC>::shfl_xor(acc[p], o));
 
     V *yr = reinterpret_cast<V *>(Y + (long long)row * ldy);
-    if (nw == 1) {
+    if (!WIDE) {
         if (gi == 0) {
 #pragma unroll
             for (int p = 0; p < VPL; ++p) {
@@ -366,7 +368,7 @@ spmm_reduce_partials_kernel(const SplitRow *__restrict__ split, int n_split,
             const int vi = gl + p * G;
             if (vi < nvec) {
                 V tot = sm[vi];
-                for (int ww = 1; ww < nw; ++ww) Vec<VEC>::add(tot, sm[ww * nvec + vi]);
+                for (int ww = 1; ww < 8; ++ww) Vec<VEC>::add(tot, sm[ww * nvec + vi]);
                 __stcs(yr + vi, tot);
             }
         }
@@ -403,19 +405,30 @@ struct SpmmArgs {
     long long ldy;   // leading dimension of Y in floats
     float *partials;
     cudaStream_t st;
+    // when set, the short-row kernel is launched on `side_stream` between the two events (fork after what precedes the
+    // call on `st`, join before what follows), so that it overlaps the chunk kernels
+    cudaStream_t side_stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
 };
 
-static const int kWideSlots = 64;  // split rows above this many slots get eight warps
 
 template <int G, int VPL, int VEC, int U, bool EXACT>
 static int launch_all(const SpmmArgs &a) {
     constexpr int RPW = 32 / G;
     const Side &s = *a.side;
+    const bool overlap = a.side_stream != nullptr && s.n_short_ranges > 0 && s.n_chunks > 0;
     if (s.n_short_ranges > 0) {
+        cudaStream_t short_stream = a.st;
+        if (overlap) {
+            DRONE_CUDA(cudaEventRecord(a.fork, a.st));
+            DRONE_CUDA(cudaStreamWaitEvent(a.side_stream, a.fork, 0));
+            short_stream = a.side_stream;
+        }
         const int grid = ceil_div(s.n_short_ranges, 8 * RPW);
-        spmm_short_stream_kernel<G, VPL, VEC, U, EXACT><<<grid, 256, 0, a.st>>>(
+        spmm_short_stream_kernel<G, VPL, VEC, U, EXACT><<<grid, 256, 0, short_stream>>>(
             s.s_range_row, s.n_short_ranges, s.s_rowptr, s.s_rows, s.s_col, s.s_val, a.X, a.ldv, a.Y, a.ldy, a.nvec);
         DRONE_LAUNCH_CHECK("spmm_short_stream_kernel");
+        if (overlap) DRONE_CUDA(cudaEventRecord(a.join, a.side_stream));
     }
     if (s.n_chunks > 0) {
         int grid = ceil_div(s.n_chunks, 8);
@@ -426,16 +439,17 @@ static int launch_all(const SpmmArgs &a) {
         DRONE_LAUNCH_CHECK("spmm_chunks_kernel");
     }
     if (s.n_split_rows > 0) {
-        spmm_reduce_partials_kernel<G, VPL, VEC><<<s.n_split_rows, 32, 0, a.st>>>(
-            s.split, s.n_split_rows, a.partials, a.Y, a.ldy, a.nvec, 0, kWideSlots);
+        spmm_reduce_partials_kernel<G, VPL, VEC, false><<<ceil_div(s.n_split_rows, 8), 256, 0, a.st>>>(
+            s.split, s.n_split_rows, a.partials, a.Y, a.ldy, a.nvec, kWideSlots);
         DRONE_LAUNCH_CHECK("spmm_reduce_partials_kernel");
-        if (s.max_nslots > kWideSlots) {
+        if (s.n_wide_rows > 0) {
             const size_t smem = sizeof(float) * 8 * (size_t)a.nvec * VEC;
-            spmm_reduce_partials_kernel<G, VPL, VEC><<<s.n_split_rows, 256, smem, a.st>>>(
-                s.split, s.n_split_rows, a.partials, a.Y, a.ldy, a.nvec, kWideSlots + 1, 0x7fffffff);
+            spmm_reduce_partials_kernel<G, VPL, VEC, true><<<s.n_wide_rows, 256, smem, a.st>>>(
+                s.wide, s.n_wide_rows, a.partials, a.Y, a.ldy, a.nvec, 0);
             DRONE_LAUNCH_CHECK("spmm_reduce_partials_kernel(wide)");
         }
     }
+    if (overlap) DRONE_CUDA(cudaStreamWaitEvent(a.st, a.join, 0));
     return DRONE_OK;
 }
 
@@ -492,6 +506,9 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
     a.ldy = ldy;
     a.partials = p->scratch;
     a.st = st;
+    a.side_stream = p->side_stream;
+    a.fork = p->fork_event;
+    a.join = p->join_event;
     const bool vec4 = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) &&
                       ((reinterpret_cast<uintptr_t>(X) & 15) == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     if (vec4) {
