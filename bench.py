@@ -52,7 +52,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cusparse", action="store_true")
     ap.add_argument("--no-gcn", action="store_true")
-    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl", "dense"],
                     help="transport of the mirror/master exchange on several GPUs")
     return ap.parse_args()
 
@@ -573,6 +573,7 @@ def run_ours_multi(args, cfg):
     comm = gs.Comm(rank, world)
     if args.exchange == "p2p":
         graph.xplan.enable_p2p(comm)
+    dense = pt.DenseExchangePlan(part, graph.host, f) if args.exchange == "dense" else None
     nnz_local = graph.dst.numel()
     nnz_total = total_e
     up, down, _ = graph.xplan.counts()
@@ -585,9 +586,15 @@ def run_ours_multi(args, cfg):
     xs = [torch.randn((graph.n_local, f), device=device, generator=gen) for _ in range(nbuf)]
     ys = [torch.empty((graph.n_local, f), device=device) for _ in range(nbuf)]
 
+    def exchange(rows):
+        if dense is not None:
+            gs.exchange_sum_dense(dense, comm, rows)
+        else:
+            gs.exchange_sum(graph.xplan, comm, rows)
+
     def step(i):
         graph.plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
-        gs.exchange_sum(graph.xplan, comm, ys[i % nbuf])
+        exchange(ys[i % nbuf])
 
     for i in range(max(args.warmup, 3)):
         step(i)
@@ -625,7 +632,7 @@ def run_ours_multi(args, cfg):
     dist.barrier()
     e0.record()
     for i in range(args.steps):
-        gs.exchange_sum(graph.xplan, comm, ys[i % nbuf])
+        exchange(ys[i % nbuf])
     e1.record()
     torch.cuda.synchronize()
     xchg = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device)
@@ -669,8 +676,10 @@ def run_ours_multi(args, cfg):
                          "traffic": None, "peak_source": peak_src, "algorithmic_bytes": b_alg,
                          "kernel": "rank 0's local drone_spmm call, timed alone", "ms": spmm_ms},
             "exchange": {"ms": float(xchg), "mirror_sync_bytes_per_step_all_ranks": int(g[:, 2].sum()),
-                         "mirror_sync_bytes_per_step_rank0": sync_bytes, "collective": "peer-memory stores + epoch flags (3 fused kernels)" if args.exchange == "p2p"
-                         else "grouped ncclSend/ncclRecv x2"},
+                         "mirror_sync_bytes_per_step_rank0": sync_bytes, "collective": {"p2p": "peer-memory stores + epoch flags (3 fused kernels)",
+                                        "nccl": "grouped ncclSend/ncclRecv x2",
+                                        "dense": "ncclReduceScatter + ncclAllGather over the boundary"}[args.exchange],
+                         "dense_boundary_rows": dense.boundary_rows() if dense is not None else None},
             "e2e": {"value": nnz_total * f / float(e2e_t), "unit": "nnz*F/s", "h2d_bytes_per_step": int(g[:, 0].sum()) * f * 4,
                     "d2h_bytes_per_step": int(g[:, 0].sum()) * f * 4, "ms_per_step": 1e3 * float(e2e_t),
                     "steps": args.e2e_steps},

@@ -78,6 +78,10 @@ def _declare(lib):
         "drone_xplan_counts": (i, [vp, vp, vp, C.POINTER(i)]),
         "drone_xplan_lists": (i, [vp, vp, vp]),
         "drone_exchange_sum": (i, [vp, vp, vp, i, i, vp]),
+        "drone_dense_xplan_create": (i, [C.POINTER(vp), i, i, i, vp, i, vp, vp, i]),
+        "drone_dense_xplan_destroy": (i, [vp]),
+        "drone_dense_xplan_boundary_rows": (ll, [vp]),
+        "drone_exchange_sum_dense": (i, [vp, vp, vp, i, i, vp]),
         "drone_exchange_sum_local": (i, [i, C.POINTER(vp), C.POINTER(vp), i, C.POINTER(i), vp]),
         "drone_pr_create": (i, [C.POINTER(vp), i, i, i, vp, vp, vp, vp, vp, vp, i, C.c_double]),
         "drone_pr_destroy": (i, [vp]),

@@ -90,6 +90,14 @@ def exchange_sum(xplan, comm, rows, stream=None):
                                         _stream_ptr(stream)))
 
 
+def exchange_sum_dense(dense_plan, comm, rows, stream=None):
+    """The exchange as ncclReduceScatter + ncclAllGather over the boundary buffer (in place)."""
+    f = rows.shape[1]
+    ld = rows.stride(0) if rows.shape[0] > 1 else max(f, rows.stride(0))
+    check(_lib.lib().drone_exchange_sum_dense(dense_plan.handle, comm.handle, C.c_void_p(rows.data_ptr()), f, int(ld),
+                                              _stream_ptr(stream)))
+
+
 def exchange_sum_local(xplans, rows_list, stream=None):
     """The same exchange among all parts held on one device."""
     n = len(xplans)

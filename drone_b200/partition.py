@@ -208,3 +208,32 @@ class ExchangePlan:
             self.close()
         except Exception:
             pass
+
+
+class DenseExchangePlan:
+    """Boundary-dense plan of one rank for the reduce-scatter / all-gather form of the exchange."""
+
+    def __init__(self, part, local_graph, max_features):
+        self._h = C.c_void_p(0)
+        owner, reps = _i32(part.owner), _i32(part.replicas)
+        check(_lib.lib().drone_dense_xplan_create(C.byref(self._h), local_graph.rank, part.n_parts, local_graph.n_local,
+                                                  _vp(local_graph.l2g), part.n_vertices, _vp(owner), _vp(reps),
+                                                  int(max_features)))
+
+    @property
+    def handle(self):
+        return self._h
+
+    def boundary_rows(self):
+        return int(_lib.lib().drone_dense_xplan_boundary_rows(self._h))
+
+    def close(self):
+        if self._h.value:
+            _lib.lib().drone_dense_xplan_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

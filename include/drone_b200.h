@@ -247,6 +247,25 @@ int drone_exchange_sum(drone_xplan *plan, drone_comm *comm, float *d_rows, int F
 int drone_xplan_enable_p2p(drone_xplan *plan, drone_comm *comm, void *stream);
 
 /*
+ * The exchange as two dense collectives, ncclReduceScatter (mirror -> master, summed) + ncclAllGather
+ * (master -> mirror), over a buffer that lists every replicated vertex once, grouped by owning rank and padded to
+ * equal groups.  Needs the partition's global tables: h_owner[v] = rank of v's master copy, h_replicas[v] = number
+ * of ranks holding v (as drone_ebv_partition returns them).  Moves rows a rank does not hold, so it pays off only
+ * when most boundary vertices are replicated on most ranks; results agree with the other transports to rounding
+ * (the order of additions inside the collective is NCCL's).  Same dataflow as GraphSum_sync_value_nccl,
+ * cuda_gcn/src/cuda/cuda_communicate.cu:374-448, expressed with collectives instead of grouped send/recv.
+ */
+typedef struct drone_dense_xplan drone_dense_xplan;
+int drone_dense_xplan_create(drone_dense_xplan **out, int rank, int nranks, int n_local,
+                             const int *h_local2global, int global_v, const int *h_owner,
+                             const int *h_replicas, int max_features);
+int drone_dense_xplan_destroy(drone_dense_xplan *plan);
+/* Rows of the boundary buffer (nranks equal groups); bytes on the wire per rank and call are about
+ * 2 * (nranks-1)/nranks * rows * F * 4. */
+long long drone_dense_xplan_boundary_rows(const drone_dense_xplan *plan);
+int drone_exchange_sum_dense(drone_dense_xplan *plan, drone_comm *comm, float *d_rows, int F, int ld, void *stream);
+
+/*
  * The same exchange among n_parts plans held by ONE process on ONE device
  * (plans[p] is rank p of n_parts, d_rows[p] its rows): messages become
  * device-to-device copies.  For running all parts of a partition on a single

@@ -81,6 +81,14 @@ def _nccl_rank(rank, world, port, ok):
         torch.cuda.synchronize()
         assert_close_to_oracle(b.data.cpu().numpy(), want_fwd[g.host.l2g])
         assert_close_to_oracle(a.grad.cpu().numpy(), want_bwd[g.host.l2g])
+        # reduce-scatter + all-gather over the dense boundary buffer: same values to rounding
+        dense = pt.DenseExchangePlan(part, g.host, f)
+        assert dense.boundary_rows() >= int((part.replicas > 1).sum())
+        rs = g.plan.spmm(db.OP_AT, a.data)
+        gs.exchange_sum_dense(dense, comm, rs)
+        torch.cuda.synchronize()
+        assert_close_to_oracle(rs.cpu().numpy(), want_fwd[g.host.l2g])
+        assert (rs - b.data).abs().max().item() <= 1e-5 * b.data.abs().max().item()
         # the peer-memory transport gives the same bits, call after call, without host synchronisation in between
         nccl_fwd, nccl_bwd = b.data.clone(), a.grad.clone()
         g.xplan.enable_p2p(comm)
