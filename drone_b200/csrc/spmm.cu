@@ -490,35 +490,58 @@ static int ensure_scratch(drone_plan *p, size_t bytes) {
     return DRONE_OK;
 }
 
+// Width of the column slices a call is cut into (0 = no slicing).  Gathering a slice of w columns touches only
+// n*w*4 bytes of X; when the whole operand does not fit in L2 but a slice does, running the slices one after the
+// other turns HBM gathers into L2 gathers at the price of re-reading the CSR stream once per slice.
+static int slice_width(const drone_plan *p, int F, bool vec4) {
+    static const int forced = tuning_int("DRONE_SLICE_WIDTH", -1);
+    if (forced == 0 || !vec4) return 0;
+    if (forced > 0) return (forced % 4 == 0 && forced < F && F % forced == 0) ? forced : 0;
+    const double l2_budget = 64e6;                      // about half of the 126 MB L2 for the gathered operand
+    if ((double)p->n_rows * F * 4 <= l2_budget) return 0;
+    for (int w : {128, 64}) {
+        if (w < F && F % w == 0 && (double)p->n_rows * w * 4 <= l2_budget) return w;
+    }
+    return 0;
+}
+
 static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long long ldx, float *Y,
                      long long ldy, cudaStream_t st) {
     const Side &s = p->side[orientation];
     if (p->n_rows == 0) return DRONE_OK;
+    const bool vec4 = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(X) & 15) == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    const int slice = slice_width(p, F, vec4);
+    const int width = slice > 0 ? slice : F;
     if (s.n_partials > 0) {
-        const int rc = ensure_scratch(p, sizeof(float) * (size_t)s.n_partials * (size_t)F);
+        const int rc = ensure_scratch(p, sizeof(float) * (size_t)s.n_partials * (size_t)width);
         if (rc) return rc;
     }
     SpmmArgs a;
     a.side = &s;
     a.n_rows = p->n_rows;
-    a.X = X;
-    a.Y = Y;
     a.ldy = ldy;
     a.partials = p->scratch;
     a.st = st;
     a.side_stream = p->side_stream;
     a.fork = p->fork_event;
     a.join = p->join_event;
-    const bool vec4 = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) &&
-                      ((reinterpret_cast<uintptr_t>(X) & 15) == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
-    if (vec4) {
-        a.nvec = F / 4;
-        a.ldv = ldx / 4;
-        return dispatch_width<4>(a);
+    for (int c0 = 0; c0 < F; c0 += width) {
+        a.X = X + c0;
+        a.Y = Y + c0;
+        int rc;
+        if (vec4) {
+            a.nvec = width / 4;
+            a.ldv = ldx / 4;
+            rc = dispatch_width<4>(a);
+        } else {
+            a.nvec = width;
+            a.ldv = ldx;
+            rc = dispatch_width<1>(a);
+        }
+        if (rc) return rc;
     }
-    a.nvec = F;
-    a.ldv = ldx;
-    return dispatch_width<1>(a);
+    return DRONE_OK;
 }
 
 }  // namespace drone
