@@ -69,15 +69,19 @@ __device__ __forceinline__ void vadd(float4 &a, const float4 &b) { a.x += b.x; a
 __device__ __forceinline__ void vadd(float &a, const float &b) { a += b; }
 
 // rows[up_rows[i], :] -> peer_up_recv[owner][dest_row[i], :]      (nvec = F / VEC vectors per row)
+// The list is walked in the order `order` gives: the mirror rows are grouped by owner, and walking them as they
+// lie would make every rank store to the same owner at the same time, whose NVLink ingress then limits all of them.
 template <int VEC>
 __global__ void p2p_push_up_kernel(const float *__restrict__ rows, long long ld, const int *__restrict__ up_rows,
-                                   const int *__restrict__ up_peer, const int *__restrict__ up_dest_row, int n_up, int nvec,
+                                   const int *__restrict__ up_peer, const int *__restrict__ up_dest_row,
+                                   const int *__restrict__ order, int n_up, int nvec,
                                    float *const *__restrict__ peer_up_recv) {
     using V = typename PVec<VEC>::type;
     const long long total = (long long)n_up * nvec;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
-        const int r = (int)(i / nvec), j = (int)(i - (long long)r * nvec);
+        const int k = (int)(i / nvec), j = (int)(i - (long long)k * nvec);
+        const int r = order[k];
         V *dst = reinterpret_cast<V *>(peer_up_recv[up_peer[r]]) + (long long)up_dest_row[r] * nvec + j;
         *dst = *(reinterpret_cast<const V *>(rows + (long long)up_rows[r] * ld) + j);
     }
@@ -164,7 +168,7 @@ void p2p_free(drone_p2p *p) {
         if (s) cudaIpcCloseMemHandle(s);
     cudaFree(p->segment);
     cudaFree(p->d_peer_up_recv); cudaFree(p->d_peer_down_recv); cudaFree(p->d_peer_flag_up); cudaFree(p->d_peer_flag_down);
-    cudaFree(p->d_up_peer); cudaFree(p->d_up_dest_row); cudaFree(p->d_down_peer); cudaFree(p->d_down_dest_row);
+    cudaFree(p->d_up_peer); cudaFree(p->d_up_dest_row); cudaFree(p->d_up_order); cudaFree(p->d_down_peer); cudaFree(p->d_down_dest_row);
     cudaFree(p->d_need_up); cudaFree(p->d_need_down);
     if (p->h_error) cudaFreeHost(p->h_error);
     cudaFree(p->d_error);
@@ -275,6 +279,23 @@ int drone_xplan_enable_p2p(drone_xplan *x, drone_comm *c, void *stream) {
             down_dest[i] = q_up_off[me] + (i - x->down_off[q]);
         }
     }
+    // Walk order of push_up: runs of kRun rows taken in turn from every owner's group, starting with the rank after
+    // this one, so that at any time a rank stores to all owners and no two ranks start on the same one.
+    std::vector<int> up_order;
+    up_order.reserve(n_up);
+    {
+        const int kRun = 16;
+        std::vector<int> next(P);
+        for (int q = 0; q < P; ++q) next[q] = x->up_off[q];
+        while (up_order.size() < n_up)
+            for (int d = 1; d <= P; ++d) {
+                const int q = (me + d) % P;
+                const int end = std::min(next[q] + kRun, x->up_off[q + 1]);
+                for (int i = next[q]; i < end; ++i) up_order.push_back(i);
+                next[q] = end;
+            }
+    }
+    if ((rc = upload_vec(&p->d_up_order, up_order))) return rc;
     if ((rc = upload_vec(&p->d_peer_up_recv, up_base))) return rc;
     if ((rc = upload_vec(&p->d_peer_down_recv, down_base))) return rc;
     if ((rc = upload_vec(&p->d_peer_flag_up, flag_up))) return rc;
@@ -317,8 +338,8 @@ int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t 
     const int nvec = vec4 ? F / 4 : F;
     if (n_up) {
         const int grid = p2p_grid((long long)n_up * nvec);
-        if (vec4) p2p_push_up_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, p->d_up_peer, p->d_up_dest_row, n_up, nvec, p->d_peer_up_recv);
-        else p2p_push_up_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, p->d_up_peer, p->d_up_dest_row, n_up, nvec, p->d_peer_up_recv);
+        if (vec4) p2p_push_up_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, p->d_up_peer, p->d_up_dest_row, p->d_up_order, n_up, nvec, p->d_peer_up_recv);
+        else p2p_push_up_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, p->d_up_peer, p->d_up_dest_row, p->d_up_order, n_up, nvec, p->d_peer_up_recv);
         DRONE_LAUNCH_CHECK("p2p_push_up_kernel");
     }
     p2p_signal_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_up, p->d_need_down, P, epoch);   // to the owners of my mirrors
