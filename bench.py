@@ -54,6 +54,10 @@ def parse_args():
     ap.add_argument("--no-gcn", action="store_true")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl", "dense"],
                     help="transport of the mirror/master exchange on several GPUs")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="several GPUs: weak = the graph grows with the GPU count (default), strong = the named graph is cut")
+    ap.add_argument("--pagerank-iters", type=int, default=0,
+                    help="several GPUs: also time this many PageRank power iterations (F=1) over the same partition")
     return ap.parse_args()
 
 
@@ -67,7 +71,8 @@ def workload_config(args):
             cfg["features"] = args.features
     # weak scaling: the graph doubles with the GPU count, so every EBV part keeps the single-GPU edge count
     n = max(args.gpus, 1)
-    cfg["scale"] += max(n.bit_length() - 1, 0)
+    if args.scaling == "weak":
+        cfg["scale"] += max(n.bit_length() - 1, 0)
     return cfg
 
 
@@ -534,15 +539,17 @@ def run_ours_multi(args, cfg):
     f = cfg["features"]
     n = 1 << cfg["scale"]
 
-    # rank 0 builds and partitions the graph; everybody receives the parts
+    # rank 0 builds and partitions the graph; every rank receives its own edges and the global tables
     t_setup = time.perf_counter()
     meta = torch.zeros(2 + world + 1, dtype=torch.int64, device=device)
     if rank == 0:
         _, u, v = gg.rmat_graph(cfg["scale"], cfg["edge_factor"], seed=cfg["seed"], device=device,
                                 symmetrise=cfg["symmetrise"], self_loops="add")
         in_deg, out_deg = gg.degrees(u, v, n)
-        part = pt.ebv_partition(n, u.cpu().numpy(), v.cpu().numpy(), world, keep_self_loops=True)
+        uh, vh = u.cpu().numpy(), v.cpu().numpy()
         del u, v
+        part = pt.ebv_partition(n, uh, vh, world, keep_self_loops=True)
+        del uh, vh
         sizes = [len(x) for x in part.part_u]
         meta[0], meta[1] = sum(sizes), n
         meta[2:2 + world + 1] = torch.tensor(np.concatenate([[0], np.cumsum(sizes)]))
@@ -550,25 +557,32 @@ def run_ours_multi(args, cfg):
     total_e = int(meta[0])
     offs = meta[2:].cpu().numpy()
     if rank == 0:
-        eu = torch.as_tensor(np.concatenate(part.part_u), device=device)
-        ev = torch.as_tensor(np.concatenate(part.part_v), device=device)
         owner = torch.as_tensor(part.owner, device=device)
         reps = torch.as_tensor(part.replicas, device=device)
+        bits = torch.as_tensor(part.presence_bits().view(np.int64), device=device)
     else:
-        eu = torch.empty(total_e, dtype=torch.int32, device=device)
-        ev = torch.empty(total_e, dtype=torch.int32, device=device)
         owner = torch.empty(n, dtype=torch.int32, device=device)
         reps = torch.empty(n, dtype=torch.int32, device=device)
+        bits = torch.empty(n, dtype=torch.int64, device=device)
         in_deg = torch.empty(n, dtype=torch.int32, device=device)
         out_deg = torch.empty(n, dtype=torch.int32, device=device)
-    for t in (eu, ev, owner, reps, in_deg, out_deg):
+    for t in (owner, reps, bits, in_deg, out_deg):
         dist.broadcast(t, 0)
-    if rank != 0:
-        eu_h, ev_h = eu.cpu().numpy(), ev.cpu().numpy()
-        part = pt.Partition(n, world, [eu_h[offs[p]:offs[p + 1]] for p in range(world)],
-                            [ev_h[offs[p]:offs[p + 1]] for p in range(world)], owner.cpu().numpy(),
-                            reps.cpu().numpy())
-    del eu, ev, owner, reps
+    if rank == 0:
+        for p in range(1, world):
+            for arr in (part.part_u[p], part.part_v[p]):
+                dist.send(torch.as_tensor(arr, device=device), dst=p)
+    else:
+        mine = []
+        for _ in range(2):
+            t = torch.empty(int(offs[rank + 1] - offs[rank]), dtype=torch.int32, device=device)
+            dist.recv(t, src=0)
+            mine.append(t.cpu().numpy())
+        pu, pv = [None] * world, [None] * world
+        pu[rank], pv[rank] = mine
+        part = pt.Partition(n, world, pu, pv, owner.cpu().numpy(), reps.cpu().numpy(),
+                            present_bits=bits.cpu().numpy().view(np.uint64))
+    del owner, reps, bits
     graph = gs.DeviceGraph(part.local_graph(rank), in_deg.cpu().numpy(), out_deg.cpu().numpy(), device, max_features=f)
     comm = gs.Comm(rank, world)
     if args.exchange == "p2p":
@@ -638,6 +652,28 @@ def run_ours_multi(args, cfg):
     xchg = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device)
     dist.all_reduce(xchg, op=dist.ReduceOp.MAX)
 
+    # PageRank power iterations (F = 1) over the same partition: pull along in-edges + the same exchange per iteration
+    pr_result = None
+    if args.pagerank_iters > 0:
+        from drone_b200 import pagerank as prm
+        pr = prm.PageRank(graph, n, comm=comm, use_double=False)
+        pr.power_iterate(3)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0.record()
+        pr.power_iterate(args.pagerank_iters)
+        e1.record()
+        torch.cuda.synchronize()
+        pr_ms = torch.tensor([e0.elapsed_time(e1) / args.pagerank_iters], device=device)
+        dist.all_reduce(pr_ms, op=dist.ReduceOp.MAX)
+        mass = torch.tensor([float(pr.values()[graph.host.mirror2worker < 0].astype(np.float64).sum())], device=device,
+                            dtype=torch.float64)
+        dist.all_reduce(mass)
+        pr_result = {"iterations": args.pagerank_iters, "ms_per_iteration": float(pr_ms),
+                     "nnz_per_s": nnz_total / (float(pr_ms) * 1e-3), "sum_over_masters": float(mass),
+                     "dtype": "f32", "exchange": "grouped ncclSend/ncclRecv of all boundary vertices + scalar all-reduce"}
+        pr.close()
+
     # end to end: host operands in, host result out, every step
     xh = torch.empty((graph.n_local, f), dtype=torch.float32).pin_memory()
     yh = torch.empty((graph.n_local, f), dtype=torch.float32).pin_memory()
@@ -668,7 +704,7 @@ def run_ours_multi(args, cfg):
         line = {
             "metric": "spmm_nnzF_per_s", "value": nnz_total * f / (ms * 1e-3), "unit": "nnz*F/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": dict(workload_descr(args, cfg, n, nnz_total), parts=world, partitioner="EBV",
                            replication_factor=float(g[:, 0].sum()) / n,
                            edge_imbalance=float(g[:, 1].max() * world / g[:, 1].sum())),
@@ -685,6 +721,8 @@ def run_ours_multi(args, cfg):
                     "steps": args.e2e_steps},
             "gpu_launches": int(g[:, 3].sum()), "clocks": clocks, "setup_s": setup_s,
         }
+        if pr_result is not None:
+            line["pagerank"] = pr_result
         print(json.dumps(line), flush=True)
     comm.close()
     dist.destroy_process_group()

@@ -79,35 +79,39 @@ private:
     std::atomic<bool> stop_{false};
 };
 
-static inline bool bit_get(const std::vector<uint64_t> &b, int i) { return (b[(size_t)i >> 6] >> (i & 63)) & 1ULL; }
-static inline void bit_set(std::vector<uint64_t> &b, int i) { b[(size_t)i >> 6] |= 1ULL << (i & 63); }
+static inline int pool_slices(int n) { return n >= (1 << 16) ? 64 : 1; }
 
-}  // namespace drone
-
-using namespace drone;
-
-extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int *h_u, const int *h_v, int n_parts,
-                                   int keep_self_loops, int *h_out_u, int *h_out_v, long long *h_part_offset,
-                                   int *h_owner, int *h_replicas) {
-    DRONE_REQUIRE(n_vertices > 0 && n_edges >= 0, "drone_ebv_partition: bad sizes (V=%d, E=%lld)", n_vertices, n_edges);
-    DRONE_REQUIRE(n_parts >= 1 && n_parts <= 64, "drone_ebv_partition: n_parts=%d outside 1..64", n_parts);
-    DRONE_REQUIRE(n_edges == 0 || (h_u && h_v), "drone_ebv_partition: NULL edge list");
-    DRONE_REQUIRE(h_out_u && h_out_v && h_part_offset && h_owner && h_replicas, "drone_ebv_partition: NULL output");
-    const int P = n_parts;
+// The partitioner proper.  Mask is an unsigned type of at least n_parts bits: held[v] has bit p set when part p holds
+// vertex v, so that scoring an edge costs two random reads whatever the number of parts.
+template <typename Mask>
+static int ebv_run(int n_vertices, long long n_edges, const int *h_u, const int *h_v, int P, int keep_self_loops,
+                   int *h_out_u, int *h_out_v, long long *h_part_offset, int *h_owner, int *h_replicas) {
     const int max_batch = 1000;
-
-    // deal + per-rank degree + per-rank stable sort by degree sum
-    std::vector<std::vector<EbvEdge>> share(P);
-    for (int r = 0; r < P; ++r) share[r].reserve((size_t)(n_edges / P + 1));
-    for (long long i = 0; i < n_edges; ++i) {
-        DRONE_REQUIRE(h_u[i] >= 0 && h_u[i] < n_vertices && h_v[i] >= 0 && h_v[i] < n_vertices,
-                      "drone_ebv_partition: edge %lld (%d,%d) outside 0..%d", i, h_u[i], h_v[i], n_vertices - 1);
-        if (!keep_self_loops && h_u[i] == h_v[i]) continue;
-        share[(size_t)(i % P)].push_back({h_u[i], h_v[i], 0});
-    }
     int hw = (int)std::thread::hardware_concurrency();
     if (hw < 1) hw = 1;
     PhasePool pool(std::min(P, hw));
+
+    // deal + per-rank degree + per-rank stable sort by degree sum
+    std::vector<std::vector<EbvEdge>> share(P);
+    std::vector<long long> bad_edge(P, -1);
+    pool.run(P, [&](int r) {
+        share[r].reserve((size_t)(n_edges / P + 1));
+        for (long long i = r; i < n_edges; i += P) {
+            const int u = h_u[i], v = h_v[i];
+            if (u < 0 || u >= n_vertices || v < 0 || v >= n_vertices) {
+                if (bad_edge[r] < 0) bad_edge[r] = i;
+                continue;
+            }
+            if (!keep_self_loops && u == v) continue;
+            share[r].push_back({u, v, 0});
+        }
+    });
+    for (int r = 0; r < P; ++r)
+        if (bad_edge[r] >= 0) {
+            const long long i = bad_edge[r];
+            return set_error(DRONE_E_INVALID, "drone_ebv_partition: edge %lld (%d,%d) outside 0..%d", i, h_u[i], h_v[i],
+                             n_vertices - 1);
+        }
     long long kept = 0;
     pool.run(P, [&](int r) {
         std::vector<int> deg((size_t)n_vertices, 0);
@@ -118,9 +122,13 @@ extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int 
     });
     for (int r = 0; r < P; ++r) kept += (long long)share[r].size();
 
-    std::vector<std::vector<uint64_t>> has(P, std::vector<uint64_t>(((size_t)n_vertices + 63) / 64, 0));
+    std::vector<Mask> held((size_t)n_vertices, 0);
     std::vector<long long> edge_count(P, 0), vertex_count(P, 0);
     std::vector<std::vector<int>> part_u(P), part_v(P);
+    for (int p = 0; p < P; ++p) {
+        part_u[p].reserve((size_t)(kept / P + kept / (16 * P) + 1024));
+        part_v[p].reserve((size_t)(kept / P + kept / (16 * P) + 1024));
+    }
     // assignment of this round: for each (sender, part) the edges in sender order
     std::vector<std::vector<int>> sent((size_t)P * P);
 
@@ -134,15 +142,21 @@ extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int 
         pool.run(P, [&](int r) {
             const long long edges_r = (long long)share[r].size();
             const long long end = std::min<long long>(start + batch, edges_r);
+            double load[64], spread[64];   // the terms of the score that do not depend on the edge
+            for (int p = 0; p < P; ++p) {
+                load[p] = 1.0 * edge_count[p] / (double)edges_r;
+                spread[p] = 1.0 * vertex_count[p] / n_vertices * P;
+            }
             for (long long i = start; i < end; ++i) {
                 const EbvEdge &e = share[r][(size_t)i];
+                const Mask hu = held[e.u], hv = held[e.v];
                 int best = -1;
                 double best_w = -100;
                 for (int p = 0; p < P; ++p) {
                     double w = 0;
-                    if (!bit_get(has[p], e.u)) w -= 1;
-                    if (!bit_get(has[p], e.v)) w -= 1;
-                    w = w - 1.0 * edge_count[p] / (double)edges_r - 1.0 * vertex_count[p] / n_vertices * P;
+                    if (!((hu >> p) & 1)) w -= 1;
+                    if (!((hv >> p) & 1)) w -= 1;
+                    w = w - load[p] - spread[p];
                     if (p == r) w += 0.1;
                     if (best_w < w) { best_w = w; best = p; }
                 }
@@ -150,16 +164,24 @@ extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int 
                 sent[(size_t)r * P + best].push_back(e.v);
             }
         });
-        // hand-over: every part appends what it was sent, in sender order, and updates its own state
+        // hand-over: every part appends what it was sent, in sender order, and updates its own state.  Parts run
+        // side by side and may meet on one vertex's mask word, hence the atomic OR; bit p is only ever set by part p.
         pool.run(P, [&](int p) {
+            const Mask bit = (Mask)((Mask)1 << p);
             for (int r = 0; r < P; ++r) {
                 const std::vector<int> &s = sent[(size_t)r * P + p];
                 for (size_t k = 0; k < s.size(); k += 2) {
                     const int u = s[k], v = s[k + 1];
                     part_u[p].push_back(u);
                     part_v[p].push_back(v);
-                    if (!bit_get(has[p], u)) { bit_set(has[p], u); vertex_count[p]++; }
-                    if (!bit_get(has[p], v)) { bit_set(has[p], v); vertex_count[p]++; }
+                    if (!(__atomic_load_n(&held[u], __ATOMIC_RELAXED) & bit)) {
+                        __atomic_fetch_or(&held[u], bit, __ATOMIC_RELAXED);
+                        vertex_count[p]++;
+                    }
+                    if (!(__atomic_load_n(&held[v], __ATOMIC_RELAXED) & bit)) {
+                        __atomic_fetch_or(&held[v], bit, __ATOMIC_RELAXED);
+                        vertex_count[p]++;
+                    }
                 }
                 edge_count[p] += (long long)(s.size() / 2);
             }
@@ -169,26 +191,57 @@ extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int 
     long long off = 0;
     for (int p = 0; p < P; ++p) {
         h_part_offset[p] = off;
-        std::copy(part_u[p].begin(), part_u[p].end(), h_out_u + off);
-        std::copy(part_v[p].begin(), part_v[p].end(), h_out_v + off);
         off += (long long)part_u[p].size();
     }
     h_part_offset[P] = off;
     if (off != kept) return set_error(DRONE_E_STATE, "drone_ebv_partition: %lld edges in, %lld out", kept, off);
+    pool.run(P, [&](int p) {
+        std::copy(part_u[p].begin(), part_u[p].end(), h_out_u + h_part_offset[p]);
+        std::copy(part_v[p].begin(), part_v[p].end(), h_out_v + h_part_offset[p]);
+    });
 
-    for (int v = 0; v < n_vertices; ++v) {
-        int reps = 0;
-        for (int p = 0; p < P; ++p) reps += bit_get(has[p], v) ? 1 : 0;
-        h_replicas[v] = reps;
-        h_owner[v] = -1;
-        if (reps == 0) continue;
-        const int want = reps > 1 ? v % reps : 0;
-        int seen = 0;
-        for (int p = 0; p < P; ++p)
-            if (bit_get(has[p], v)) {
-                if (seen == want) { h_owner[v] = p; break; }
-                ++seen;
-            }
-    }
+    const int slices = pool_slices(n_vertices);
+    pool.run(slices, [&](int s) {
+        const int v0 = (int)((long long)n_vertices * s / slices), v1 = (int)((long long)n_vertices * (s + 1) / slices);
+        for (int v = v0; v < v1; ++v) {
+            const Mask m = held[v];
+            int reps = 0;
+            for (int p = 0; p < P; ++p) reps += (int)((m >> p) & 1);
+            h_replicas[v] = reps;
+            h_owner[v] = -1;
+            if (reps == 0) continue;
+            const int want = reps > 1 ? v % reps : 0;
+            int seen = 0;
+            for (int p = 0; p < P; ++p)
+                if ((m >> p) & 1) {
+                    if (seen == want) { h_owner[v] = p; break; }
+                    ++seen;
+                }
+        }
+    });
     return DRONE_OK;
+}
+
+}  // namespace drone
+
+using namespace drone;
+
+extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int *h_u, const int *h_v, int n_parts,
+                                   int keep_self_loops, int *h_out_u, int *h_out_v, long long *h_part_offset,
+                                   int *h_owner, int *h_replicas) {
+    DRONE_REQUIRE(n_vertices > 0 && n_edges >= 0, "drone_ebv_partition: bad sizes (V=%d, E=%lld)", n_vertices, n_edges);
+    DRONE_REQUIRE(n_parts >= 1 && n_parts <= 64, "drone_ebv_partition: n_parts=%d outside 1..64", n_parts);
+    DRONE_REQUIRE(n_edges == 0 || (h_u && h_v), "drone_ebv_partition: NULL edge list");
+    DRONE_REQUIRE(h_out_u && h_out_v && h_part_offset && h_owner && h_replicas, "drone_ebv_partition: NULL output");
+    if (n_parts <= 8)
+        return ebv_run<uint8_t>(n_vertices, n_edges, h_u, h_v, n_parts, keep_self_loops, h_out_u, h_out_v, h_part_offset,
+                                h_owner, h_replicas);
+    if (n_parts <= 16)
+        return ebv_run<uint16_t>(n_vertices, n_edges, h_u, h_v, n_parts, keep_self_loops, h_out_u, h_out_v, h_part_offset,
+                                 h_owner, h_replicas);
+    if (n_parts <= 32)
+        return ebv_run<uint32_t>(n_vertices, n_edges, h_u, h_v, n_parts, keep_self_loops, h_out_u, h_out_v, h_part_offset,
+                                 h_owner, h_replicas);
+    return ebv_run<uint64_t>(n_vertices, n_edges, h_u, h_v, n_parts, keep_self_loops, h_out_u, h_out_v, h_part_offset,
+                             h_owner, h_replicas);
 }

@@ -24,7 +24,7 @@ def _vp(a):
 class Partition:
     """Result of the EBV vertex cut of a directed edge list over n_parts parts."""
 
-    def __init__(self, n_vertices, n_parts, part_u, part_v, owner, replicas):
+    def __init__(self, n_vertices, n_parts, part_u, part_v, owner, replicas, present_bits=None):
         self.n_vertices = n_vertices
         self.n_parts = n_parts
         self.part_u = part_u            # list of int32 arrays (global ids), G.<p> order
@@ -32,6 +32,9 @@ class Partition:
         self.owner = owner              # [V] part holding the master copy (-1: vertex has no edge)
         self.replicas = replicas        # [V] number of parts holding the vertex
         self._present = None
+        # [V] uint64, bit p set when part p holds the vertex.  A rank that was sent only its own edges (part_u / part_v
+        # of the other parts are None) is given this table instead, which is all the routing tables need of them.
+        self.present_bits = present_bits
 
     # ----- statistics the reference prints (EBV_mpi.cpp:379-401) -----
     def replication_factor(self):
@@ -41,7 +44,18 @@ class Partition:
         sizes = np.array([len(u) for u in self.part_u], dtype=np.float64)
         return float(sizes.max() * self.n_parts / max(sizes.sum(), 1))
 
+    def presence_bits(self):
+        """[V] uint64 with bit p set when part p holds the vertex."""
+        if self.present_bits is None:
+            bits = np.zeros(self.n_vertices, np.uint64)
+            for q in range(self.n_parts):
+                bits[self.present(q)] |= np.uint64(1 << q)
+            self.present_bits = bits
+        return self.present_bits
+
     def present(self, p):
+        if self.present_bits is not None:
+            return (self.present_bits >> np.uint64(p)) & np.uint64(1) != 0
         if self._present is None:
             self._present = []
             for q in range(self.n_parts):
@@ -120,8 +134,8 @@ def ebv_partition(n_vertices, u, v, n_parts, keep_self_loops=True):
     replicas = np.empty(n_vertices, np.int32)
     check(_lib.lib().drone_ebv_partition(n_vertices, e, _vp(u), _vp(v), n_parts, int(bool(keep_self_loops)),
                                          _vp(out_u), _vp(out_v), _vp(off), _vp(owner), _vp(replicas)))
-    part_u = [out_u[off[p]:off[p + 1]].copy() for p in range(n_parts)]
-    part_v = [out_v[off[p]:off[p + 1]].copy() for p in range(n_parts)]
+    part_u = [out_u[off[p]:off[p + 1]] for p in range(n_parts)]     # views: no second copy of the edge list
+    part_v = [out_v[off[p]:off[p + 1]] for p in range(n_parts)]
     return Partition(n_vertices, n_parts, part_u, part_v, owner, replicas)
 
 
