@@ -56,6 +56,9 @@ def parse_args():
                     help="transport of the mirror/master exchange on several GPUs")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="several GPUs: weak = the graph grows with the GPU count (default), strong = the named graph is cut")
+    ap.add_argument("--pipeline-groups", type=int, default=1,
+                    help="several GPUs: aggregate and exchange the rows in this many groups, group g's exchange "
+                         "overlapping group g+1's aggregation (1 = aggregation, then exchange)")
     ap.add_argument("--pagerank-iters", type=int, default=0,
                     help="several GPUs: also time this many PageRank power iterations (F=1) over the same partition")
     return ap.parse_args()
@@ -335,6 +338,12 @@ def run_ours(args, cfg):
         except Exception as e:  # the head-to-head is informative, never fatal
             line["cusparse"] = {"error": repr(e)}
 
+    if args.pagerank_iters > 0:      # the path at F = 1 on the workload's own graph, for comparison with several GPUs
+        try:
+            line["pagerank_workload_graph"] = one_part_pagerank(device, n, index, dst, out_deg, args.pagerank_iters)
+        except Exception as e:
+            line["pagerank_workload_graph"] = {"error": repr(e)}
+
     if not args.no_gcn:
         del xs, ys, xh, yh
         torch.cuda.empty_cache()
@@ -451,6 +460,33 @@ def gcn_epoch_timing(device, epochs=5):
     return out
 
 
+def one_part_pagerank(device, n, index, dst, out_degree, iterations):
+    """Time per power iteration (float) of PageRank over a whole graph held as one part on `device`."""
+    import types
+    from drone_b200 import pagerank as prk, partition as pt
+    host = types.SimpleNamespace(rank=0, n_parts=1, n_local=n, l2g=np.arange(n, dtype=np.int32),
+                                 mirror2worker=np.full(n, -1, np.int32), master_worker_index=np.zeros(n + 1, np.int32),
+                                 master2workers=np.zeros(0, np.int32))
+    g = types.SimpleNamespace(host=host, n_local=n, device=device, index=index, dst=dst, out_degree=out_degree,
+                              mirror2worker=torch.full((n,), -1, dtype=torch.int32, device=device),
+                              xplan=pt.ExchangePlan(host, 1))
+    pr1 = prk.PageRank(g, n, use_double=False, eps=0.0)
+    pr1.power_iterate(3, 0.85)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    pr1.power_iterate(iterations, 0.85)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_it = e0.elapsed_time(e1) / iterations
+    nnz = int(dst.numel())
+    b_alg = 4 * nnz + 4 * (n + 1) + 8 * n + 8 * n       # columns, row pointers, published pairs, state in/out
+    res = {"vertices": n, "edges": nnz, "iterations": iterations, "ms_per_iteration": ms_it,
+           "edges_per_s": nnz / (ms_it * 1e-3), "algorithmic_GBps": b_alg / (ms_it * 1e-3) / 1e9}
+    pr1.close()
+    return res
+
+
 def pagerank_timing(device):
     """PageRank, the path at feature width 1.
     (a) R-MAT scale 16, edge factor 16, self-loops and duplicates removed, EBV into 2 parts (both held on this GPU):
@@ -498,25 +534,7 @@ def pagerank_timing(device):
     index, dst = gg.csr_by_source(u, v, n)
     _, outd = gg.degrees(u, v, n)
     del u, v
-    host = types.SimpleNamespace(rank=0, n_parts=1, n_local=n, l2g=np.arange(n, dtype=np.int32),
-                                 mirror2worker=np.full(n, -1, np.int32), master_worker_index=np.zeros(n + 1, np.int32),
-                                 master2workers=np.zeros(0, np.int32))
-    g = types.SimpleNamespace(host=host, n_local=n, device=device, index=index, dst=dst, out_degree=outd,
-                              mirror2worker=torch.full((n,), -1, dtype=torch.int32, device=device),
-                              xplan=pt.ExchangePlan(host, 1))
-    pr1 = prk.PageRank(g, n, use_double=False, eps=0.0)
-    pr1.power_iterate(3, 0.85)
-    torch.cuda.synchronize()
-    e0.record()
-    pr1.power_iterate(20, 0.85)
-    e1.record()
-    torch.cuda.synchronize()
-    ms_it = e0.elapsed_time(e1) / 20
-    nnz = int(dst.numel())
-    b_alg = 4 * nnz + 4 * (n + 1) + 8 * n + 8 * n       # columns, row pointers, published pairs, state in/out
-    out["rmat22_1part_float"] = {"vertices": n, "edges": nnz, "ms_per_iteration": ms_it,
-                                 "edges_per_s": nnz / (ms_it * 1e-3), "algorithmic_GBps": b_alg / (ms_it * 1e-3) / 1e9}
-    pr1.close()
+    out["rmat22_1part_float"] = one_part_pagerank(device, n, index, dst, outd, 20)
     return out
 
 
@@ -606,7 +624,14 @@ def run_ours_multi(args, cfg):
         else:
             gs.exchange_sum(graph.xplan, comm, rows)
 
+    piped = None
+    if args.pipeline_groups > 1 and dense is None:
+        piped = gs.PipelinedAggregation(graph, comm, f, n_groups=args.pipeline_groups, p2p=args.exchange == "p2p")
+
     def step(i):
+        if piped is not None:
+            piped(db.OP_AT, xs[i % nbuf], ys[i % nbuf])
+            return
         graph.plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
         exchange(ys[i % nbuf])
 
@@ -706,6 +731,7 @@ def run_ours_multi(args, cfg):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": dict(workload_descr(args, cfg, n, nnz_total), parts=world, partitioner="EBV",
+                           pipeline_groups=args.pipeline_groups if piped is not None else 1,
                            replication_factor=float(g[:, 0].sum()) / n,
                            edge_imbalance=float(g[:, 1].max() * world / g[:, 1].sum())),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

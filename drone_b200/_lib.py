@@ -63,6 +63,8 @@ def _declare(lib):
         "drone_plan_get_stats": (i, [vp, C.POINTER(PlanStats)]),
         "drone_plan_get_csr": (i, [vp, i, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "drone_spmm": (i, [vp, i, i, vp, i, vp, i, vp]),
+        "drone_plan_set_row_classes": (i, [vp, vp, i, vp]),
+        "drone_spmm_rows": (i, [vp, i, i, i, vp, i, vp, i, vp]),
         "drone_spmm_host": (i, [vp, i, i, vp, vp]),
         "drone_spmm_static_scratch": (i, [vp, i, i, vp, i, vp, i, vp]),
         "drone_host_alloc": (i, [C.POINTER(vp), C.c_size_t]),
@@ -94,6 +96,7 @@ def _declare(lib):
         "drone_pr_set_isolated_count": (i, [vp, ll]),
         "drone_pr_device_arrays": (i, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "drone_ebv_partition": (i, [i, ll, vp, vp, i, i, vp, vp, vp, vp, vp]),
+        "drone_presence_bits_host": (i, [i, i, vp, vp, vp, vp]),
         "drone_graph_build_host": (i, [i, i, vp, vp, vp, vp, vp, vp, C.POINTER(i)]),
         "drone_route_tables_host": (i, [i, vp, vp, vp, vp, i, i, vp, vp, i, vp, vp, vp]),
         "drone_rmat_edges": (i, [i, ll, C.c_ulonglong, C.c_double, C.c_double, C.c_double, ll, vp, vp, vp]),

@@ -245,3 +245,31 @@ extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int 
     return ebv_run<uint64_t>(n_vertices, n_edges, h_u, h_v, n_parts, keep_self_loops, h_out_u, h_out_v, h_part_offset,
                              h_owner, h_replicas);
 }
+
+// bits[v] gets bit p set when vertex v is an endpoint of an edge of part p (the parts lie one after the other in
+// h_u / h_v, part p at [h_part_offset[p], h_part_offset[p+1])).
+extern "C" int drone_presence_bits_host(int n_vertices, int n_parts, const int *h_u, const int *h_v,
+                                        const long long *h_part_offset, unsigned long long *h_bits) {
+    DRONE_REQUIRE(n_vertices > 0 && n_parts >= 1 && n_parts <= 64, "drone_presence_bits_host: bad sizes");
+    DRONE_REQUIRE(h_u && h_v && h_part_offset && h_bits, "drone_presence_bits_host: NULL argument");
+    int hw = (int)std::thread::hardware_concurrency();
+    if (hw < 1) hw = 1;
+    PhasePool pool(std::min(std::max(n_parts, 8), hw));
+    const int slices = pool_slices(n_vertices);
+    pool.run(slices, [&](int s) {
+        const long long v0 = (long long)n_vertices * s / slices, v1 = (long long)n_vertices * (s + 1) / slices;
+        std::fill(h_bits + v0, h_bits + v1, 0ULL);
+    });
+    std::atomic<int> bad{0};
+    pool.run(n_parts, [&](int p) {
+        const unsigned long long bit = 1ULL << p;
+        for (long long i = h_part_offset[p]; i < h_part_offset[p + 1]; ++i) {
+            const int u = h_u[i], v = h_v[i];
+            if (u < 0 || u >= n_vertices || v < 0 || v >= n_vertices) { bad.store(1); continue; }
+            if (!(__atomic_load_n(&h_bits[u], __ATOMIC_RELAXED) & bit)) __atomic_fetch_or(&h_bits[u], bit, __ATOMIC_RELAXED);
+            if (!(__atomic_load_n(&h_bits[v], __ATOMIC_RELAXED) & bit)) __atomic_fetch_or(&h_bits[v], bit, __ATOMIC_RELAXED);
+        }
+    });
+    if (bad.load()) return set_error(DRONE_E_INVALID, "drone_presence_bits_host: an edge names a vertex outside 0..%d", n_vertices - 1);
+    return DRONE_OK;
+}

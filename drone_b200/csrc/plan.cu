@@ -105,12 +105,12 @@ __global__ void count_chunks_kernel(const int *__restrict__ rowptr, int n_rows, 
 }
 
 __global__ void fill_chunks_kernel(const int *__restrict__ rowptr, int n_rows, int chunk_nnz,
-                                   const int *__restrict__ chunk_off, const int *__restrict__ slot_off,
-                                   const int *__restrict__ split_off, Chunk *__restrict__ chunks,
-                                   SplitRow *__restrict__ split) {
+                                   const int *__restrict__ chunk_cnt, const int *__restrict__ chunk_off,
+                                   const int *__restrict__ slot_off, const int *__restrict__ split_off,
+                                   Chunk *__restrict__ chunks, SplitRow *__restrict__ split) {
     for (long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x; r < n_rows;
          r += (long long)gridDim.x * blockDim.x) {
-        const int nc = chunk_off[r + 1] - chunk_off[r];
+        const int nc = chunk_cnt[r];
         if (nc == 0) continue;
         const int s = rowptr[r], e = rowptr[r + 1];
         const int c0 = chunk_off[r];
@@ -176,20 +176,41 @@ __global__ void fill_short_kernel(const int *__restrict__ rowptr, const int *__r
     }
 }
 
-// s_range_row[i] = first short row whose stream offset is >= i * range_nnz
-__global__ void short_ranges_kernel(const int *__restrict__ s_rowptr, int n_short, int n_ranges, int range_nnz,
-                                    int *__restrict__ s_range_row) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i <= n_ranges;
+// out[i] = first short row in [row_lo, row_hi) whose stream offset is >= first_entry + i * range_nnz, for i < n_ranges
+__global__ void short_ranges_kernel(const int *__restrict__ s_rowptr, int row_lo, int row_hi, long long first_entry,
+                                    int n_ranges, int range_nnz, int *__restrict__ out) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_ranges;
          i += (long long)gridDim.x * blockDim.x) {
-        if (i == n_ranges) { s_range_row[i] = n_short; continue; }
-        const long long target = i * (long long)range_nnz;
-        int lo = 0, hi = n_short;  // first index with s_rowptr[idx] >= target
+        const long long target = first_entry + i * (long long)range_nnz;
+        int lo = row_lo, hi = row_hi;  // first index with s_rowptr[idx] >= target
         while (lo < hi) {
             const int mid = lo + ((hi - lo) >> 1);
             if (s_rowptr[mid] < target) lo = mid + 1; else hi = mid;
         }
-        s_range_row[i] = lo;
+        out[i] = lo;
     }
+}
+
+// permuted[i] = cnt[order[i]] for i < n, permuted[n] = 0
+__global__ void gather_counts_kernel(const int *__restrict__ cnt, const int *__restrict__ order, int n,
+                                     int *__restrict__ permuted) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i <= n;
+         i += (long long)gridDim.x * blockDim.x)
+        permuted[i] = i < n ? cnt[order[i]] : 0;
+}
+
+// off[order[i]] = permuted_off[i] for i < n, off[n] = permuted_off[n]
+__global__ void scatter_offsets_kernel(const int *__restrict__ permuted_off, const int *__restrict__ order, int n,
+                                       int *__restrict__ off) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i <= n;
+         i += (long long)gridDim.x * blockDim.x)
+        off[i < n ? order[i] : n] = permuted_off[i];
+}
+
+__global__ void check_classes_kernel(const int *__restrict__ cls, int n, int n_classes, int *bad) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        if (cls[i] < 0 || cls[i] >= n_classes) *bad = 1;
 }
 
 __global__ void max_nslots_kernel(const SplitRow *__restrict__ split, int n, int *out) {
@@ -308,14 +329,59 @@ static int build_transpose(drone_plan *p, cudaStream_t st) {
     return DRONE_OK;
 }
 
-// Work lists of the long rows of one orientation.
+static void free_lists(Side &s) {
+    cudaFree(s.chunks);
+    cudaFree(s.split);
+    cudaFree(s.wide);
+    cudaFree(s.s_rows);
+    cudaFree(s.s_rowptr);
+    cudaFree(s.s_col);
+    cudaFree(s.s_val);
+    cudaFree(s.s_range_row);
+    s.chunks = nullptr;
+    s.split = s.wide = nullptr;
+    s.s_rows = s.s_rowptr = s.s_col = s.s_range_row = nullptr;
+    s.s_val = nullptr;
+    s.ready = false;
+}
+
+// Exclusive scan of n+1 per-row counts into per-row offsets.  With row classes the offsets are class-major: rows are
+// numbered in the order `p->row_order` lists them.  starts[c] = offset at which class c begins (starts[n_classes] =
+// total).  scratch: 2 arrays of n+1 ints.
+static int class_major_scan(const drone_plan *p, const int *cnt, int *off, int *scratch, void *tmp, size_t tmp_bytes,
+                            int *starts, cudaStream_t st) {
+    const int n = p->n_rows;
+    if (!p->row_order) {
+        DRONE_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, cnt, off, n + 1, st));
+        count_launch();
+        starts[0] = 0;
+        DRONE_CUDA(cudaMemcpyAsync(&starts[1], off + n, sizeof(int), cudaMemcpyDeviceToHost, st));
+        DRONE_CUDA(cudaStreamSynchronize(st));
+        return DRONE_OK;
+    }
+    int *permuted = scratch, *permuted_off = scratch + (size_t)(n + 1);
+    gather_counts_kernel<<<grid_for(n + 1), 256, 0, st>>>(cnt, p->row_order, n, permuted);
+    DRONE_LAUNCH_CHECK("gather_counts_kernel");
+    DRONE_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, permuted, permuted_off, n + 1, st));
+    count_launch();
+    scatter_offsets_kernel<<<grid_for(n + 1), 256, 0, st>>>(permuted_off, p->row_order, n, off);
+    DRONE_LAUNCH_CHECK("scatter_offsets_kernel");
+    for (int c = 0; c <= p->n_classes; ++c)
+        DRONE_CUDA(cudaMemcpyAsync(&starts[c], permuted_off + p->class_start[c], sizeof(int), cudaMemcpyDeviceToHost, st));
+    DRONE_CUDA(cudaStreamSynchronize(st));
+    return DRONE_OK;
+}
+
+// Work lists of one orientation: chunks and split rows of the long rows, the flagged stream of the short rows.
 static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
     const int n = p->n_rows;
-    int *buf = nullptr;  // 8 arrays of n+1 ints: counts x4, offsets x4
+    const int K = p->n_classes;
+    int *buf = nullptr;  // 10 arrays of n+1 ints: counts x4, offsets x4, scratch x2
     const size_t stride = (size_t)(n + 1);
-    DRONE_CUDA(cudaMalloc(&buf, sizeof(int) * stride * 8));
+    DRONE_CUDA(cudaMalloc(&buf, sizeof(int) * stride * 10));
     int *cnt[4] = {buf, buf + stride, buf + 2 * stride, buf + 3 * stride};
     int *off[4] = {buf + 4 * stride, buf + 5 * stride, buf + 6 * stride, buf + 7 * stride};
+    int *scratch = buf + 8 * stride;
     count_chunks_kernel<<<grid_for(n + 1), 256, 0, st>>>(s.rowptr, n, p->short_row_limit, p->chunk_nnz,
                                                         cnt[0], cnt[1], cnt[2], cnt[3]);
     DRONE_LAUNCH_CHECK("count_chunks_kernel");
@@ -323,42 +389,50 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
     void *tmp = nullptr;
     DRONE_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, cnt[0], off[0], n + 1, st));
     DRONE_CUDA(cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1));
-    for (int i = 0; i < 4; ++i) {
-        DRONE_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, cnt[i], off[i], n + 1, st));
-        count_launch();
-    }
-    int totals[4];
-    for (int i = 0; i < 4; ++i)
-        DRONE_CUDA(cudaMemcpyAsync(&totals[i], off[i] + n, sizeof(int), cudaMemcpyDeviceToHost, st));
-    DRONE_CUDA(cudaStreamSynchronize(st));
-    s.n_chunks = totals[0];
-    s.n_partials = totals[1];
-    s.n_split_rows = totals[2];
-    s.n_long_rows = totals[3];
+    int rc;
+    int slot_start[kMaxRowClasses + 1], long_start[kMaxRowClasses + 1];
+    if ((rc = class_major_scan(p, cnt[0], off[0], scratch, tmp, tmp_bytes, s.chunk_start, st))) return rc;
+    if ((rc = class_major_scan(p, cnt[1], off[1], scratch, tmp, tmp_bytes, slot_start, st))) return rc;
+    if ((rc = class_major_scan(p, cnt[2], off[2], scratch, tmp, tmp_bytes, s.split_start, st))) return rc;
+    if ((rc = class_major_scan(p, cnt[3], off[3], scratch, tmp, tmp_bytes, long_start, st))) return rc;
+    s.n_classes = K;
+    s.n_chunks = s.chunk_start[K];
+    s.n_partials = slot_start[K];
+    s.n_split_rows = s.split_start[K];
+    s.n_long_rows = long_start[K];
     s.max_nslots = 0;
+    s.n_wide_rows = 0;
+    for (int c = 0; c <= K; ++c) s.wide_start[c] = 0;
     if (s.n_chunks > 0) {
         DRONE_CUDA(cudaMalloc(&s.chunks, sizeof(Chunk) * (size_t)s.n_chunks));
         DRONE_CUDA(cudaMalloc(&s.split, sizeof(SplitRow) * (size_t)(s.n_split_rows > 0 ? s.n_split_rows : 1)));
-        fill_chunks_kernel<<<grid_for(n), 256, 0, st>>>(s.rowptr, n, p->chunk_nnz, off[0], off[1], off[2],
+        fill_chunks_kernel<<<grid_for(n), 256, 0, st>>>(s.rowptr, n, p->chunk_nnz, cnt[0], off[0], off[1], off[2],
                                                        s.chunks, s.split);
         DRONE_LAUNCH_CHECK("fill_chunks_kernel");
         if (s.n_split_rows > 0) {
-            int *d_max = cnt[0];  // reuse
-            DRONE_CUDA(cudaMemsetAsync(d_max, 0, sizeof(int), st));
+            int *d_max = scratch, *d_count = scratch + 1;
+            DRONE_CUDA(cudaMemsetAsync(d_max, 0, 2 * sizeof(int), st));
             max_nslots_kernel<<<grid_for(s.n_split_rows), 256, 0, st>>>(s.split, s.n_split_rows, d_max);
             DRONE_LAUNCH_CHECK("max_nslots_kernel");
             DRONE_CUDA(cudaMemcpyAsync(&s.max_nslots, d_max, sizeof(int), cudaMemcpyDeviceToHost, st));
-            int *d_count = cnt[1];
-            DRONE_CUDA(cudaMemsetAsync(d_count, 0, sizeof(int), st));
-            select_wide_kernel<<<grid_for(s.n_split_rows), 256, 0, st>>>(s.split, s.n_split_rows, nullptr, d_count);
-            DRONE_LAUNCH_CHECK("select_wide_kernel");
-            DRONE_CUDA(cudaMemcpyAsync(&s.n_wide_rows, d_count, sizeof(int), cudaMemcpyDeviceToHost, st));
-            DRONE_CUDA(cudaStreamSynchronize(st));
-            if (s.n_wide_rows > 0) {
-                DRONE_CUDA(cudaMalloc(&s.wide, sizeof(SplitRow) * (size_t)s.n_wide_rows));
-                DRONE_CUDA(cudaMemsetAsync(d_count, 0, sizeof(int), st));
-                select_wide_kernel<<<grid_for(s.n_split_rows), 256, 0, st>>>(s.split, s.n_split_rows, s.wide, d_count);
-                DRONE_LAUNCH_CHECK("select_wide_kernel");
+            // two passes over the classes in turn: count the wide rows, then copy them (class-major as well)
+            for (int pass = 0; pass < 2; ++pass) {
+                if (pass == 1) {
+                    DRONE_CUDA(cudaStreamSynchronize(st));
+                    s.n_wide_rows = s.wide_start[K];
+                    if (s.n_wide_rows == 0) break;
+                    DRONE_CUDA(cudaMalloc(&s.wide, sizeof(SplitRow) * (size_t)s.n_wide_rows));
+                    DRONE_CUDA(cudaMemsetAsync(d_count, 0, sizeof(int), st));
+                }
+                for (int c = 0; c < K; ++c) {
+                    const int lo = s.split_start[c], cn = s.split_start[c + 1] - lo;
+                    if (cn > 0) {
+                        select_wide_kernel<<<grid_for(cn), 256, 0, st>>>(s.split + lo, cn, pass ? s.wide : nullptr, d_count);
+                        DRONE_LAUNCH_CHECK("select_wide_kernel");
+                    }
+                    if (pass == 0)
+                        DRONE_CUDA(cudaMemcpyAsync(&s.wide_start[c + 1], d_count, sizeof(int), cudaMemcpyDeviceToHost, st));
+                }
             }
         }
         DRONE_CUDA(cudaStreamSynchronize(st));
@@ -366,17 +440,15 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
     // stream of the short rows
     count_short_kernel<<<grid_for(n + 1), 256, 0, st>>>(s.rowptr, n, p->short_row_limit, cnt[0], cnt[1]);
     DRONE_LAUNCH_CHECK("count_short_kernel");
-    for (int i = 0; i < 2; ++i) {
-        DRONE_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, cnt[i], off[i], n + 1, st));
-        count_launch();
-    }
-    int short_totals[2];
-    for (int i = 0; i < 2; ++i)
-        DRONE_CUDA(cudaMemcpyAsync(&short_totals[i], off[i] + n, sizeof(int), cudaMemcpyDeviceToHost, st));
-    DRONE_CUDA(cudaStreamSynchronize(st));
-    s.n_short_rows = short_totals[0];
-    s.n_short_entries = short_totals[1];
-    s.n_short_ranges = s.n_short_entries > 0 ? ceil_div(s.n_short_entries, kShortRangeNnz) : 0;
+    int srow_start[kMaxRowClasses + 1], sent_start[kMaxRowClasses + 1];
+    if ((rc = class_major_scan(p, cnt[0], off[0], scratch, tmp, tmp_bytes, srow_start, st))) return rc;
+    if ((rc = class_major_scan(p, cnt[1], off[1], scratch, tmp, tmp_bytes, sent_start, st))) return rc;
+    s.n_short_rows = srow_start[K];
+    s.n_short_entries = sent_start[K];
+    s.range_start[0] = 0;
+    for (int c = 0; c < K; ++c)
+        s.range_start[c + 1] = s.range_start[c] + ceil_div(sent_start[c + 1] - sent_start[c], kShortRangeNnz);
+    s.n_short_ranges = s.range_start[K];
     if (s.n_short_rows > 0) {
         DRONE_CUDA(cudaMalloc(&s.s_rows, sizeof(int) * (size_t)s.n_short_rows));
         DRONE_CUDA(cudaMalloc(&s.s_rowptr, sizeof(int) * (size_t)(s.n_short_rows + 1)));
@@ -388,10 +460,19 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
         DRONE_LAUNCH_CHECK("fill_short_kernel");
         DRONE_CUDA(cudaMemcpyAsync(s.s_rowptr + s.n_short_rows, &s.n_short_entries, sizeof(int),
                                    cudaMemcpyHostToDevice, st));
-        short_ranges_kernel<<<grid_for(s.n_short_ranges + 1), 256, 0, st>>>(s.s_rowptr, s.n_short_rows,
-                                                                           s.n_short_ranges, kShortRangeNnz,
-                                                                           s.s_range_row);
-        DRONE_LAUNCH_CHECK("short_ranges_kernel");
+        // ranges never straddle two classes; entry range_start[c] is also the end of class c-1's last range
+        for (int c = 0; c < K; ++c) {
+            const int nr = s.range_start[c + 1] - s.range_start[c];
+            if (nr > 0) {
+                short_ranges_kernel<<<grid_for(nr), 256, 0, st>>>(s.s_rowptr, srow_start[c], srow_start[c + 1],
+                                                                 sent_start[c], nr, kShortRangeNnz,
+                                                                 s.s_range_row + s.range_start[c]);
+                DRONE_LAUNCH_CHECK("short_ranges_kernel");
+            }
+        }
+        for (int c = 1; c <= K; ++c)   // after the kernels in stream order: the closing entry of every class
+            DRONE_CUDA(cudaMemcpyAsync(s.s_range_row + s.range_start[c], &srow_start[c], sizeof(int),
+                                       cudaMemcpyHostToDevice, st));
         DRONE_CUDA(cudaStreamSynchronize(st));
     }
     cudaFree(tmp);
@@ -508,6 +589,7 @@ int drone_plan_destroy(drone_plan *p) {
     cudaSetDevice(p->device);
     free_side(p->side[0]);
     free_side(p->side[1]);
+    cudaFree(p->row_order);
     cudaFree(p->scratch);
     cudaFree(p->stage_x);
     cudaFree(p->stage_y);
@@ -518,6 +600,72 @@ int drone_plan_destroy(drone_plan *p) {
     if (prev >= 0) cudaSetDevice(prev);
     delete p;
     return DRONE_OK;
+}
+
+int drone_plan_set_row_classes(drone_plan *p, const int *d_row_class, int n_classes, void *stream) {
+    DRONE_REQUIRE(p != nullptr, "drone_plan_set_row_classes: plan is NULL");
+    DRONE_REQUIRE(n_classes >= 1 && n_classes <= kMaxRowClasses, "drone_plan_set_row_classes: n_classes=%d outside 1..%d",
+                  n_classes, kMaxRowClasses);
+    DRONE_REQUIRE(n_classes == 1 || d_row_class != nullptr, "drone_plan_set_row_classes: d_row_class is NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    int prev = -1;
+    DRONE_CUDA(cudaGetDevice(&prev));
+    if (prev != p->device) DRONE_CUDA(cudaSetDevice(p->device));
+    const int n = p->n_rows;
+    DRONE_CUDA(cudaDeviceSynchronize());   // calls that still read the lists must have finished
+    cudaFree(p->row_order);
+    p->row_order = nullptr;
+    p->n_classes = 1;
+    p->class_start[0] = 0;
+    p->class_start[1] = n;
+    if (n_classes > 1 && n > 0) {
+        int *keys_out = nullptr, *rows = nullptr, *counts = nullptr;
+        DRONE_CUDA(cudaMalloc(&keys_out, sizeof(int) * (size_t)n));
+        DRONE_CUDA(cudaMalloc(&rows, sizeof(int) * (size_t)n));
+        DRONE_CUDA(cudaMalloc(&p->row_order, sizeof(int) * (size_t)n));
+        DRONE_CUDA(cudaMalloc(&counts, sizeof(int) * (kMaxRowClasses + 1)));
+        DRONE_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * (kMaxRowClasses + 1), st));
+        check_classes_kernel<<<grid_for(n), 256, 0, st>>>(d_row_class, n, n_classes, counts + kMaxRowClasses);
+        DRONE_LAUNCH_CHECK("check_classes_kernel");
+        int bad = 0;
+        DRONE_CUDA(cudaMemcpyAsync(&bad, counts + kMaxRowClasses, sizeof(int), cudaMemcpyDeviceToHost, st));
+        DRONE_CUDA(cudaStreamSynchronize(st));
+        if (bad) {
+            cudaFree(keys_out); cudaFree(rows); cudaFree(counts);
+            cudaFree(p->row_order);
+            p->row_order = nullptr;
+            if (prev != p->device) cudaSetDevice(prev);
+            return set_error(DRONE_E_INVALID, "drone_plan_set_row_classes: a row has a class outside 0..%d", n_classes - 1);
+        }
+        histogram_kernel<<<grid_for(n), 256, 0, st>>>(d_row_class, n, counts);
+        DRONE_LAUNCH_CHECK("histogram_kernel");
+        iota_kernel<<<grid_for(n), 256, 0, st>>>(rows, n);
+        DRONE_LAUNCH_CHECK("iota_kernel");
+        int end_bit = 1;
+        while ((1 << end_bit) < n_classes) ++end_bit;
+        size_t tmp_bytes = 0;
+        void *tmp = nullptr;
+        // stable: rows stay ascending inside a class
+        DRONE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, d_row_class, keys_out, rows, p->row_order, n, 0, end_bit, st));
+        DRONE_CUDA(cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1));
+        DRONE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tmp_bytes, d_row_class, keys_out, rows, p->row_order, n, 0, end_bit, st));
+        count_launch();
+        int h_counts[kMaxRowClasses];
+        DRONE_CUDA(cudaMemcpyAsync(h_counts, counts, sizeof(int) * kMaxRowClasses, cudaMemcpyDeviceToHost, st));
+        DRONE_CUDA(cudaStreamSynchronize(st));
+        cudaFree(tmp); cudaFree(keys_out); cudaFree(rows); cudaFree(counts);
+        p->n_classes = n_classes;
+        for (int c = 0; c < n_classes; ++c) p->class_start[c + 1] = p->class_start[c] + h_counts[c];
+    }
+    int rc = DRONE_OK;
+    for (int o = 0; o < 2 && rc == DRONE_OK; ++o) {
+        Side &s = p->side[o];
+        if (!s.rowptr) continue;
+        free_lists(s);
+        rc = build_work_lists(p, s, st);
+    }
+    if (prev != p->device) cudaSetDevice(prev);
+    return rc;
 }
 
 int drone_plan_get_stats(const drone_plan *p, drone_plan_stats *out) {

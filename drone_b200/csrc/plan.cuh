@@ -10,6 +10,7 @@ constexpr int kShortRangeNnz = 64;          // stream entries per lane group (pl
 constexpr unsigned kLastInRow = 0x80000000u; // flag on s_col: last entry of its row
 constexpr unsigned kPlaceholder = 0x40000000u; // flag on s_col: row has no nonzeros, entry carries no data
 constexpr unsigned kColMask = 0x3fffffffu;
+constexpr int kMaxRowClasses = 16;         // row classes a plan can be given (drone_plan_set_row_classes)
 
 // One chunk of a long row: nonzeros [k0, k0+len) of `row`.  slot >= 0 means the
 // chunk's sum goes to partial-sum slot `slot` (the row has several chunks);
@@ -57,6 +58,11 @@ struct Side {
     int n_split_rows = 0;
     int n_partials = 0;
     int max_nslots = 0;        // largest nslots over split rows
+    // With row classes the four lists are class-major (all work of class 0 first, then class 1, ...; rows ascending
+    // inside a class) and list x of class c is [x_start[c], x_start[c+1]).  Without classes everything is class 0.
+    int n_classes = 1;
+    int range_start[kMaxRowClasses + 1] = {0}, chunk_start[kMaxRowClasses + 1] = {0};
+    int split_start[kMaxRowClasses + 1] = {0}, wide_start[kMaxRowClasses + 1] = {0};
 };
 
 }  // namespace drone
@@ -74,6 +80,10 @@ struct drone_plan {
     // device staging for drone_spmm_host
     float *stage_x = nullptr, *stage_y = nullptr;
     size_t stage_bytes = 0;
+    // row classes: rows in class-major order and where each class starts in that order (NULL / 1 class: none set)
+    int *row_order = nullptr;  // [n_rows]
+    int n_classes = 1;
+    int class_start[drone::kMaxRowClasses + 1] = {0};
     cudaStream_t own_stream = nullptr;
     // second stream and fork/join events: the short-row kernel runs beside the chunk kernels of the same call
     cudaStream_t side_stream = nullptr;

@@ -409,43 +409,55 @@ struct SpmmArgs {
     // call on `st`, join before what follows), so that it overlaps the chunk kernels
     cudaStream_t side_stream = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr;
+    int row_class = -1;   // >= 0: only the rows of that class of a plan with row classes
 };
 
+
+// The part of a class-major list with class starts `start` that the call computes.
+static inline void class_range(int row_class, int n_classes, const int *start, int *lo, int *count) {
+    *lo = row_class < 0 ? 0 : start[row_class];
+    *count = (row_class < 0 ? start[n_classes] : start[row_class + 1]) - *lo;
+}
 
 template <int G, int VPL, int VEC, int U, bool EXACT>
 static int launch_all(const SpmmArgs &a) {
     constexpr int RPW = 32 / G;
     const Side &s = *a.side;
-    const bool overlap = a.side_stream != nullptr && s.n_short_ranges > 0 && s.n_chunks > 0;
-    if (s.n_short_ranges > 0) {
+    int range_lo, n_ranges, chunk_lo, n_chunks, split_lo, n_split, wide_lo, n_wide;
+    class_range(a.row_class, s.n_classes, s.range_start, &range_lo, &n_ranges);
+    class_range(a.row_class, s.n_classes, s.chunk_start, &chunk_lo, &n_chunks);
+    class_range(a.row_class, s.n_classes, s.split_start, &split_lo, &n_split);
+    class_range(a.row_class, s.n_classes, s.wide_start, &wide_lo, &n_wide);
+    const bool overlap = a.side_stream != nullptr && n_ranges > 0 && n_chunks > 0;
+    if (n_ranges > 0) {
         cudaStream_t short_stream = a.st;
         if (overlap) {
             DRONE_CUDA(cudaEventRecord(a.fork, a.st));
             DRONE_CUDA(cudaStreamWaitEvent(a.side_stream, a.fork, 0));
             short_stream = a.side_stream;
         }
-        const int grid = ceil_div(s.n_short_ranges, 8 * RPW);
+        const int grid = ceil_div(n_ranges, 8 * RPW);
         spmm_short_stream_kernel<G, VPL, VEC, U, EXACT><<<grid, 256, 0, short_stream>>>(
-            s.s_range_row, s.n_short_ranges, s.s_rowptr, s.s_rows, s.s_col, s.s_val, a.X, a.ldv, a.Y, a.ldy, a.nvec);
+            s.s_range_row + range_lo, n_ranges, s.s_rowptr, s.s_rows, s.s_col, s.s_val, a.X, a.ldv, a.Y, a.ldy, a.nvec);
         DRONE_LAUNCH_CHECK("spmm_short_stream_kernel");
         if (overlap) DRONE_CUDA(cudaEventRecord(a.join, a.side_stream));
     }
-    if (s.n_chunks > 0) {
-        int grid = ceil_div(s.n_chunks, 8);
+    if (n_chunks > 0) {
+        int grid = ceil_div(n_chunks, 8);
         static const int resident = resident_blocks();
         if (resident > 0 && grid > resident) grid = resident;
         spmm_chunks_kernel<G, VPL, VEC, 2 * U, EXACT><<<grid, 256, 0, a.st>>>(
-            s.chunks, s.n_chunks, s.col, s.val, a.X, a.ldv, a.Y, a.ldy, a.partials, a.nvec);
+            s.chunks + chunk_lo, n_chunks, s.col, s.val, a.X, a.ldv, a.Y, a.ldy, a.partials, a.nvec);
         DRONE_LAUNCH_CHECK("spmm_chunks_kernel");
     }
-    if (s.n_split_rows > 0) {
-        spmm_reduce_partials_kernel<G, VPL, VEC, false><<<ceil_div(s.n_split_rows, 8), 256, 0, a.st>>>(
-            s.split, s.n_split_rows, a.partials, a.Y, a.ldy, a.nvec, kWideSlots);
+    if (n_split > 0) {
+        spmm_reduce_partials_kernel<G, VPL, VEC, false><<<ceil_div(n_split, 8), 256, 0, a.st>>>(
+            s.split + split_lo, n_split, a.partials, a.Y, a.ldy, a.nvec, kWideSlots);
         DRONE_LAUNCH_CHECK("spmm_reduce_partials_kernel");
-        if (s.n_wide_rows > 0) {
+        if (n_wide > 0) {
             const size_t smem = sizeof(float) * 8 * (size_t)a.nvec * VEC;
-            spmm_reduce_partials_kernel<G, VPL, VEC, true><<<s.n_wide_rows, 256, smem, a.st>>>(
-                s.wide, s.n_wide_rows, a.partials, a.Y, a.ldy, a.nvec, 0);
+            spmm_reduce_partials_kernel<G, VPL, VEC, true><<<n_wide, 256, smem, a.st>>>(
+                s.wide + wide_lo, n_wide, a.partials, a.Y, a.ldy, a.nvec, 0);
             DRONE_LAUNCH_CHECK("spmm_reduce_partials_kernel(wide)");
         }
     }
@@ -506,7 +518,7 @@ static int slice_width(const drone_plan *p, int F, bool vec4) {
 }
 
 static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long long ldx, float *Y,
-                     long long ldy, cudaStream_t st) {
+                     long long ldy, cudaStream_t st, int row_class = -1) {
     const Side &s = p->side[orientation];
     if (p->n_rows == 0) return DRONE_OK;
     const bool vec4 = (F % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) &&
@@ -526,6 +538,7 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
     a.side_stream = p->side_stream;
     a.fork = p->fork_event;
     a.join = p->join_event;
+    a.row_class = row_class;
     for (int c0 = 0; c0 < F; c0 += width) {
         a.X = X + c0;
         a.Y = Y + c0;
@@ -565,6 +578,27 @@ int drone_spmm(drone_plan *p, int orientation, int F, const float *d_X, int ldx,
     DRONE_CUDA(cudaGetDevice(&dev));
     if (dev != p->device) DRONE_CUDA(cudaSetDevice(p->device));
     const int rc = spmm_impl(p, orientation, F, d_X, ldx, d_Y, ldy, (cudaStream_t)stream);
+    if (dev != p->device) cudaSetDevice(dev);
+    return rc;
+}
+
+int drone_spmm_rows(drone_plan *p, int orientation, int row_class, int F, const float *d_X, int ldx, float *d_Y, int ldy,
+                    void *stream) {
+    DRONE_REQUIRE(p != nullptr, "drone_spmm_rows: plan is NULL");
+    DRONE_REQUIRE(orientation == DRONE_OP_A || orientation == DRONE_OP_AT, "drone_spmm_rows: orientation=%d", orientation);
+    DRONE_REQUIRE(p->side[orientation].ready, "drone_spmm_rows: orientation %d was not prepared by drone_plan_create",
+                  orientation);
+    DRONE_REQUIRE(row_class >= 0 && row_class < p->n_classes, "drone_spmm_rows: row_class=%d, the plan has %d classes",
+                  row_class, p->n_classes);
+    DRONE_REQUIRE(F >= 1 && F <= 1024, "drone_spmm_rows: feature width F=%d outside 1..1024", F);
+    DRONE_REQUIRE(ldx >= F && ldy >= F, "drone_spmm_rows: leading dimensions (ldx=%d, ldy=%d) below F=%d", ldx, ldy, F);
+    if (p->n_rows == 0) return DRONE_OK;
+    DRONE_REQUIRE(d_X && d_Y, "drone_spmm_rows: NULL operand");
+    DRONE_REQUIRE(d_X != d_Y, "drone_spmm_rows: X and Y must not alias");
+    int dev = -1;
+    DRONE_CUDA(cudaGetDevice(&dev));
+    if (dev != p->device) DRONE_CUDA(cudaSetDevice(p->device));
+    const int rc = spmm_impl(p, orientation, F, d_X, ldx, d_Y, ldy, (cudaStream_t)stream, row_class);
     if (dev != p->device) cudaSetDevice(dev);
     return rc;
 }

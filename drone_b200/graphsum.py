@@ -108,6 +108,52 @@ def exchange_sum_local(xplans, rows_list, stream=None):
     check(_lib.lib().drone_exchange_sum_local(n, plans, ptrs, f, lds, _stream_ptr(stream)))
 
 
+def row_groups(local2global, n_groups):
+    """Group of every local row, the same on every rank that holds the vertex: a multiplicative hash of the global id."""
+    h = (np.asarray(local2global).astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)) >> np.uint64(40)
+    return (h % np.uint64(n_groups)).astype(np.int32)
+
+
+class PipelinedAggregation:
+    """Aggregation followed by the mirror/master exchange, in n_groups groups of rows: while group g+1 is aggregated
+    on the caller's stream, the rows of group g are exchanged on a second stream.  Same result as
+    plan.spmm(...) + exchange_sum(...) (bit for bit with the peer-memory and send/recv transports).  The data flow of
+    CUDAGraphSum::forward / backward (cuda_gcn/src/cuda/cuda_module.cu:210-307, 310-389) with the two steps
+    overlapped; the reference runs them one after the other."""
+
+    def __init__(self, graph, comm, max_features, n_groups=4, p2p=True):
+        self.graph, self.comm, self.n_groups = graph, comm, int(n_groups)
+        groups = row_groups(graph.host.l2g, self.n_groups)
+        self.row_class = torch.as_tensor(groups, device=graph.device)
+        graph.plan.set_row_classes(self.row_class, self.n_groups)
+        self.xplans = [ExchangePlan(graph.host, max_features, row_mask=groups == g) for g in range(self.n_groups)]
+        if p2p and comm is not None and comm.nranks > 1:
+            for x in self.xplans:
+                x.enable_p2p(comm)
+        with torch.cuda.device(graph.device):
+            # high priority: the exchange kernels are short links of a dependency chain across GPUs; at equal priority
+            # each would queue behind the thousands of blocks of the aggregation running beside it
+            self.side = torch.cuda.Stream(priority=-1)
+            self.ready = [torch.cuda.Event() for _ in range(self.n_groups)]
+            self.done = torch.cuda.Event()
+
+    def __call__(self, orientation, x, out):
+        main = torch.cuda.current_stream(self.graph.device)
+        for g in range(self.n_groups):
+            self.graph.plan.spmm(orientation, x, out=out, row_class=g)
+            self.ready[g].record(main)
+            self.side.wait_event(self.ready[g])
+            exchange_sum(self.xplans[g], self.comm, out, stream=self.side)
+        self.done.record(self.side)
+        main.wait_event(self.done)
+        return out
+
+    def close(self):
+        for x in self.xplans:
+            x.close()
+        self.xplans = []
+
+
 class GraphSum:
     """Drop-in shape of CUDAGraphSum: GraphSum(in, out, graph, comm, dim, worker_id, worker_num, name, layer)."""
 

@@ -35,6 +35,7 @@ class Partition:
         # [V] uint64, bit p set when part p holds the vertex.  A rank that was sent only its own edges (part_u / part_v
         # of the other parts are None) is given this table instead, which is all the routing tables need of them.
         self.present_bits = present_bits
+        self._flat = None               # (u, v) of all parts in one array each, when the parts are views of them
 
     # ----- statistics the reference prints (EBV_mpi.cpp:379-401) -----
     def replication_factor(self):
@@ -47,9 +48,11 @@ class Partition:
     def presence_bits(self):
         """[V] uint64 with bit p set when part p holds the vertex."""
         if self.present_bits is None:
-            bits = np.zeros(self.n_vertices, np.uint64)
-            for q in range(self.n_parts):
-                bits[self.present(q)] |= np.uint64(1 << q)
+            u = np.ascontiguousarray(np.concatenate(self.part_u), np.int32) if self._flat is None else self._flat[0]
+            v = np.ascontiguousarray(np.concatenate(self.part_v), np.int32) if self._flat is None else self._flat[1]
+            off = np.concatenate([[0], np.cumsum([len(x) for x in self.part_u])]).astype(np.int64)
+            bits = np.empty(self.n_vertices, np.uint64)
+            check(_lib.lib().drone_presence_bits_host(self.n_vertices, self.n_parts, _vp(u), _vp(v), _vp(off), _vp(bits)))
             self.present_bits = bits
         return self.present_bits
 
@@ -136,7 +139,9 @@ def ebv_partition(n_vertices, u, v, n_parts, keep_self_loops=True):
                                          _vp(out_u), _vp(out_v), _vp(off), _vp(owner), _vp(replicas)))
     part_u = [out_u[off[p]:off[p + 1]] for p in range(n_parts)]     # views: no second copy of the edge list
     part_v = [out_v[off[p]:off[p + 1]] for p in range(n_parts)]
-    return Partition(n_vertices, n_parts, part_u, part_v, owner, replicas)
+    part = Partition(n_vertices, n_parts, part_u, part_v, owner, replicas)
+    part._flat = (out_u, out_v)
+    return part
 
 
 class LocalGraph:
@@ -181,14 +186,22 @@ class LocalGraph:
 class ExchangePlan:
     """Static routing plan of one rank (drone_xplan)."""
 
-    def __init__(self, local_graph, max_features):
+    def __init__(self, local_graph, max_features, row_mask=None):
+        """row_mask ([n_local] bool): plan the exchange of those rows only (every rank must select the same
+        vertices, e.g. by a function of the global id)."""
         g = local_graph
         self.rank, self.n_parts, self.n_local = g.rank, g.n_parts, g.n_local
-        self._keep = g
+        m2w, mwi, workers = g.mirror2worker, g.master_worker_index, g.master2workers
+        if row_mask is not None:
+            row_mask = np.asarray(row_mask, bool)[:g.n_local]
+            m2w = _i32(np.where(row_mask, m2w[:g.n_local], -1))
+            per_row = np.diff(mwi[:g.n_local + 1])
+            workers = _i32(workers[np.repeat(row_mask, per_row)])
+            mwi = _i32(np.concatenate([[0], np.cumsum(np.where(row_mask, per_row, 0))]))
+        self._keep = (g, m2w, mwi, workers)
         self._h = C.c_void_p(0)
         check(_lib.lib().drone_xplan_create(C.byref(self._h), g.rank, g.n_parts, g.n_local, _vp(g.l2g),
-                                            _vp(g.mirror2worker), _vp(g.master_worker_index), _vp(g.master2workers),
-                                            int(max_features)))
+                                            _vp(m2w), _vp(mwi), _vp(workers), int(max_features)))
 
     @property
     def handle(self):

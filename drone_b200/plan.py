@@ -91,8 +91,20 @@ class AggregationPlan:
                 out.append(_view_device_memory(ptr.value, n, dt, self.device).clone())
         return tuple(out)
 
-    def spmm(self, orientation, x, out=None, stream=None):
-        """out[r,:] = sum_k val[k]*x[col[k],:] (rows of the chosen orientation).  x: [n_rows, F] float32."""
+    def set_row_classes(self, row_class, n_classes, stream=None):
+        """Give every row a class in 0..n_classes-1 (int32 CUDA tensor [n_rows]); spmm(..., row_class=c) then
+        computes the rows of one class only.  n_classes = 1 removes the classes."""
+        if n_classes > 1 and not (row_class.is_cuda and row_class.dtype == torch.int32 and row_class.is_contiguous()
+                                  and row_class.numel() == self.n_rows):
+            raise ValueError("row_class must be a contiguous int32 CUDA tensor with one entry per row")
+        with torch.cuda.device(self.device):
+            check(_lib.lib().drone_plan_set_row_classes(self._h, _ptr(row_class) if n_classes > 1 else C.c_void_p(0),
+                                                        int(n_classes), _stream_ptr(stream)))
+        self.n_classes = int(n_classes)
+
+    def spmm(self, orientation, x, out=None, stream=None, row_class=None):
+        """out[r,:] = sum_k val[k]*x[col[k],:] (rows of the chosen orientation).  x: [n_rows, F] float32.
+        With row_class only the rows of that class are written."""
         if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1):
             raise ValueError("x must be a 2-D float32 CUDA tensor with unit inner stride")
         if x.shape[0] != self.n_rows:
@@ -105,8 +117,12 @@ class AggregationPlan:
         ldx = x.stride(0) if self.n_rows > 1 else max(f, x.stride(0))
         ldy = out.stride(0) if self.n_rows > 1 else max(f, out.stride(0))
         with torch.cuda.device(self.device):
-            check(_lib.lib().drone_spmm(self._h, int(orientation), f, _ptr(x), int(ldx), _ptr(out), int(ldy),
-                                        _stream_ptr(stream)))
+            if row_class is None:
+                check(_lib.lib().drone_spmm(self._h, int(orientation), f, _ptr(x), int(ldx), _ptr(out), int(ldy),
+                                            _stream_ptr(stream)))
+            else:
+                check(_lib.lib().drone_spmm_rows(self._h, int(orientation), int(row_class), f, _ptr(x), int(ldx),
+                                                 _ptr(out), int(ldy), _stream_ptr(stream)))
         return out
 
     def spmm_host(self, orientation, x_host, out_host):

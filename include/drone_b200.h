@@ -121,6 +121,22 @@ int drone_spmm(drone_plan *plan, int orientation, int F,
                const float *d_X, int ldx, float *d_Y, int ldy, void *stream);
 
 /*
+ * Row classes: a way to compute the aggregation a group of output rows at a time, so that what follows the
+ * aggregation for a group (the mirror/master exchange of those rows, cuda_gcn/src/cuda/cuda_module.cu:267-272)
+ * can run on another stream while the next group is still being aggregated.
+ *
+ * drone_plan_set_row_classes gives every row a class in 0..n_classes-1 (d_row_class[n_rows], device memory; at most
+ * 16 classes; n_classes = 1 removes the classes) and rebuilds the plan's work lists class by class; it synchronises
+ * the device.  drone_spmm is unaffected (all rows, same bits as before).  drone_spmm_rows computes only the rows of
+ * one class and leaves every other row of Y as it is; calling it for every class gives bit for bit what drone_spmm
+ * gives.  Calls of one plan must still be ordered among themselves (they share the partial-sum scratch).
+ * The reference has no counterpart: it runs cusparseSpMM over all rows and only then starts the exchange.
+ */
+int drone_plan_set_row_classes(drone_plan *plan, const int *d_row_class, int n_classes, void *stream);
+int drone_spmm_rows(drone_plan *plan, int orientation, int row_class, int F,
+                    const float *d_X, int ldx, float *d_Y, int ldy, void *stream);
+
+/*
  * Same operation with HOST operands: copies X to the device, aggregates, and
  * copies Y back, synchronising before it returns.  Device staging buffers are
  * owned by the plan and reused across calls.  h_X and h_Y are dense
@@ -352,6 +368,14 @@ int drone_ebv_partition(int n_vertices, long long n_edges, const int *h_u, const
                         int n_parts, int keep_self_loops,
                         int *h_out_u, int *h_out_v, long long *h_part_offset,
                         int *h_owner, int *h_replicas);
+
+/*
+ * Which parts hold which vertex, from the partitioned edge list drone_ebv_partition returned: h_bits[v] has bit p
+ * set when v is an endpoint of an edge of part p.  One word per vertex is what a rank needs of the other parts to
+ * write its Master.<p> rows (EBV_mpi.cpp:583-603 walks the parts' vertex sets for the same purpose).
+ */
+int drone_presence_bits_host(int n_vertices, int n_parts, const int *h_u, const int *h_v,
+                             const long long *h_part_offset, unsigned long long *h_bits);
 
 /*
  * One rank's local graph from the edge list of its G.<p> file (host arrays in,

@@ -43,6 +43,58 @@ def test_all_parts_on_one_gpu(cuda_device, oracle, parts, f):
         assert scale > 0
 
 
+@pytest.mark.parametrize("parts,groups,f", [(2, 2, 32), (4, 3, 41), (3, 4, 64)])
+def test_rows_in_groups_give_the_same_bits(cuda_device, oracle, parts, groups, f):
+    """Aggregating and exchanging the rows a group at a time (groups chosen from the global id, so every part makes
+    the same choice) gives bit for bit the result of one aggregation followed by one exchange."""
+    n, part, in_deg, out_deg, x, want_fwd, want_bwd = setup_case(oracle, parts, scale=11, seed=21, f=f, sym=True)
+    graphs = [gs.DeviceGraph(part.local_graph(p), in_deg, out_deg, cuda_device, max_features=64) for p in range(parts)]
+    xs = [torch.as_tensor(x[g.host.l2g], device=cuda_device) for g in graphs]
+    for op, want in ((db.OP_AT, want_fwd), (db.OP_A, want_bwd)):
+        whole = [g.plan.spmm(op, xx) for g, xx in zip(graphs, xs)]
+        gs.exchange_sum_local([g.xplan for g in graphs], whole)
+        klass = [gs.row_groups(g.host.l2g, groups) for g in graphs]
+        for g, k in zip(graphs, klass):
+            g.plan.set_row_classes(torch.as_tensor(k, device=cuda_device), groups)
+        sub = [[pt.ExchangePlan(g.host, 64, row_mask=k == c) for c in range(groups)] for g, k in zip(graphs, klass)]
+        assert sum(int(s.counts()[0].sum()) for s in sub[0]) == int(graphs[0].xplan.counts()[0].sum())
+        rows = [torch.full((g.n_local, f), float("nan"), device=cuda_device) for g in graphs]
+        for c in range(groups):
+            for g, xx, r in zip(graphs, xs, rows):
+                g.plan.spmm(op, xx, out=r, row_class=c)
+            gs.exchange_sum_local([s[c] for s in sub], rows)
+        all_rows = [g.plan.spmm(op, xx) for g, xx in zip(graphs, xs)]      # the plain call on a plan with classes
+        gs.exchange_sum_local([g.xplan for g in graphs], all_rows)
+        torch.cuda.synchronize()
+        for p, g in enumerate(graphs):
+            assert torch.equal(rows[p], whole[p])
+            assert torch.equal(all_rows[p], whole[p])
+            assert_close_to_oracle(rows[p].cpu().numpy(), want[g.host.l2g])
+        for g in graphs:
+            g.plan.set_row_classes(None, 1)
+        again = [g.plan.spmm(op, xx) for g, xx in zip(graphs, xs)]
+        gs.exchange_sum_local([g.xplan for g in graphs], again)
+        for p in range(parts):
+            assert torch.equal(again[p], whole[p])
+
+
+def test_row_classes_check_arguments(cuda_device):
+    n, u, v = gg.rmat_graph(9, 8, seed=5, device=cuda_device, self_loops="add")
+    index, dst = gg.csr_by_source(u, v, n)
+    ind, outd = gg.degrees(u, v, n)
+    plan = db.AggregationPlan(index, dst, in_degree=ind, out_degree=outd)
+    x = torch.randn((n, 8), device=cuda_device)
+    with pytest.raises(db.DroneError, match="row_class"):
+        plan.spmm(db.OP_AT, x, row_class=1)                 # no classes set
+    bad = torch.full((n,), 3, dtype=torch.int32, device=cuda_device)
+    with pytest.raises(db.DroneError, match="class outside"):
+        plan.set_row_classes(bad, 2)
+    with pytest.raises(db.DroneError, match="n_classes"):
+        plan.set_row_classes(bad, 17)
+    want = plan.spmm(db.OP_AT, x)                           # the failed calls left the plan usable
+    assert torch.isfinite(want).all()
+
+
 def test_exchange_is_repeatable_and_checks_arguments(cuda_device, oracle):
     n, part, in_deg, out_deg, x, want_fwd, _ = setup_case(oracle, 3, scale=10, seed=9, f=16)
     graphs = [gs.DeviceGraph(part.local_graph(p), in_deg, out_deg, cuda_device, max_features=16) for p in range(3)]
@@ -97,6 +149,16 @@ def _nccl_rank(rank, world, port, ok):
             layer.backward()
         torch.cuda.synchronize()
         assert torch.equal(b.data, nccl_fwd) and torch.equal(a.grad, nccl_bwd)
+        # aggregation and exchange overlapped over four row groups: the same bits again
+        piped = gs.PipelinedAggregation(g, comm, f, n_groups=4)
+        for op, src, want_bits in ((db.OP_AT, a.data, nccl_fwd), (db.OP_A, b.grad, nccl_bwd)):
+            for _ in range(3):
+                out = torch.full((g.n_local, f), float("nan"), device=dev)
+                piped(op, src, out)
+                torch.cuda.synchronize()
+                assert torch.equal(out, want_bits)
+        piped.close()
+        g.plan.set_row_classes(None, 1)
         narrow = torch.as_tensor(x[g.host.l2g][:, :5].copy(), device=dev)      # a width below max_features
         ref = g.plan.spmm(db.OP_AT, narrow)
         gs.exchange_sum(g.xplan, comm, ref)

@@ -117,3 +117,24 @@ def test_bad_input_is_an_error():
         pt.ebv_partition(4, np.array([0, 9], np.int32), np.array([1, 2], np.int32), 2)
     with pytest.raises(db.DroneError, match="n_parts"):
         pt.ebv_partition(4, np.array([0], np.int32), np.array([1], np.int32), 0)
+
+
+def test_rank_with_only_its_own_edges_builds_the_same_tables():
+    """A rank that holds its own edges plus the presence words of all vertices gets the same local graph and
+    routing tables as one that holds the whole partition."""
+    n, u, v = gg.rmat_graph(11, 8, seed=77, device="cpu", self_loops="add")
+    u, v = np.asarray(u), np.asarray(v)
+    parts = 5
+    full = pt.ebv_partition(n, u, v, parts)
+    bits = full.presence_bits()
+    plain = pt.Partition(n, parts, full.part_u, full.part_v, full.owner, full.replicas)
+    for q in range(parts):
+        assert np.array_equal((bits >> np.uint64(q)) & np.uint64(1) != 0, plain.present(q))
+    assert np.array_equal(np.array([bin(int(b)).count("1") for b in bits]), full.replicas)
+    for p in range(parts):
+        pu, pv = [None] * parts, [None] * parts
+        pu[p], pv[p] = full.part_u[p], full.part_v[p]
+        alone = pt.Partition(n, parts, pu, pv, full.owner, full.replicas, present_bits=bits)
+        a, b = alone.local_graph(p), plain.local_graph(p)
+        for name in ("l2g", "index", "dst", "master_worker_index", "master2workers", "mirror2worker"):
+            assert np.array_equal(getattr(a, name), getattr(b, name)), name
