@@ -95,6 +95,12 @@ def _declare(lib):
         "drone_pr_values": (i, [vp, vp, vp]),
         "drone_pr_set_isolated_count": (i, [vp, ll]),
         "drone_pr_device_arrays": (i, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
+        "drone_mp_create": (i, [C.POINTER(vp), i, i, i, vp, vp, vp, vp, vp, vp]),
+        "drone_mp_destroy": (i, [vp]),
+        "drone_mp_peval": (i, [vp, i, C.POINTER(PRResponse), vp]),
+        "drone_mp_inceval": (i, [vp, C.POINTER(PRResponse), vp]),
+        "drone_mp_step_local": (i, [i, C.POINTER(vp), i, i, C.POINTER(PRResponse), vp]),
+        "drone_mp_values": (i, [vp, vp, vp]),
         "drone_ebv_partition": (i, [i, ll, vp, vp, i, i, vp, vp, vp, vp, vp]),
         "drone_presence_bits_host": (i, [i, i, vp, vp, vp, vp]),
         "drone_graph_build_host": (i, [i, i, vp, vp, vp, vp, vp, vp, C.POINTER(i)]),

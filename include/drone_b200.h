@@ -353,6 +353,48 @@ int drone_pr_device_arrays(drone_pr *pr, void **d_pr, void **d_acc, void **d_dif
 /* Current values by local id into h_out (n_local floats or doubles); synchronises. */
 int drone_pr_values(drone_pr *pr, void *h_out, void *stream);
 
+/* ------------------------------------------------------------------------- */
+/* Connected components and shortest paths (minimum propagation)               */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * The "cc_cuda" and "sssp_cuda" jobs: a value is pushed along the local out-edges until nothing changes (a label
+ * as it is, a distance plus the edge length), then mirrors and masters exchange minima over the same static plan
+ * as the aggregation.  One handle is one worker's state; it replaces CCValues / SSSPValues and the Graph.active /
+ * Graph.updateByMessage arrays (DRONE/src/cuda/algorithm/cc.h:18-22, sssp.h:8-12, DRONE/src/cuda/graph.h:33-35).
+ *
+ * drone_mp_create: d_index / d_dst = the worker's CSR by source (build_graph, DRONE/src/cuda/graph.cu:94-103),
+ *   d_edge_len = Graph.edgeLen (NULL: every edge has length 1, what build_graph stores), d_local2global =
+ *   Graph.Local2Global; all four are device arrays the caller keeps alive while the handle exists.
+ * drone_mp_peval   = CC_PEVal (cc.cu:319-383) or SSSP_PEVal (sssp.cu:398-476): start values, local run, exchange.
+ *   source_global_id is SSSP's startId (ignored for labels; a worker that does not hold it starts idle).
+ * drone_mp_inceval = CC_IncEVal (cc.cu:400-447) / SSSP_IncEVal (sssp.cu:494-538): vertices lowered by a message
+ *   form the new frontier, local run, exchange.
+ * The returned Response has the reference's meaning field by field: the four sizes count the boundary vertices that
+ * changed and were sent / received, VisitedSize counts the non-zero entries of `active` (common.cu:6-16); the
+ * job is over when all four sizes are zero on every worker (DRONE/src/tools/cuda_convert.go:47-52).
+ *
+ * Two differences from the reference's kernels, both on purpose: labels start as the GLOBAL vertex id, as in the CPU
+ * job (DRONE/src/algorithm/CC.go:73-79) — cc_init (cc.cu:14) writes the local index, which workers cannot compare;
+ * and a shorter distance always re-activates its vertex — sssp_exec (sssp.cu:67) asks for an improvement above
+ * 1e-6.  With unit lengths the second rule gives the same distances.  Results do not depend on the order of the
+ * atomics: the fixed point of a minimum is unique.  Distances use 1e8 for "not reached" (sssp.cu:33).
+ */
+#define DRONE_MP_CC   0
+#define DRONE_MP_SSSP 1
+typedef struct drone_mp drone_mp;
+int drone_mp_create(drone_mp **out, int kind, int n_local, int nnz, const int *d_index, const int *d_dst,
+                    const float *d_edge_len, const int *d_local2global, drone_xplan *xplan, drone_comm *comm);
+int drone_mp_destroy(drone_mp *job);
+int drone_mp_peval(drone_mp *job, int source_global_id, drone_pr_response *res, void *stream);
+int drone_mp_inceval(drone_mp *job, drone_pr_response *res, void *stream);
+/* One superstep of ALL parts of a partition held by one process on one device (jobs[p] is worker p of n_parts):
+ * messages become device-to-device copies; res[n_parts].  No counterpart in the reference. */
+int drone_mp_step_local(int n_parts, drone_mp **jobs, int is_peval, int source_global_id, drone_pr_response *res,
+                        void *stream);
+/* Current values by local id into h_out: n_local int32 labels or float32 distances; synchronises. */
+int drone_mp_values(drone_mp *job, void *h_out, void *stream);
+
 /*
  * EBV vertex-cut partitioner (host, single process).  Input: directed edge
  * list in global ids.  Output: the edges grouped by part in the order the

@@ -1,8 +1,8 @@
-"""numpy-facing wrappers of the CPU oracle (oracle/drone_oracle.c, oracle/pagerank_oracle.c).
+"""numpy-facing wrappers of the CPU oracle (oracle/drone_oracle.c, oracle/pagerank_oracle.c, oracle/minprop_oracle.c).
 
 TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
 CPU-baseline / reference legs of bench.py; never by the drone_b200 package.
-Parity status is stated in the headers of the two C files.
+Parity status is stated in the headers of the C files.
 """
 import ctypes as C
 import os
@@ -16,7 +16,7 @@ _SO = os.path.join(_HERE, "_build", "libdrone_oracle.so")
 
 def build(force=False):
     """Compile the oracle with the committed Makefile (gcc, a few seconds)."""
-    srcs = [os.path.join(_HERE, f) for f in ("drone_oracle.c", "pagerank_oracle.c", "Makefile")]
+    srcs = [os.path.join(_HERE, f) for f in ("drone_oracle.c", "pagerank_oracle.c", "minprop_oracle.c", "Makefile")]
     if force or not os.path.exists(_SO) or any(os.path.getmtime(s) > os.path.getmtime(_SO) for s in srcs):
         subprocess.run(["make", "-C", _HERE, "-B" if force else "-s"], check=True,
                        stdout=subprocess.DEVNULL)
@@ -223,6 +223,47 @@ def pr_drone_cuda(global_v, parts_u, parts_v, out_degree, owner, eps=1e-6, max_s
         steps = lib().oracle_pr_drone_cuda_f64(len(parts_u), global_v, _p(eoff, C.c_int), _p(eu, C.c_int),
                                                _p(ev, C.c_int), _p(od, C.c_int), _p(ow, C.c_int), C.c_double(eps),
                                                int(max_steps), _p(out, C.c_double), _p(sizes, C.c_longlong))
+    return out, steps, sizes[:steps]
+
+
+def cc_fixed_point(rowptr, col):
+    """label[v] = smallest id among the vertices that reach v along the edges (v included)."""
+    rowptr, col = _i32(rowptr), _i32(col)
+    n = len(rowptr) - 1
+    out = np.empty(n, np.int32)
+    lib().oracle_cc_fixed_point(n, _p(rowptr, C.c_int), _p(col, C.c_int), _p(out, C.c_int))
+    return out
+
+
+def sssp_f32(rowptr, col, source, edge_len=None):
+    """float32 distances from `source` (1e8 = not reached); edge_len None means 1.0 everywhere."""
+    rowptr, col = _i32(rowptr), _i32(col)
+    n = len(rowptr) - 1
+    out = np.empty(n, np.float32)
+    el = _f32(edge_len) if edge_len is not None else None
+    lib().oracle_sssp_f32(n, _p(rowptr, C.c_int), _p(col, C.c_int), _p(el, C.c_float) if el is not None else None,
+                          int(source), _p(out, C.c_float))
+    return out
+
+
+MP_CC, MP_SSSP = 0, 1
+
+
+def mp_drone_cuda(kind, global_v, parts_u, parts_v, owner, source=-1, parts_len=None, max_steps=1000):
+    """DRONE's GPU jobs "cc_cuda" (kind MP_CC) / "sssp_cuda" (MP_SSSP) over a partition.
+    Returns (values[global_v] float32, supersteps, sizes[steps, P, 5]): per worker and superstep the four exchange
+    sizes of struct Response and VisitedSize."""
+    P = len(parts_u)
+    eoff = np.concatenate([[0], np.cumsum([len(x) for x in parts_u])]).astype(np.int32)
+    eu = _i32(np.concatenate(parts_u)) if eoff[-1] else np.zeros(1, np.int32)
+    ev = _i32(np.concatenate(parts_v)) if eoff[-1] else np.zeros(1, np.int32)
+    el = _f32(np.concatenate(parts_len)) if parts_len is not None else None
+    ow = _i32(owner)
+    out = np.empty(global_v, np.float32)
+    sizes = np.zeros((max_steps + 1, P, 5), np.int64)
+    steps = lib().oracle_mp_drone_cuda(int(kind), P, int(global_v), _p(eoff, C.c_int), _p(eu, C.c_int), _p(ev, C.c_int),
+                                       _p(el, C.c_float) if el is not None else None, _p(ow, C.c_int), int(source),
+                                       int(max_steps), _p(out, C.c_float), _p(sizes, C.c_longlong))
     return out, steps, sizes[:steps]
 
 
