@@ -101,6 +101,7 @@ def _declare(lib):
         "drone_mp_inceval": (i, [vp, C.POINTER(PRResponse), vp]),
         "drone_mp_step_local": (i, [i, C.POINTER(vp), i, i, C.POINTER(PRResponse), vp]),
         "drone_mp_values": (i, [vp, vp, vp]),
+        "drone_mp_device_arrays": (i, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "drone_ebv_partition": (i, [i, ll, vp, vp, i, i, vp, vp, vp, vp, vp]),
         "drone_presence_bits_host": (i, [i, i, vp, vp, vp, vp]),
         "drone_graph_build_host": (i, [i, i, vp, vp, vp, vp, vp, vp, C.POINTER(i)]),

@@ -1,10 +1,12 @@
 /*
- * drone_pr_compat.h — the C interface DRONE's Go workers bind through cgo for the pr_cuda job, served by
- * libdrone_b200.  libdrone_pr_compat.so exports exactly these symbols, so it can take the place of
- * libGRAPH_Lib + libPR_Lib + libALG_COMMON_Lib on the link line of DRONE/src/tools/cuda_convert.go:6-12.
+ * drone_pr_compat.h — the C interface DRONE's Go workers bind through cgo for the pr_cuda, cc_cuda and sssp_cuda
+ * jobs, served by libdrone_b200.  libdrone_pr_compat.so exports exactly these symbols, so it can take the place of
+ * libGRAPH_Lib + libPR_Lib + libCC_Lib + libSSSP_Lib + libALG_COMMON_Lib on the link line of
+ * DRONE/src/tools/cuda_convert.go:6-12.
  *
  * The struct layouts repeat, field for field, DRONE/src/cuda/graph.h:16-43 (Graph, Comm),
- * DRONE/src/cuda/algorithm/pr.h:7-16 (PRValues) and DRONE/src/cuda/algorithm/common.h:23-27 (Response): Go
+ * DRONE/src/cuda/algorithm/pr.h:7-16 (PRValues), cc.h:18-22 (CCValues), sssp.h:8-12 (SSSPValues) and
+ * DRONE/src/cuda/algorithm/common.h:23-27 (Response): Go
  * allocates Comm and PRValues itself and receives Response by value, so sizes and offsets are part of the ABI.
  */
 #ifndef DRONE_PR_COMPAT_H
@@ -48,6 +50,18 @@ typedef struct PRValues {
     int *outDegree;
 } PRValues;
 
+typedef struct CCValues {
+    int *sendID, *recvID;              /* unused: the exchange is static */
+    int *sendCCValue, *recvCCValue;    /* unused */
+    int *ccValue;                      /* device, [localVertexSize]: labels (GLOBAL vertex ids), set by CC_PEVal */
+} CCValues;
+
+typedef struct SSSPValues {
+    int *sendID, *recvID;              /* unused */
+    float *sendDis, *recvDis;          /* unused */
+    float *distance;                   /* device, [localVertexSize]; 1e8 = not reached; set by SSSP_PEVal */
+} SSSPValues;
+
 typedef struct Response {
     int Mirror2MasterSendSize, Mirror2MasterRecvSize, Master2MirrorSendSize, Master2MirrorRecvSize;
     int VisitedSize, LocalVertexSize;
@@ -67,6 +81,13 @@ void addMirrorRoute(Graph *g, int *mirrorVertex, int *masterWorker, int mirrorSi
 void loadOutDegree(Graph *g, PRValues *values, int *globalOutDegree);
 Response PR_PEVal(Graph *g, PRValues *values, int workerId, int workerNum, Comm *comm);
 Response PR_IncEVal(Graph *g, PRValues *values, int workerId, int workerNum, Comm *comm);
+
+
+/* DRONE/src/cuda/algorithm/cc.h:25-26 and sssp.h:15-16 */
+Response CC_PEVal(Graph *g, CCValues *values, int workerId, int workerNum, Comm *comm);
+Response CC_IncEVal(Graph *g, CCValues *values, int workerId, int workerNum, Comm *comm);
+Response SSSP_PEVal(Graph *g, SSSPValues *values, int startId, int workerId, int workerNum, Comm *comm);
+Response SSSP_IncEVal(Graph *g, SSSPValues *values, int workerId, int workerNum, Comm *comm);
 
 #ifdef __cplusplus
 }

@@ -26,6 +26,7 @@ struct GraphImpl {
     drone_xplan *xplan = nullptr;
     drone_comm *dcomm = nullptr;
     drone_pr *pr = nullptr;
+    drone_mp *cc = nullptr, *sssp = nullptr;
 };
 
 GraphImpl *impl_of(Graph *g) { return reinterpret_cast<GraphImpl *>(g); }
@@ -209,6 +210,48 @@ static Response run_step(Graph *gp, PRValues *values, int workerId, int workerNu
     static_assert(sizeof(Response) == sizeof(drone_pr_response), "Response layout");
     memcpy(&res, &r, sizeof(res));
     return res;
+}
+
+// CC / SSSP: one drone_mp handle per job kind and graph, made at the first PEval.
+static Response run_mp(Graph *gp, int kind, drone_mp **job, void **value_out, int start_id, Comm *comm, bool peval) {
+    GraphImpl *g = impl_of(gp);
+    check_cuda(cudaSetDevice(gp->GID), "cudaSetDevice");   // calls arrive on arbitrary OS threads
+    if (!*job) {
+        build_routes(g);
+        check(drone_mp_create(job, kind, g->n_local, g->n_edges, gp->index, gp->dst,
+                              kind == DRONE_MP_SSSP ? gp->edgeLen : nullptr, gp->Local2Global, g->xplan, g->dcomm),
+              "drone_mp_create");
+    }
+    check(drone_mp_device_arrays(*job, value_out, &gp->active, &gp->updateByMessage), "drone_mp_device_arrays");
+    drone_pr_response r;
+    check(peval ? drone_mp_peval(*job, start_id, &r, comm->s) : drone_mp_inceval(*job, &r, comm->s),
+          peval ? "drone_mp_peval" : "drone_mp_inceval");
+    Response res;
+    memcpy(&res, &r, sizeof(res));
+    return res;
+}
+
+Response CC_PEVal(Graph *g, CCValues *values, int workerId, int workerNum, Comm *comm) {
+    (void)workerId; (void)workerNum;
+    values->sendID = values->recvID = values->sendCCValue = values->recvCCValue = nullptr;
+    return run_mp(g, DRONE_MP_CC, &impl_of(g)->cc, (void **)&values->ccValue, -1, comm, true);
+}
+
+Response CC_IncEVal(Graph *g, CCValues *values, int workerId, int workerNum, Comm *comm) {
+    (void)workerId; (void)workerNum;
+    return run_mp(g, DRONE_MP_CC, &impl_of(g)->cc, (void **)&values->ccValue, -1, comm, false);
+}
+
+Response SSSP_PEVal(Graph *g, SSSPValues *values, int startId, int workerId, int workerNum, Comm *comm) {
+    (void)workerId; (void)workerNum;
+    values->sendID = values->recvID = nullptr;
+    values->sendDis = values->recvDis = nullptr;
+    return run_mp(g, DRONE_MP_SSSP, &impl_of(g)->sssp, (void **)&values->distance, startId, comm, true);
+}
+
+Response SSSP_IncEVal(Graph *g, SSSPValues *values, int workerId, int workerNum, Comm *comm) {
+    (void)workerId; (void)workerNum;
+    return run_mp(g, DRONE_MP_SSSP, &impl_of(g)->sssp, (void **)&values->distance, -1, comm, false);
 }
 
 Response PR_PEVal(Graph *g, PRValues *values, int workerId, int workerNum, Comm *comm) {

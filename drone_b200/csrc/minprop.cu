@@ -460,6 +460,14 @@ int drone_mp_step_local(int n_parts, drone_mp **jobs, int is_peval, int source_g
     return mp_run(parts, is_peval != 0, source_global_id, true, res, stream);
 }
 
+int drone_mp_device_arrays(drone_mp *p, void **d_value, int **d_active, int **d_update_by_message) {
+    DRONE_REQUIRE(p != nullptr, "drone_mp_device_arrays: NULL job");
+    if (d_value) *d_value = p->value;
+    if (d_active) *d_active = p->active;
+    if (d_update_by_message) *d_update_by_message = p->ubm;
+    return DRONE_OK;
+}
+
 int drone_mp_values(drone_mp *p, void *h_out, void *stream) {
     DRONE_REQUIRE(p != nullptr && h_out != nullptr, "drone_mp_values: NULL argument");
     if (p->n_local == 0) return DRONE_OK;

@@ -392,6 +392,9 @@ int drone_mp_inceval(drone_mp *job, drone_pr_response *res, void *stream);
  * messages become device-to-device copies; res[n_parts].  No counterpart in the reference. */
 int drone_mp_step_local(int n_parts, drone_mp **jobs, int is_peval, int source_global_id, drone_pr_response *res,
                         void *stream);
+/* Device arrays of the state by local id, owned by the handle: what CCValues.ccValue / SSSPValues.distance and
+ * Graph.active / Graph.updateByMessage point to in the reference (int32 labels or float32 distances). */
+int drone_mp_device_arrays(drone_mp *job, void **d_value, int **d_active, int **d_update_by_message);
 /* Current values by local id into h_out: n_local int32 labels or float32 distances; synchronises. */
 int drone_mp_values(drone_mp *job, void *h_out, void *stream);
 

@@ -37,6 +37,16 @@ class PRValues(C.Structure):   # DRONE/src/cuda/algorithm/pr.h:7-16
                 ("globalAcc", C.c_void_p), ("globalDiff", C.c_void_p), ("outDegree", C.c_void_p)]
 
 
+class CCValues(C.Structure):   # DRONE/src/cuda/algorithm/cc.h:18-22
+    _fields_ = [("sendID", C.c_void_p), ("recvID", C.c_void_p), ("sendCCValue", C.c_void_p),
+                ("recvCCValue", C.c_void_p), ("ccValue", C.c_void_p)]
+
+
+class SSSPValues(C.Structure):  # DRONE/src/cuda/algorithm/sssp.h:8-12
+    _fields_ = [("sendID", C.c_void_p), ("recvID", C.c_void_p), ("sendDis", C.c_void_p), ("recvDis", C.c_void_p),
+                ("distance", C.c_void_p)]
+
+
 class Response(C.Structure):   # DRONE/src/cuda/algorithm/common.h:23-27
     _fields_ = [("Mirror2MasterSendSize", C.c_int), ("Mirror2MasterRecvSize", C.c_int),
                 ("Master2MirrorSendSize", C.c_int), ("Master2MirrorRecvSize", C.c_int), ("VisitedSize", C.c_int),
@@ -61,7 +71,37 @@ def pr_lib():
     for fn in (lib.PR_PEVal, lib.PR_IncEVal):
         fn.restype = Response
         fn.argtypes = [C.POINTER(Graph), C.POINTER(PRValues), C.c_int, C.c_int, C.POINTER(Comm)]
+    for fn in (lib.CC_PEVal, lib.CC_IncEVal):
+        fn.restype = Response
+        fn.argtypes = [C.POINTER(Graph), C.POINTER(CCValues), C.c_int, C.c_int, C.POINTER(Comm)]
+    lib.SSSP_PEVal.restype = lib.SSSP_IncEVal.restype = Response
+    lib.SSSP_PEVal.argtypes = [C.POINTER(Graph), C.POINTER(SSSPValues), C.c_int, C.c_int, C.c_int, C.POINTER(Comm)]
+    lib.SSSP_IncEVal.argtypes = [C.POINTER(Graph), C.POINTER(SSSPValues), C.c_int, C.c_int, C.POINTER(Comm)]
     return lib
+
+
+def run_cc_and_sssp(lib, g, comm, rank, world, source, all_reduce=None):
+    """The superstep loops of CCworkerCUDA / SSSPworkerCUDA with the master's stop rule; returns labels, distances
+    (device pointers inside the value structs) and the number of supersteps of each job."""
+    out = []
+    for job in ("cc", "sssp"):
+        vals = CCValues() if job == "cc" else SSSPValues()
+        if job == "cc":
+            res = lib.CC_PEVal(g, C.byref(vals), rank, world, C.byref(comm))
+        else:
+            res = lib.SSSP_PEVal(g, C.byref(vals), source, rank, world, C.byref(comm))
+        steps = 1
+        while True:
+            busy = (res.Mirror2MasterSendSize + res.Mirror2MasterRecvSize + res.Master2MirrorSendSize +
+                    res.Master2MirrorRecvSize)
+            if all_reduce is not None:
+                busy = all_reduce(busy)
+            if busy == 0 or steps > 200:
+                break
+            res = (lib.CC_IncEVal if job == "cc" else lib.SSSP_IncEVal)(g, C.byref(vals), rank, world, C.byref(comm))
+            steps += 1
+        out.append((vals, steps))
+    return out
 
 
 def ints(a):
@@ -117,6 +157,28 @@ def test_pr_c_interface_single_worker(cuda_device, oracle, tmp_path, monkeypatch
     assert np.isfinite(got).all() and got[l2g].min() > 0.1
     ref = n * dense_power(n, u, v, 400, float(np.float32(0.85)))
     assert np.max(np.abs(got[l2g] - ref[l2g]) / ref[l2g]) < 2e-3     # float, eps = 1e-6, 30 supersteps
+
+
+def device_ints(ptr, n, dev):
+    from drone_b200.plan import _view_device_memory
+    return _view_device_memory(ptr, n, torch.int32, dev).clone().cpu().numpy()
+
+
+def test_cc_and_sssp_c_interface_single_worker(cuda_device, oracle, tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    from test_minprop_oracle import csr
+    lib = pr_lib()
+    n, u, v, out_deg, part = pr_case(scale=9, seed=45, parts=1)
+    g, comm, _ = run_pr_worker(lib, part, 0, 1, n, out_deg)
+    nloc = lib.getLocalVertexSize(g)
+    l2g = part.local_graph(0).l2g
+    source = int(u[3])
+    (cc, cc_steps), (sp, sp_steps) = run_cc_and_sssp(lib, g, comm, 0, 1, source)
+    assert cc_steps == 1 and sp_steps == 1
+    rowptr, col, _ = csr(n, u, v)
+    assert np.array_equal(device_ints(cc.ccValue, nloc, cuda_device), oracle.cc_fixed_point(rowptr, col)[l2g])
+    assert np.array_equal(device_floats(sp.distance, nloc, cuda_device), oracle.sssp_f32(rowptr, col, source)[l2g])
+    assert g.contents.active and g.contents.updateByMessage
 
 
 def gcn_lib():
@@ -177,6 +239,27 @@ def _two_workers(rank, world, workdir, ok):
     keep = lg.mirror2worker == -1
     gid = lg.l2g[keep]
     assert np.max(np.abs(vals[keep] - want[gid]) / want[gid]) < 2e-4
+
+    # the cc_cuda and sssp_cuda jobs through the same Graph and communicator
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(29700 + os.getppid() % 2000)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def total(x):
+        t = torch.tensor([x], dtype=torch.int64)
+        dist.all_reduce(t)
+        return int(t)
+
+    from test_minprop_oracle import csr
+    source = int(u[3])
+    (cc, cc_steps), (sp, sp_steps) = run_cc_and_sssp(lib, g, comm, rank, world, source, all_reduce=total)
+    rowptr, col, _ = csr(n, u, v)
+    assert np.array_equal(device_ints(cc.ccValue, nloc, dev), oracle.cc_fixed_point(rowptr, col)[lg.l2g])
+    assert np.array_equal(device_floats(sp.distance, nloc, dev), oracle.sssp_f32(rowptr, col, source)[lg.l2g])
+    assert cc_steps == oracle.mp_drone_cuda(oracle.MP_CC, n, part.part_u, part.part_v, part.owner)[1]
+    assert sp_steps == oracle.mp_drone_cuda(oracle.MP_SSSP, n, part.part_u, part.part_v, part.owner, source=source)[1]
+    dist.barrier()
+    dist.destroy_process_group()
 
     # the C++ GraphSum module over the communicator that build_graph created
     glib = gcn_lib()
