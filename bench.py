@@ -356,6 +356,10 @@ def run_ours(args, cfg):
             line["pagerank"] = pagerank_timing(device)
         except Exception as e:
             line["pagerank"] = {"error": repr(e)}
+        try:
+            line["minprop"] = minprop_timing(device)
+        except Exception as e:
+            line["minprop"] = {"error": repr(e)}
 
     if not args.no_cpu_baseline:
         from oracle import oracle
@@ -485,6 +489,47 @@ def one_part_pagerank(device, n, index, dst, out_degree, iterations):
            "edges_per_s": nnz / (ms_it * 1e-3), "algorithmic_GBps": b_alg / (ms_it * 1e-3) / 1e9}
     pr1.close()
     return res
+
+
+def minprop_timing(device):
+    """The cc_cuda / sssp_cuda jobs on one part: labels on R-MAT-20 symmetrised (connected components) and
+    unit-length distances on R-MAT-22 directed from the vertex with the most out-edges, each checked against the CPU
+    restatement (one host core) and timed next to it."""
+    import types
+    from drone_b200 import graphgen as gg, minprop as mpj, partition as pt
+    from oracle import oracle
+    out = {}
+    for name, scale, sym, kind in (("cc_rmat20_sym", 20, True, mpj.CC), ("sssp_rmat22_directed", 22, False, mpj.SSSP)):
+        n, u, v = gg.rmat_graph(scale, 16, seed=20261140 + scale, device=device, symmetrise=sym, self_loops="drop")
+        index, dst = gg.csr_by_source(u, v, n)
+        _, outd = gg.degrees(u, v, n)
+        source = int(torch.argmax(outd)) if kind == mpj.SSSP else -1
+        del u, v
+        host = types.SimpleNamespace(rank=0, n_parts=1, n_local=n, l2g=np.arange(n, dtype=np.int32),
+                                     mirror2worker=np.full(n, -1, np.int32), master_worker_index=np.zeros(n + 1, np.int32),
+                                     master2workers=np.zeros(0, np.int32))
+        g = types.SimpleNamespace(host=host, n_local=n, device=device, index=index, dst=dst,
+                                  xplan=pt.ExchangePlan(host, 1))
+        job = mpj.MinProp(g, kind)
+        job.peval(source)                       # warm-up
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = job.peval(source)                 # synchronous: returns when the local run has converged
+        gpu_s = time.perf_counter() - t0
+        got = job.values()
+        ih, dh = index.cpu().numpy(), dst.cpu().numpy()
+        t0 = time.perf_counter()
+        want = oracle.cc_fixed_point(ih, dh) if kind == mpj.CC else oracle.sssp_f32(ih, dh, source)
+        cpu_s = time.perf_counter() - t0
+        nnz = int(dst.numel())
+        out[name] = {"vertices": n, "edges": nnz, "gpu_ms": 1e3 * gpu_s, "cpu_restatement_s": cpu_s, "cpu_cores": 1,
+                     "identical_to_restatement": bool(np.array_equal(got, want)), "visited": int(res.VisitedSize),
+                     "distinct_labels" if kind == mpj.CC else "reached": int(len(np.unique(got)) if kind == mpj.CC
+                                                                              else (got < 1e8).sum())}
+        job.close()
+        del index, dst, outd
+        torch.cuda.empty_cache()
+    return out
 
 
 def pagerank_timing(device):

@@ -5,8 +5,9 @@
 // DRONE/src/cuda/algorithm/cc.cu and sssp.cu (PEval / IncEval and their helper kernels) with these changes:
 //   * one state, one set of kernels for both jobs: distances are non-negative floats, whose bit patterns order like
 //     unsigned integers, so both kinds are "atomicMin on a 32-bit word";
-//   * a warp works on 32 vertices; rows above kSerialDegree edges are spread over the warp's lanes (the reference
-//     walks every row with one thread, which a hub row turns into one long serial loop);
+//   * a warp works on 32 vertices; rows above kSerialDegree edges are spread over the warp's lanes, and rows above
+//     kHeavyDegree are cut into chunks that a second kernel hands to all warps of the grid (the reference walks
+//     every row with one thread, which a hub row turns into one long serial loop);
 //   * the exchange uses the static plan (rows in a fixed order, no ids on the wire, no allocation per superstep);
 //     every boundary vertex travels as {value, flag} and only flagged entries count and are applied, which gives the
 //     same values and the same Response sizes as the reference's lists of changed vertices;
@@ -36,13 +37,18 @@ struct drone_mp {
     int *active = nullptr;         // [n] -1 idle, s = in the frontier of step s; > 0 after a run: lowered in that run
     int *ubm = nullptr;            // [n] lowered by a received message since the last sweep
     uint2 *send = nullptr, *recv = nullptr;   // [max(up, down)] {value, flag}
-    int *counters = nullptr;       // [0..3] exchange sizes, [4] VisitedSize, [5] "a step lowered something"
+    int *counters = nullptr;       // [0..3] exchange sizes, [4] VisitedSize, [5] "a step lowered something",
+                                   // [6] entries in `heavy`
+    int2 *heavy = nullptr;         // [heavy_cap] {vertex, chunk}: this step's chunks of frontier rows above kHeavyDegree
+    int heavy_cap = 0;
     bool started = false;
 };
 
 namespace drone {
 
 constexpr int kSerialDegree = 8;     // rows up to this many edges are walked by their own lane
+constexpr int kHeavyDegree = 4096;   // rows above this many edges are cut into chunks for the whole grid
+constexpr int kHeavyChunk = 2048;    // edges per chunk
 constexpr int kStepsPerLook = 4;     // relaxation steps launched between two reads of the changed word
 constexpr unsigned kFarBits = 0x4CBEBC20u;   // 1e8f, the reference's "not reached" (sssp.cu:33)
 
@@ -106,7 +112,7 @@ __device__ __forceinline__ void mp_relax_edge(unsigned now, int k, const int *__
 template <int KIND>
 __global__ void __launch_bounds__(256)
 mp_relax_kernel(const int *__restrict__ index, const int *__restrict__ dst, const float *__restrict__ len,
-                unsigned *value, int *active, int n, int step, int *counters) {
+                unsigned *value, int *active, int n, int step, int *counters, int2 *heavy, int heavy_cap) {
     const int lane = threadIdx.x & 31;
     const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
     const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -122,6 +128,13 @@ mp_relax_kernel(const int *__restrict__ index, const int *__restrict__ dst, cons
             if (end - beg <= kSerialDegree) {
                 for (int k = beg; k < end; ++k) mp_relax_edge<KIND>(now, k, dst, len, value, active, step, counters);
                 front = false;
+            } else if (end - beg > kHeavyDegree) {
+                const int n_chunks = (end - beg + kHeavyChunk - 1) / kHeavyChunk;
+                const int at = atomicAdd(counters + 6, n_chunks);
+                if (at + n_chunks <= heavy_cap) {          // always true: the capacity covers every row at once
+                    for (int c = 0; c < n_chunks; ++c) heavy[at + c] = make_int2((int)v, c);
+                    front = false;
+                }
             }
         }
         unsigned todo = __ballot_sync(0xffffffffu, front);
@@ -132,6 +145,24 @@ mp_relax_kernel(const int *__restrict__ index, const int *__restrict__ dst, cons
             const unsigned x = __shfl_sync(0xffffffffu, now, src);
             for (int k = b + lane; k < e; k += 32) mp_relax_edge<KIND>(x, k, dst, len, value, active, step, counters);
         }
+    }
+}
+
+// The chunks queued by mp_relax_kernel in the same step, one warp per chunk.
+template <int KIND>
+__global__ void __launch_bounds__(256)
+mp_relax_heavy_kernel(const int *__restrict__ index, const int *__restrict__ dst, const float *__restrict__ len,
+                      unsigned *value, int *active, int step, int *counters, const int2 *heavy, int heavy_cap) {
+    const int lane = threadIdx.x & 31;
+    const int count = min(counters[6], heavy_cap);
+    const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long i = warp0; i < count; i += n_warps) {
+        const int2 item = heavy[i];
+        const int b = index[item.x] + item.y * kHeavyChunk;
+        const int e = min(b + kHeavyChunk, index[item.x + 1]);
+        const unsigned x = value[item.x];
+        for (int k = b + lane; k < e; k += 32) mp_relax_edge<KIND>(x, k, dst, len, value, active, step, counters);
     }
 }
 
@@ -248,13 +279,21 @@ static int mp_local_run(drone_mp *p, cudaStream_t st) {
     while (changed) {
         DRONE_CUDA(cudaMemsetAsync(p->counters + 5, 0, sizeof(int), st));
         for (int i = 0; i < kStepsPerLook; ++i, ++step) {
-            if (p->kind == DRONE_MP_CC)
+            DRONE_CUDA(cudaMemsetAsync(p->counters + 6, 0, sizeof(int), st));
+            if (p->kind == DRONE_MP_CC) {
                 mp_relax_kernel<DRONE_MP_CC><<<grid, 256, 0, st>>>(p->index, p->dst, nullptr, p->value, p->active, n, step,
-                                                                   p->counters);
-            else
+                                                                   p->counters, p->heavy, p->heavy_cap);
+                DRONE_LAUNCH_CHECK("mp_relax_kernel");
+                mp_relax_heavy_kernel<DRONE_MP_CC><<<grid, 256, 0, st>>>(p->index, p->dst, nullptr, p->value, p->active, step,
+                                                                         p->counters, p->heavy, p->heavy_cap);
+            } else {
                 mp_relax_kernel<DRONE_MP_SSSP><<<grid, 256, 0, st>>>(p->index, p->dst, p->len, p->value, p->active, n, step,
-                                                                     p->counters);
-            DRONE_LAUNCH_CHECK("mp_relax_kernel");
+                                                                     p->counters, p->heavy, p->heavy_cap);
+                DRONE_LAUNCH_CHECK("mp_relax_kernel");
+                mp_relax_heavy_kernel<DRONE_MP_SSSP><<<grid, 256, 0, st>>>(p->index, p->dst, p->len, p->value, p->active, step,
+                                                                           p->counters, p->heavy, p->heavy_cap);
+            }
+            DRONE_LAUNCH_CHECK("mp_relax_heavy_kernel");
         }
         DRONE_CUDA(cudaMemcpyAsync(&changed, p->counters + 5, sizeof(int), cudaMemcpyDeviceToHost, st));
         DRONE_CUDA(cudaStreamSynchronize(st));
@@ -399,6 +438,10 @@ int drone_mp_create(drone_mp **out, int kind, int n_local, int nnz, const int *d
     if (err == cudaSuccess) err = cudaMalloc(&p->send, sizeof(uint2) * nb);
     if (err == cudaSuccess) err = cudaMalloc(&p->recv, sizeof(uint2) * nb);
     if (err == cudaSuccess) err = cudaMalloc(&p->counters, sizeof(int) * 8);
+    // every row above kHeavyDegree in the frontier at once: at most nnz / kHeavyChunk full chunks plus one partial
+    // chunk per such row, of which there are fewer than nnz / kHeavyDegree
+    p->heavy_cap = nnz / kHeavyChunk + nnz / kHeavyDegree + 16;
+    if (err == cudaSuccess) err = cudaMalloc(&p->heavy, sizeof(int2) * (size_t)p->heavy_cap);
     if (err != cudaSuccess) {
         drone_mp_destroy(p);
         return set_error(DRONE_E_CUDA, "drone_mp_create: %s", cudaGetErrorString(err));
@@ -413,6 +456,7 @@ int drone_mp_destroy(drone_mp *p) {
     cudaGetDevice(&prev);
     cudaSetDevice(p->device);
     cudaFree(p->value); cudaFree(p->active); cudaFree(p->ubm); cudaFree(p->send); cudaFree(p->recv); cudaFree(p->counters);
+    cudaFree(p->heavy);
     if (prev >= 0) cudaSetDevice(prev);
     delete p;
     return DRONE_OK;
