@@ -104,7 +104,14 @@ def _declare(lib):
         "drone_mp_device_arrays": (i, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "drone_ebv_partition": (i, [i, ll, vp, vp, i, i, vp, vp, vp, vp, vp]),
         "drone_presence_bits_host": (i, [i, i, vp, vp, vp, vp]),
+        "drone_text_ints_count": (i, [C.c_char_p, C.POINTER(ll), C.POINTER(ll)]),
+        "drone_text_ints_read": (i, [C.c_char_p, vp, ll, vp, ll, C.POINTER(ll), C.POINTER(ll)]),
+        "drone_text_edges_read": (i, [C.c_char_p, vp, vp, ll, C.POINTER(ll)]),
+        "drone_partition_write": (i, [C.c_char_p, i, i, vp, vp, vp, vp, vp, vp]),
+        "drone_partition_read_header": (i, [C.c_char_p, C.POINTER(i), C.POINTER(i), vp]),
+        "drone_partition_read": (i, [C.c_char_p, i, vp, vp, vp, vp, vp]),
         "drone_graph_build_host": (i, [i, i, vp, vp, vp, vp, vp, vp, C.POINTER(i)]),
+        "drone_graph_build_device": (i, [i, i, vp, vp, vp, vp, vp, vp, C.POINTER(i), vp]),
         "drone_route_tables_host": (i, [i, vp, vp, vp, vp, i, i, vp, vp, i, vp, vp, vp]),
         "drone_rmat_edges": (i, [i, ll, C.c_ulonglong, C.c_double, C.c_double, C.c_double, ll, vp, vp, vp]),
         "drone_rmat_edges_host": (i, [i, ll, C.c_ulonglong, C.c_double, C.c_double, C.c_double, ll, vp, vp]),

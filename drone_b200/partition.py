@@ -103,27 +103,96 @@ class Partition:
         return LocalGraph(self, p)
 
 
+def read_text_ints(path, with_lines=False):
+    """All integers of a text file (int32, file order); with_lines also returns the index of the first value of every
+    line that holds one, closed by the total.  Parsed by the library with all host threads."""
+    lib = _lib.lib()
+    nv, nl = C.c_longlong(0), C.c_longlong(0)
+    bpath = os.fsencode(path)
+    size = os.path.getsize(path) if os.path.exists(path) else 0     # a missing file is the library's error to report
+    cap = size // 2 + 1                           # an integer takes at least a digit and a separator
+    values = np.empty(cap, np.int32)              # untouched pages cost nothing
+    lines = np.empty(cap + 1, np.int64) if with_lines else None
+    check(lib.drone_text_ints_read(bpath, _vp(values), cap, _vp(lines) if with_lines else None, cap,
+                                   C.byref(nv), C.byref(nl)))
+    values = values[:nv.value]
+    return (values, lines[:nl.value + 1]) if with_lines else values
+
+
+def read_edge_list(path):
+    """(u, v) of a "u v" per line file such as G.<p>."""
+    size = os.path.getsize(path) if os.path.exists(path) else 0
+    cap = size // 4 + 1                           # an edge takes at least two digits and two separators
+    u, v = np.empty(cap, np.int32), np.empty(cap, np.int32)
+    n = C.c_longlong(0)
+    try:
+        check(_lib.lib().drone_text_edges_read(os.fsencode(path), _vp(u), _vp(v), cap, C.byref(n)))
+    except _lib.DroneError as e:
+        if "odd number" in str(e):
+            raise ValueError(str(e))
+        raise
+    return u[:n.value], v[:n.value]
+
+
 def read_partition_files(directory, n_vertices, n_parts):
     """Parse G./Master./Mirror. files (as cuda_gcn/src/common/parser.cu:59-131 does) back into a Partition."""
     part_u, part_v = [], []
     owner = np.full(n_vertices, -1, np.int32)
     replicas = np.zeros(n_vertices, np.int32)
     for p in range(n_parts):
-        e = np.loadtxt(os.path.join(directory, "G.%d" % p), dtype=np.int32, ndmin=2)
-        part_u.append(_i32(e[:, 0]) if e.size else np.zeros(0, np.int32))
-        part_v.append(_i32(e[:, 1]) if e.size else np.zeros(0, np.int32))
+        pu, pv = read_edge_list(os.path.join(directory, "G.%d" % p))
+        part_u.append(pu)
+        part_v.append(pv)
         seen = np.zeros(n_vertices, bool)
-        seen[part_u[-1]] = True
-        seen[part_v[-1]] = True
+        seen[pu] = True
+        seen[pv] = True
         replicas += seen
         owner[seen & (owner < 0)] = p                 # single-replica vertices: the part that has them
     for p in range(n_parts):
-        with open(os.path.join(directory, "Master.%d" % p)) as f:
-            for line in f:
-                t = line.split()
-                if t:
-                    owner[int(t[0])] = p
+        values, lines = read_text_ints(os.path.join(directory, "Master.%d" % p), with_lines=True)
+        owner[values[lines[:-1]]] = p                 # first integer of every line: a master vertex of part p
     return Partition(n_vertices, n_parts, part_u, part_v, owner, replicas)
+
+
+def save_partition(part, path):
+    """The whole partition in the library's binary format (drone_partition_write)."""
+    off = np.concatenate([[0], np.cumsum([len(x) for x in part.part_u])]).astype(np.int64)
+    if part._flat is not None:
+        u, v = part._flat
+    else:
+        u = _i32(np.concatenate(part.part_u)) if off[-1] else np.zeros(1, np.int32)
+        v = _i32(np.concatenate(part.part_v)) if off[-1] else np.zeros(1, np.int32)
+    check(_lib.lib().drone_partition_write(os.fsencode(path), part.n_vertices, part.n_parts, _vp(off), _vp(u), _vp(v),
+                                           _vp(_i32(part.owner)), _vp(_i32(part.replicas)), _vp(part.presence_bits())))
+
+
+def load_partition(path, part=None):
+    """A Partition from the binary format.  part = p reads the edges of part p only (the other parts' edge lists are
+    None; the presence words stand in for them), which is what one rank of a job needs."""
+    lib = _lib.lib()
+    nv, npart = C.c_int(0), C.c_int(0)
+    off = np.zeros(65, np.int64)
+    bpath = os.fsencode(path)
+    check(lib.drone_partition_read_header(bpath, C.byref(nv), C.byref(npart), _vp(off)))
+    n, P = nv.value, npart.value
+    off = off[:P + 1]
+    if part is not None and not 0 <= part < P:
+        raise _lib.DroneError(-1, "load_partition: part %d of %d" % (part, P))
+    e0, e1 = (0, int(off[P])) if part is None else (int(off[part]), int(off[part + 1]))
+    u = np.empty(max(e1 - e0, 1), np.int32)
+    v = np.empty(max(e1 - e0, 1), np.int32)
+    owner, replicas, bits = np.empty(n, np.int32), np.empty(n, np.int32), np.empty(n, np.uint64)
+    check(lib.drone_partition_read(bpath, -1 if part is None else int(part), _vp(u), _vp(v), _vp(owner), _vp(replicas),
+                                   _vp(bits)))
+    if part is None:
+        pu = [u[off[p]:off[p + 1]] for p in range(P)]
+        pv = [v[off[p]:off[p + 1]] for p in range(P)]
+        out = Partition(n, P, pu, pv, owner, replicas, present_bits=bits)
+        out._flat = (u, v)
+        return out
+    pu, pv = [None] * P, [None] * P
+    pu[part], pv[part] = u[:e1 - e0], v[:e1 - e0]
+    return Partition(n, P, pu, pv, owner, replicas, present_bits=bits)
 
 
 def ebv_partition(n_vertices, u, v, n_parts, keep_self_loops=True):
@@ -181,6 +250,30 @@ class LocalGraph:
     def local_degrees(self, global_in_degree, global_out_degree):
         """Global degrees indexed by local id (setDegree, cuda_gcn/src/common/parser.cu:25-35)."""
         return _i32(global_in_degree[self.l2g]), _i32(global_out_degree[self.l2g])
+
+
+def device_local_graph(u, v, global_v, stream=None):
+    """Local numbering and CSR by source of one part from its edge list on the device (int32 CUDA tensors).
+    Returns (n_local, g2l, l2g, index, dst) as CUDA tensors; identical to what LocalGraph builds on the host."""
+    import torch
+    from .plan import _stream_ptr
+    if not (u.is_cuda and v.is_cuda and u.dtype == torch.int32 and v.dtype == torch.int32 and u.is_contiguous() and
+            v.is_contiguous() and u.numel() == v.numel()):
+        raise ValueError("u and v must be contiguous int32 CUDA tensors of one length")
+    e = u.numel()
+    cap = min(int(global_v), 2 * e) + 1
+    dev = u.device
+    g2l = torch.empty(int(global_v), dtype=torch.int32, device=dev)
+    l2g = torch.empty(cap, dtype=torch.int32, device=dev)
+    index = torch.empty(cap + 1, dtype=torch.int32, device=dev)
+    dst = torch.empty(max(e, 1), dtype=torch.int32, device=dev)
+    n = C.c_int(0)
+    with torch.cuda.device(dev):
+        check(_lib.lib().drone_graph_build_device(int(global_v), e, C.c_void_p(u.data_ptr()), C.c_void_p(v.data_ptr()),
+                                                  C.c_void_p(g2l.data_ptr()), C.c_void_p(l2g.data_ptr()),
+                                                  C.c_void_p(index.data_ptr()), C.c_void_p(dst.data_ptr()), C.byref(n),
+                                                  _stream_ptr(stream)))
+    return n.value, g2l, l2g[:n.value], index[:n.value + 1], dst[:e]
 
 
 class ExchangePlan:

@@ -423,6 +423,36 @@ int drone_presence_bits_host(int n_vertices, int n_parts, const int *h_u, const 
                              const long long *h_part_offset, unsigned long long *h_bits);
 
 /*
+ * Loading from disk (host code).
+ *
+ * drone_text_ints_count / drone_text_ints_read: all integers of a text file in file order, and for every line that
+ * holds at least one integer the index of its first value (line_start[n_lines] = n_values closes the list; pass
+ * NULL when lines do not matter).  Reads the three formats of a partition directory — G.<p> ("u v"), Master.<p>
+ * ("vertex worker worker ..."), Mirror.<p> ("vertex worker") — with all host threads; replaces the fscanf / getline
+ * loops of Parser::parseGraph, cuda_gcn/src/common/parser.cu:72-131, and the line-by-line reader of the Go loader,
+ * DRONE/src/graph/cuda_graph.go:32-60.  Anything but digits, signs and white space is an error (byte offset in the
+ * message).  Call count first, allocate, then read; or read straight away into buffers of file size / 2 + 1 entries,
+ * which always suffice (an integer takes at least one digit and one separator), and take the counts it returns.
+ *
+ * drone_partition_write / _read_header / _read: one binary file for a whole partition: header, part offsets, owner,
+ * replicas, presence words (see drone_presence_bits_host), then u and v of all parts, parts one after the other in
+ * G.<p> order.  drone_partition_read with part >= 0 reads that part's edges only (part = -1: all edges); any output
+ * pointer may be NULL.  part_offset needs n_parts + 1 entries (at most 65).  No counterpart in the reference, whose
+ * workers each parse their text files at every start.
+ */
+int drone_text_ints_count(const char *path, long long *n_values, long long *n_lines);
+int drone_text_ints_read(const char *path, int *values, long long cap_values, long long *line_start, long long cap_lines,
+                         long long *n_values, long long *n_lines);
+/* The integers of a "u v" per line file dealt into two arrays (each needs room for file size / 4 + 1 entries). */
+int drone_text_edges_read(const char *path, int *u, int *v, long long cap_edges, long long *n_edges);
+int drone_partition_write(const char *path, int n_vertices, int n_parts, const long long *part_offset,
+                          const int *u, const int *v, const int *owner, const int *replicas,
+                          const unsigned long long *present_bits);
+int drone_partition_read_header(const char *path, int *n_vertices, int *n_parts, long long *part_offset);
+int drone_partition_read(const char *path, int part, int *u, int *v, int *owner, int *replicas,
+                         unsigned long long *present_bits);
+
+/*
  * One rank's local graph from the edge list of its G.<p> file (host arrays in,
  * host arrays out): local ids in first-seen order, CSR by source vertex with
  * destinations in edge-list order.  h_g2l[global_v] gets -1 for absent
@@ -432,6 +462,16 @@ int drone_presence_bits_host(int n_vertices, int n_parts, const int *h_u, const 
  */
 int drone_graph_build_host(int global_v, int n_edges, const int *h_u, const int *h_v,
                            int *h_g2l, int *h_l2g, int *h_index, int *h_dst, int *n_local_out);
+
+/*
+ * The same local graph built on the device from device arrays d_u / d_v (n_edges < 2^30): d_g2l[global_v],
+ * d_l2g and d_index with room for min(global_v, 2*n_edges) (+1) entries, d_dst[n_edges]; *n_local_out is written on
+ * the host.  Output identical to drone_graph_build_host; the call synchronises `stream` and allocates scratch of
+ * about 12 bytes per vertex id and 12 bytes per edge.  Replaces the serial host loops of build_graph,
+ * cuda_gcn/src/cuda/graph.cu:54-103.
+ */
+int drone_graph_build_device(int global_v, int n_edges, const int *d_u, const int *d_v,
+                             int *d_g2l, int *d_l2g, int *d_index, int *d_dst, int *n_local_out, void *stream);
 
 /*
  * Routing tables by local id from the rows of Master.<p> (master_vertex[i] has

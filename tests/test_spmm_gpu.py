@@ -220,3 +220,26 @@ def test_empty_graph(cuda_device):
     out = torch.full((10, 5), 3.0, device=cuda_device)
     plan.spmm(db.OP_A, torch.ones((10, 5), device=cuda_device), out=out)
     assert (out == 0).all()
+
+
+@pytest.mark.parametrize("scale,parts", [(10, 1), (12, 3), (14, 8)])
+def test_device_graph_build_matches_the_host_builder(cuda_device, scale, parts):
+    """drone_graph_build_device against drone_graph_build_host: numbering, row pointers and destinations, bit for bit."""
+    from drone_b200 import partition as pt
+    n, u, v = gg.rmat_graph(scale, 8, seed=scale, device="cpu", self_loops="add")
+    part = pt.ebv_partition(n, u.numpy(), v.numpy(), parts)
+    for p in range(parts):
+        host = part.local_graph(p)
+        du = torch.as_tensor(part.part_u[p].copy(), device=cuda_device)
+        dv = torch.as_tensor(part.part_v[p].copy(), device=cuda_device)
+        n_local, g2l, l2g, index, dst = pt.device_local_graph(du, dv, n)
+        assert n_local == host.n_local
+        assert np.array_equal(g2l.cpu().numpy(), host.g2l)
+        assert np.array_equal(l2g.cpu().numpy(), host.l2g)
+        assert np.array_equal(index.cpu().numpy(), host.index)
+        assert np.array_equal(dst.cpu().numpy(), host.dst)
+    empty = torch.zeros(0, dtype=torch.int32, device=cuda_device)
+    assert pt.device_local_graph(empty, empty, 16)[0] == 0
+    bad = torch.tensor([3, 99], dtype=torch.int32, device=cuda_device)
+    with pytest.raises(db.DroneError, match="outside"):
+        pt.device_local_graph(bad, bad, 16)
