@@ -33,7 +33,8 @@ def build_ref(force=False):
     if not os.path.isdir(os.path.join(REFERENCE_ROOT, "cuda_gcn", "src")):
         return _REF_SO if os.path.exists(_REF_SO) else None
     deps = [os.path.join(_HERE, f) for f in ("ref_driver.cu", "Makefile", "ref_shim/mpi.h", "ref_shim/utils_override.h")]
-    if force or not os.path.exists(_REF_SO) or any(os.path.getmtime(d) > os.path.getmtime(_REF_SO) for d in deps):
+    if force or not os.path.exists(_REF_SO) or not os.path.exists(os.path.join(_HERE, "_ref", "libref_drone_jobs.so")) \
+            or any(os.path.getmtime(d) > os.path.getmtime(_REF_SO) for d in deps):
         subprocess.run(["make", "-C", _HERE, "ref", "REFERENCE=" + REFERENCE_ROOT] + (["-B"] if force else []),
                        check=True, stdout=subprocess.DEVNULL)
     return _REF_SO
@@ -41,6 +42,15 @@ def build_ref(force=False):
 
 def reference_available():
     return os.path.exists(_REF_SO)
+
+
+_REF_JOBS_SO = os.path.join(_HERE, "_ref", "libref_drone_jobs.so")
+
+
+def reference_jobs_library():
+    """Path of the reference's own GPU jobs (build_graph, addMasterRoute, addMirrorRoute, loadOutDegree, PR_*, CC_*,
+    SSSP_* compiled from DRONE/src/cuda by `make ref`), or None when it was not built."""
+    return _REF_JOBS_SO if os.path.exists(_REF_JOBS_SO) else None
 
 
 def reference_graphsum(global_v, u, v, global_in_degree, global_out_degree, x, out_grad):

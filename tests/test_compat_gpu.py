@@ -59,7 +59,11 @@ class Response(C.Structure):   # DRONE/src/cuda/algorithm/common.h:23-27
 
 def pr_lib():
     db.lib()
-    lib = C.CDLL(os.path.join(LIBDIR, "libdrone_pr_compat.so"))
+    return bind_jobs(C.CDLL(os.path.join(LIBDIR, "libdrone_pr_compat.so")))
+
+
+def bind_jobs(lib):
+    """Prototypes of the cgo-facing interface (DRONE/src/cuda/graph.h:45-52, algorithm/pr.h, cc.h, sssp.h)."""
     ip = C.POINTER(C.c_int)
     lib.build_graph.restype = C.POINTER(Graph)
     lib.build_graph.argtypes = [C.c_int, C.c_int, ip, ip, C.c_int, C.c_int, C.POINTER(Comm)]
