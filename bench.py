@@ -360,6 +360,7 @@ def run_ours(args, cfg):
             line["minprop"] = minprop_timing(device)
         except Exception as e:
             line["minprop"] = {"error": repr(e)}
+        line["jobs_head_to_head"] = jobs_head_to_head()
 
     if not args.no_cpu_baseline:
         from oracle import oracle
@@ -489,6 +490,23 @@ def one_part_pagerank(device, n, index, dst, out_degree, iterations):
            "edges_per_s": nnz / (ms_it * 1e-3), "algorithmic_GBps": b_alg / (ms_it * 1e-3) / 1e9}
     pr1.close()
     return res
+
+
+def jobs_head_to_head(timeout_s=240):
+    """pr_cuda supersteps and one sssp_cuda run through the cgo-facing C interface, once with the reference's own
+    sources (oracle/_ref/libref_drone_jobs.so) and once with this repository's drop-in, same driver, same R-MAT-20
+    graph, one worker (baseline/jobs_driver.py; each in a child process)."""
+    import subprocess
+    out = {}
+    for which in ("reference", "dropin"):
+        try:
+            r = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "jobs_driver.py"), "--lib", which],
+                               capture_output=True, text=True, timeout=timeout_s)
+            lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+            out[which] = json.loads(lines[-1]) if lines else {"error": "exit %d: %s" % (r.returncode, r.stderr[-300:])}
+        except Exception as e:
+            out[which] = {"error": repr(e)}
+    return out
 
 
 def minprop_timing(device):
