@@ -78,6 +78,42 @@ def reference_graphsum(global_v, u, v, global_in_degree, global_out_degree, x, o
     return l2g[:n].copy(), out_data[:n].copy(), in_grad[:n].copy(), values[:len(u)].copy()
 
 
+def reference_graphsum_worker(part, rank, global_in_degree, global_out_degree, x, out_grad):
+    """One worker of the REFERENCE's CUDAGraphSum over a partition (one process per GPU; all workers must call this
+    at the same time, with DRONE_REF_ID_FILE / DRONE_REF_RANK set for the MPI_Bcast stand-in).  Returns
+    (l2g, out_data, in_grad) by the reference's local id, after its own mirror/master exchange."""
+    ref = C.CDLL(_REF_SO)
+    u, v = _i32(part.part_u[rank]), _i32(part.part_v[rank])
+    mv, num, wk = part.master_rows(rank)
+    mr, ow = part.mirror_rows(rank)
+
+    def arr(a):
+        a = _i32(a)
+        return a if a.size else np.zeros(1, np.int32)
+
+    mv, num, wk, mr, ow = arr(mv), arr(num), arr(wk), arr(mr), arr(ow)
+    sizes = [len(part.master_rows(rank)[0]), len(part.master_rows(rank)[2]), len(part.mirror_rows(rank)[0])]
+    ind, outd = _i32(global_in_degree), _i32(global_out_degree)
+    x, out_grad = _f32(x), _f32(out_grad)
+    dim = x.shape[1]
+    n_v = part.n_vertices
+    cap = min(n_v, 2 * len(u)) + 1
+    out_data = np.zeros((cap, dim), np.float32)
+    in_grad = np.zeros((cap, dim), np.float32)
+    values = np.zeros(max(len(u), 1), np.float32)
+    l2g = np.zeros(cap, np.int32)
+    n = C.c_int(0)
+    rc = ref.ref_graphsum_run_worker(int(n_v), len(u), _p(u, C.c_int), _p(v, C.c_int), int(rank), int(part.n_parts),
+                                     _p(mv, C.c_int), _p(num, C.c_int), _p(wk, C.c_int), sizes[0], sizes[1],
+                                     _p(mr, C.c_int), _p(ow, C.c_int), sizes[2], _p(ind, C.c_int), _p(outd, C.c_int), dim,
+                                     _p(x, C.c_float), _p(out_grad, C.c_float), _p(out_data, C.c_float),
+                                     _p(in_grad, C.c_float), _p(values, C.c_float), _p(l2g, C.c_int), C.byref(n))
+    if rc != 0:
+        raise RuntimeError("reference GraphSum run failed (%d)" % rc)
+    n = n.value
+    return l2g[:n].copy(), out_data[:n].copy(), in_grad[:n].copy()
+
+
 _lib = None
 
 

@@ -8,15 +8,19 @@
 
 #include "cuda_module.cuh"
 
-extern "C" int ref_graphsum_run(int global_v, int n_edges, int *u, int *v, const int *global_in_degree,
-                                const int *global_out_degree, int dim, const float *h_in_data,
-                                const float *h_out_grad, float *h_out_data, float *h_in_grad, float *h_values,
-                                int *h_local2global, int *n_local_out) {
+// One worker of worker_num (one process per GPU; several workers need the file-based MPI_Bcast stand-in of
+// ref_shim/mpi.h).  The Master.<p> / Mirror.<p> rows are passed as the reference's parser passes them
+// (cuda_gcn/src/common/parser.cu:86-131).
+extern "C" int ref_graphsum_run_worker(int global_v, int n_edges, int *u, int *v, int worker_id, int worker_num,
+                                       int *master_vertex, int *mirror_number, int *mirror_workers, int master_size,
+                                       int mirror_worker_size, int *mirror_vertex, int *master_worker, int mirror_size,
+                                       const int *global_in_degree, const int *global_out_degree, int dim,
+                                       const float *h_in_data, const float *h_out_grad, float *h_out_data,
+                                       float *h_in_grad, float *h_values, int *h_local2global, int *n_local_out) {
     Comm *comm = new Comm();
-    Graph *g = build_graph(global_v, n_edges, u, v, 0, 1, comm);
-    int none = 0;
-    addMasterRoute(g, &none, &none, &none, 0, 0);
-    addMirrorRoute(g, &none, &none, 0);
+    Graph *g = build_graph(global_v, n_edges, u, v, worker_id, worker_num, comm);
+    addMasterRoute(g, master_vertex, mirror_number, mirror_workers, master_size, mirror_worker_size);
+    addMirrorRoute(g, mirror_vertex, master_worker, mirror_size);
     const int n = getLocalVertexSize(g);
     *n_local_out = n;
     std::vector<int> l2g(n), ind(n), outd(n);
@@ -36,7 +40,7 @@ extern "C" int ref_graphsum_run(int global_v, int n_edges, int *u, int *v, const
     CUDAVariable *out = new CUDAVariable(n * dim, true, false);
     Buffer *buffer = new Buffer();
     buffer->maxDim = dim;
-    buffer_init(buffer, g, 0, 1);
+    buffer_init(buffer, g, worker_id, worker_num);
     // local rows are in the reference's first-seen order; the caller passes operands by GLOBAL id
     std::vector<float> tmp((size_t)n * dim);
     for (int i = 0; i < n; ++i)
@@ -46,7 +50,7 @@ extern "C" int ref_graphsum_run(int global_v, int n_edges, int *u, int *v, const
         for (int j = 0; j < dim; ++j) tmp[(size_t)i * dim + j] = h_out_grad[(size_t)l2g[i] * dim + j];
     cudaMemcpy(out->grad, tmp.data(), sizeof(float) * tmp.size(), cudaMemcpyHostToDevice);
 
-    CUDAGraphSum *layer = new CUDAGraphSum(in, out, g, comm, degree, buffer, dim, 0, 1, "graphSum_ref", 0);
+    CUDAGraphSum *layer = new CUDAGraphSum(in, out, g, comm, degree, buffer, dim, worker_id, worker_num, "graphSum_ref", 0);
     // forward and backward each end in an exchange that, with one worker, launches over zero rows; the launch errors
     // are cleared here and the reference's exit() on them is caught (see ref_shim/utils_override.h)
     try {
@@ -67,4 +71,14 @@ extern "C" int ref_graphsum_run(int global_v, int n_edges, int *u, int *v, const
     // the reference's destructor deletes an uninitialised pointer when batch_type != SEMI_BATCH: the layer is leaked
     cudaGetLastError();
     return 0;
+}
+
+extern "C" int ref_graphsum_run(int global_v, int n_edges, int *u, int *v, const int *global_in_degree,
+                                const int *global_out_degree, int dim, const float *h_in_data,
+                                const float *h_out_grad, float *h_out_data, float *h_in_grad, float *h_values,
+                                int *h_local2global, int *n_local_out) {
+    int none = 0;
+    return ref_graphsum_run_worker(global_v, n_edges, u, v, 0, 1, &none, &none, &none, 0, 0, &none, &none, 0,
+                                   global_in_degree, global_out_degree, dim, h_in_data, h_out_grad, h_out_data, h_in_grad,
+                                   h_values, h_local2global, n_local_out);
 }
