@@ -3,9 +3,12 @@
  * (minimum propagation along out-edges over an EBV-partitioned graph).
  *
  * TEST INFRASTRUCTURE ONLY (same rules as drone_oracle.c).
- * Parity status: the reference holds no golden labels or distances for these jobs
- * ("parity unpinned"); the functions below restate its procedure and are cross-checked
- * against plain single-graph fixed points in tests/test_minprop_oracle.py.
+ * Parity status: the reference holds no golden labels or distances for these jobs.  The
+ * restatement is pinned by running the reference's own sources (compiled into oracle/_ref) on
+ * a GPU box: distances, labels (one worker, ids in first-seen order) and the Response sizes of
+ * every superstep are identical on one and two workers (tests/test_reference_jobs_gpu.py).  On
+ * the CPU it is cross-checked against plain single-graph fixed points
+ * (tests/test_minprop_oracle.py).
  *
  * What is restated:
  *   local run      — DRONE/src/cuda/algorithm/cc.cu:9-46 (cc_init, cc_exec) and :320-345 / :398-420 (the loops of

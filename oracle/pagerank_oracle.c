@@ -3,11 +3,14 @@
  * EBV-partitioned graph.
  *
  * TEST INFRASTRUCTURE ONLY (same rules as drone_oracle.c).
- * Parity status: the reference holds no golden PageRank values
- * ("parity unpinned"); the Go job cannot be built here (no Go toolchain, its
- * gRPC/protobuf dependencies are neither vendored nor version-pinned), so the
- * functions below restate its arithmetic and are cross-checked against each
- * other and against a dense power iteration in tests/test_oracle.py.
+ * Parity status: the reference holds no golden PageRank values.  The GPU job
+ * is pinned by running the reference's own sources (compiled into oracle/_ref)
+ * on a GPU box next to the library, on one and two workers
+ * (tests/test_reference_jobs_gpu.py: values within 5e-4, float atomics in
+ * another order).  The Go job cannot be built here (no Go toolchain, its
+ * gRPC/protobuf dependencies are neither vendored nor version-pinned): its
+ * restatement below stays unpinned and is cross-checked against the other
+ * procedures and against a dense power iteration in tests/test_oracle.py.
  *
  * Three procedures:
  *   oracle_pr_drone_cpu      — the CPU job "pr":   DRONE/src/algorithm/PageRank.go:22-125,
