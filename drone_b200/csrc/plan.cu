@@ -607,53 +607,58 @@ int drone_plan_set_row_classes(drone_plan *p, const int *d_row_class, int n_clas
     DRONE_REQUIRE(n_classes >= 1 && n_classes <= kMaxRowClasses, "drone_plan_set_row_classes: n_classes=%d outside 1..%d",
                   n_classes, kMaxRowClasses);
     DRONE_REQUIRE(n_classes == 1 || d_row_class != nullptr, "drone_plan_set_row_classes: d_row_class is NULL");
+    struct Restore {      // the caller's device comes back on every way out
+        int prev = -1, mine = -1;
+        ~Restore() { if (prev >= 0 && prev != mine) cudaSetDevice(prev); }
+    } dev;
+    struct Temp {         // scratch of this call
+        int *keys_out = nullptr, *rows = nullptr, *counts = nullptr, *order = nullptr;
+        void *sort = nullptr;
+        ~Temp() { cudaFree(keys_out); cudaFree(rows); cudaFree(counts); cudaFree(order); cudaFree(sort); }
+    } t;
     cudaStream_t st = (cudaStream_t)stream;
-    int prev = -1;
-    DRONE_CUDA(cudaGetDevice(&prev));
-    if (prev != p->device) DRONE_CUDA(cudaSetDevice(p->device));
+    DRONE_CUDA(cudaGetDevice(&dev.prev));
+    dev.mine = p->device;
+    if (dev.prev != p->device) DRONE_CUDA(cudaSetDevice(p->device));
     const int n = p->n_rows;
+    int h_counts[kMaxRowClasses] = {0};
+    const bool classes = n_classes > 1 && n > 0;
+    if (classes) {        // everything that can fail on the input happens before the plan is touched
+        DRONE_CUDA(cudaMalloc(&t.keys_out, sizeof(int) * (size_t)n));
+        DRONE_CUDA(cudaMalloc(&t.rows, sizeof(int) * (size_t)n));
+        DRONE_CUDA(cudaMalloc(&t.order, sizeof(int) * (size_t)n));
+        DRONE_CUDA(cudaMalloc(&t.counts, sizeof(int) * (kMaxRowClasses + 1)));
+        DRONE_CUDA(cudaMemsetAsync(t.counts, 0, sizeof(int) * (kMaxRowClasses + 1), st));
+        check_classes_kernel<<<grid_for(n), 256, 0, st>>>(d_row_class, n, n_classes, t.counts + kMaxRowClasses);
+        DRONE_LAUNCH_CHECK("check_classes_kernel");
+        int bad = 0;
+        DRONE_CUDA(cudaMemcpyAsync(&bad, t.counts + kMaxRowClasses, sizeof(int), cudaMemcpyDeviceToHost, st));
+        DRONE_CUDA(cudaStreamSynchronize(st));
+        if (bad) return set_error(DRONE_E_INVALID, "drone_plan_set_row_classes: a row has a class outside 0..%d", n_classes - 1);
+        histogram_kernel<<<grid_for(n), 256, 0, st>>>(d_row_class, n, t.counts);
+        DRONE_LAUNCH_CHECK("histogram_kernel");
+        iota_kernel<<<grid_for(n), 256, 0, st>>>(t.rows, n);
+        DRONE_LAUNCH_CHECK("iota_kernel");
+        int end_bit = 1;
+        while ((1 << end_bit) < n_classes) ++end_bit;
+        size_t tmp_bytes = 0;
+        // stable: rows stay ascending inside a class
+        DRONE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, d_row_class, t.keys_out, t.rows, t.order, n, 0, end_bit, st));
+        DRONE_CUDA(cudaMalloc(&t.sort, tmp_bytes > 0 ? tmp_bytes : 1));
+        DRONE_CUDA(cub::DeviceRadixSort::SortPairs(t.sort, tmp_bytes, d_row_class, t.keys_out, t.rows, t.order, n, 0, end_bit, st));
+        count_launch();
+        DRONE_CUDA(cudaMemcpyAsync(h_counts, t.counts, sizeof(int) * kMaxRowClasses, cudaMemcpyDeviceToHost, st));
+        DRONE_CUDA(cudaStreamSynchronize(st));
+    }
     DRONE_CUDA(cudaDeviceSynchronize());   // calls that still read the lists must have finished
     cudaFree(p->row_order);
     p->row_order = nullptr;
     p->n_classes = 1;
     p->class_start[0] = 0;
     p->class_start[1] = n;
-    if (n_classes > 1 && n > 0) {
-        int *keys_out = nullptr, *rows = nullptr, *counts = nullptr;
-        DRONE_CUDA(cudaMalloc(&keys_out, sizeof(int) * (size_t)n));
-        DRONE_CUDA(cudaMalloc(&rows, sizeof(int) * (size_t)n));
-        DRONE_CUDA(cudaMalloc(&p->row_order, sizeof(int) * (size_t)n));
-        DRONE_CUDA(cudaMalloc(&counts, sizeof(int) * (kMaxRowClasses + 1)));
-        DRONE_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * (kMaxRowClasses + 1), st));
-        check_classes_kernel<<<grid_for(n), 256, 0, st>>>(d_row_class, n, n_classes, counts + kMaxRowClasses);
-        DRONE_LAUNCH_CHECK("check_classes_kernel");
-        int bad = 0;
-        DRONE_CUDA(cudaMemcpyAsync(&bad, counts + kMaxRowClasses, sizeof(int), cudaMemcpyDeviceToHost, st));
-        DRONE_CUDA(cudaStreamSynchronize(st));
-        if (bad) {
-            cudaFree(keys_out); cudaFree(rows); cudaFree(counts);
-            cudaFree(p->row_order);
-            p->row_order = nullptr;
-            if (prev != p->device) cudaSetDevice(prev);
-            return set_error(DRONE_E_INVALID, "drone_plan_set_row_classes: a row has a class outside 0..%d", n_classes - 1);
-        }
-        histogram_kernel<<<grid_for(n), 256, 0, st>>>(d_row_class, n, counts);
-        DRONE_LAUNCH_CHECK("histogram_kernel");
-        iota_kernel<<<grid_for(n), 256, 0, st>>>(rows, n);
-        DRONE_LAUNCH_CHECK("iota_kernel");
-        int end_bit = 1;
-        while ((1 << end_bit) < n_classes) ++end_bit;
-        size_t tmp_bytes = 0;
-        void *tmp = nullptr;
-        // stable: rows stay ascending inside a class
-        DRONE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, d_row_class, keys_out, rows, p->row_order, n, 0, end_bit, st));
-        DRONE_CUDA(cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1));
-        DRONE_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tmp_bytes, d_row_class, keys_out, rows, p->row_order, n, 0, end_bit, st));
-        count_launch();
-        int h_counts[kMaxRowClasses];
-        DRONE_CUDA(cudaMemcpyAsync(h_counts, counts, sizeof(int) * kMaxRowClasses, cudaMemcpyDeviceToHost, st));
-        DRONE_CUDA(cudaStreamSynchronize(st));
-        cudaFree(tmp); cudaFree(keys_out); cudaFree(rows); cudaFree(counts);
+    if (classes) {
+        p->row_order = t.order;
+        t.order = nullptr;
         p->n_classes = n_classes;
         for (int c = 0; c < n_classes; ++c) p->class_start[c + 1] = p->class_start[c] + h_counts[c];
     }
@@ -664,7 +669,6 @@ int drone_plan_set_row_classes(drone_plan *p, const int *d_row_class, int n_clas
         free_lists(s);
         rc = build_work_lists(p, s, st);
     }
-    if (prev != p->device) cudaSetDevice(prev);
     return rc;
 }
 

@@ -93,6 +93,16 @@ def test_row_classes_check_arguments(cuda_device):
         plan.set_row_classes(bad, 17)
     want = plan.spmm(db.OP_AT, x)                           # the failed calls left the plan usable
     assert torch.isfinite(want).all()
+    good = (torch.arange(n, device=cuda_device) % 2).to(torch.int32)
+    plan.set_row_classes(good, 2)
+    with pytest.raises(db.DroneError, match="class outside"):
+        plan.set_row_classes(bad, 3)                        # rejected before anything changes: still two classes
+    out = torch.zeros_like(want)
+    plan.spmm(db.OP_AT, x, out=out, row_class=0)
+    plan.spmm(db.OP_AT, x, out=out, row_class=1)
+    assert torch.equal(out, want)
+    with pytest.raises(db.DroneError, match="row_class"):
+        plan.spmm(db.OP_AT, x, out=out, row_class=2)
 
 
 def test_exchange_is_repeatable_and_checks_arguments(cuda_device, oracle):
