@@ -383,11 +383,13 @@ static int tuning_int(const char *name, int dflt) {
     return (v && *v) ? atoi(v) : dflt;
 }
 
-// Blocks per launch when DRONE_CHUNK_BLOCKS_PER_SM asks for a resident grid of the chunk kernel (each warp then
-// strides over the chunk list); 0, the default, keeps one warp per chunk.  Measured: a resident grid is 5 % faster on
-// R-MAT-20 at F = 64 and 10-15 % slower on R-MAT-26 at F = 32 and on the Reddit-shaped graph, so it is opt-in.
+// Grid of the chunk kernel: 16 blocks per SM, every warp striding over the chunk list (DRONE_CHUNK_BLOCKS_PER_SM
+// overrides; 0 launches one warp per chunk).  Measured against one warp per chunk, with the short-row kernel running
+// beside it on the side stream: R-MAT-20 sym F = 64 0.688 -> 0.618 ms, R-MAT-22 F = 32 1.26 -> 1.09 ms, R-MAT-26 F = 32
+// 25.7 -> 23.3 ms, GCN epoch on the Reddit-shaped graph 15.2 -> 15.0 ms.  8 per SM is slightly better on the R-MAT
+// graphs (0.609 / 1.07 ms) and worse on the Reddit-shaped one (15.7 ms); 32 per SM loses again (1.11 ms on R-MAT-22).
 static int resident_blocks() {
-    const int per_sm = tuning_int("DRONE_CHUNK_BLOCKS_PER_SM", 0);
+    const int per_sm = tuning_int("DRONE_CHUNK_BLOCKS_PER_SM", 16);
     if (per_sm <= 0) return 0;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
