@@ -376,9 +376,14 @@ static int class_major_scan(const drone_plan *p, const int *cnt, int *off, int *
 static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
     const int n = p->n_rows;
     const int K = p->n_classes;
-    int *buf = nullptr;  // 10 arrays of n+1 ints: counts x4, offsets x4, scratch x2
+    struct Temp {        // freed on every way out
+        int *buf = nullptr;
+        void *scan = nullptr;
+        ~Temp() { cudaFree(buf); cudaFree(scan); }
+    } t;
     const size_t stride = (size_t)(n + 1);
-    DRONE_CUDA(cudaMalloc(&buf, sizeof(int) * stride * 10));
+    DRONE_CUDA(cudaMalloc(&t.buf, sizeof(int) * stride * 10));  // 10 arrays of n+1 ints: counts x4, offsets x4, scratch x2
+    int *buf = t.buf;
     int *cnt[4] = {buf, buf + stride, buf + 2 * stride, buf + 3 * stride};
     int *off[4] = {buf + 4 * stride, buf + 5 * stride, buf + 6 * stride, buf + 7 * stride};
     int *scratch = buf + 8 * stride;
@@ -386,9 +391,9 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
                                                         cnt[0], cnt[1], cnt[2], cnt[3]);
     DRONE_LAUNCH_CHECK("count_chunks_kernel");
     size_t tmp_bytes = 0;
-    void *tmp = nullptr;
     DRONE_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, cnt[0], off[0], n + 1, st));
-    DRONE_CUDA(cudaMalloc(&tmp, tmp_bytes > 0 ? tmp_bytes : 1));
+    DRONE_CUDA(cudaMalloc(&t.scan, tmp_bytes > 0 ? tmp_bytes : 1));
+    void *tmp = t.scan;
     int rc;
     int slot_start[kMaxRowClasses + 1], long_start[kMaxRowClasses + 1];
     if ((rc = class_major_scan(p, cnt[0], off[0], scratch, tmp, tmp_bytes, s.chunk_start, st))) return rc;
@@ -475,8 +480,6 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
                                        cudaMemcpyHostToDevice, st));
         DRONE_CUDA(cudaStreamSynchronize(st));
     }
-    cudaFree(tmp);
-    cudaFree(buf);
     s.ready = true;
     return DRONE_OK;
 }
