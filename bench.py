@@ -622,7 +622,7 @@ def run_ours_multi(args, cfg):
 
     # rank 0 builds and partitions the graph; every rank receives its own edges and the global tables
     t_setup = time.perf_counter()
-    meta = torch.zeros(2 + world + 1, dtype=torch.int64, device=device)
+    part, extra = None, ()
     if rank == 0:
         _, u, v = gg.rmat_graph(cfg["scale"], cfg["edge_factor"], seed=cfg["seed"], device=device,
                                 symmetrise=cfg["symmetrise"], self_loops="add")
@@ -631,40 +631,10 @@ def run_ours_multi(args, cfg):
         del u, v
         part = pt.ebv_partition(n, uh, vh, world, keep_self_loops=True)
         del uh, vh
-        sizes = [len(x) for x in part.part_u]
-        meta[0], meta[1] = sum(sizes), n
-        meta[2:2 + world + 1] = torch.tensor(np.concatenate([[0], np.cumsum(sizes)]))
-    dist.broadcast(meta, 0)
-    total_e = int(meta[0])
-    offs = meta[2:].cpu().numpy()
-    if rank == 0:
-        owner = torch.as_tensor(part.owner, device=device)
-        reps = torch.as_tensor(part.replicas, device=device)
-        bits = torch.as_tensor(part.presence_bits().view(np.int64), device=device)
-    else:
-        owner = torch.empty(n, dtype=torch.int32, device=device)
-        reps = torch.empty(n, dtype=torch.int32, device=device)
-        bits = torch.empty(n, dtype=torch.int64, device=device)
-        in_deg = torch.empty(n, dtype=torch.int32, device=device)
-        out_deg = torch.empty(n, dtype=torch.int32, device=device)
-    for t in (owner, reps, bits, in_deg, out_deg):
-        dist.broadcast(t, 0)
-    if rank == 0:
-        for p in range(1, world):
-            for arr in (part.part_u[p], part.part_v[p]):
-                dist.send(torch.as_tensor(arr, device=device), dst=p)
-    else:
-        mine = []
-        for _ in range(2):
-            t = torch.empty(int(offs[rank + 1] - offs[rank]), dtype=torch.int32, device=device)
-            dist.recv(t, src=0)
-            mine.append(t.cpu().numpy())
-        pu, pv = [None] * world, [None] * world
-        pu[rank], pv[rank] = mine
-        part = pt.Partition(n, world, pu, pv, owner.cpu().numpy(), reps.cpu().numpy(),
-                            present_bits=bits.cpu().numpy().view(np.uint64))
-    del owner, reps, bits
-    graph = gs.DeviceGraph(part.local_graph(rank), in_deg.cpu().numpy(), out_deg.cpu().numpy(), device, max_features=f)
+        extra = (in_deg.cpu().numpy(), out_deg.cpu().numpy())
+        del in_deg, out_deg
+    part, (in_deg, out_deg), total_e = pt.scatter_partition(part, n, world, device, extra=extra, n_extra=2)
+    graph = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, device, max_features=f)
     comm = gs.Comm(rank, world)
     if args.exchange == "p2p":
         graph.xplan.enable_p2p(comm)

@@ -252,6 +252,54 @@ class LocalGraph:
         return _i32(global_in_degree[self.l2g]), _i32(global_out_degree[self.l2g])
 
 
+def scatter_partition(part, n_vertices, n_parts, device, extra=(), n_extra=0):
+    """Hand a partition that rank 0 holds to the ranks of the default torch.distributed group (any backend; tensors
+    travel on `device`).  Rank 0 passes the Partition and `extra`, a list of int32 arrays of n_vertices entries that
+    everybody needs (degrees); the others pass part=None and the number of such arrays.  Every rank p gets back
+    (partition, extras, total_edges): its own edges, the owner / replica tables and one presence word per vertex --
+    what LocalGraph and the exchange plans need of the other parts -- and the extra arrays as numpy.  Rank 0 keeps
+    its full partition."""
+    import torch
+    import torch.distributed as dist
+    rank = dist.get_rank()
+    meta = torch.zeros(n_parts + 1, dtype=torch.int64, device=device)
+    if rank == 0:
+        sizes = [len(x) for x in part.part_u]
+        meta[:] = torch.as_tensor(np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64))
+        extra = [np.ascontiguousarray(a, dtype=np.int32) for a in extra]
+        n_extra = len(extra)
+    dist.broadcast(meta, 0)
+    offs = meta.cpu().numpy()
+    if rank == 0:
+        tables = [torch.as_tensor(_i32(part.owner), device=device), torch.as_tensor(_i32(part.replicas), device=device),
+                  torch.as_tensor(part.presence_bits().view(np.int64), device=device)]
+        tables += [torch.as_tensor(a, device=device) for a in extra]
+    else:
+        tables = [torch.empty(n_vertices, dtype=torch.int32, device=device),
+                  torch.empty(n_vertices, dtype=torch.int32, device=device),
+                  torch.empty(n_vertices, dtype=torch.int64, device=device)]
+        tables += [torch.empty(n_vertices, dtype=torch.int32, device=device) for _ in range(n_extra)]
+    for t in tables:
+        dist.broadcast(t, 0)
+    extras = [t.cpu().numpy() for t in tables[3:]]
+    if rank == 0:
+        for p in range(1, n_parts):
+            for arr in (part.part_u[p], part.part_v[p]):
+                dist.send(torch.as_tensor(np.ascontiguousarray(arr, dtype=np.int32), device=device), dst=p)
+        mine = part
+    else:
+        got = []
+        for _ in range(2):
+            t = torch.empty(int(offs[rank + 1] - offs[rank]), dtype=torch.int32, device=device)
+            dist.recv(t, src=0)
+            got.append(t.cpu().numpy())
+        pu, pv = [None] * n_parts, [None] * n_parts
+        pu[rank], pv[rank] = got
+        mine = Partition(n_vertices, n_parts, pu, pv, tables[0].cpu().numpy(), tables[1].cpu().numpy(),
+                         present_bits=tables[2].cpu().numpy().view(np.uint64))
+    return mine, extras, int(offs[n_parts])
+
+
 def device_local_graph(u, v, global_v, stream=None):
     """Local numbering and CSR by source of one part from its edge list on the device (int32 CUDA tensors).
     Returns (n_local, g2l, l2g, index, dst) as CUDA tensors; identical to what LocalGraph builds on the host."""

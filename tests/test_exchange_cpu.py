@@ -137,3 +137,49 @@ def test_two_gloo_ranks():
         p.join(timeout=180)
     assert all(p.exitcode == 0 for p in procs)
     assert list(ok) == [1, 1]
+
+
+def _scatter_rank(rank, world, port, ok):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n, u, v = gg.rmat_graph(10, 8, seed=19, self_loops="add")
+        u, v = u.numpy(), v.numpy()
+        full = pt.ebv_partition(n, u, v, world)              # every rank can compute it: the check below needs it
+        in_deg = np.bincount(v, minlength=n).astype(np.int32)
+        out_deg = np.bincount(u, minlength=n).astype(np.int32)
+        if rank == 0:
+            mine, extras, total = pt.scatter_partition(full, n, world, torch.device("cpu"), extra=(in_deg, out_deg))
+        else:
+            mine, extras, total = pt.scatter_partition(None, n, world, torch.device("cpu"), n_extra=2)
+        assert total == len(u)
+        assert np.array_equal(extras[0], in_deg) and np.array_equal(extras[1], out_deg)
+        if rank != 0:
+            assert all(mine.part_u[q] is None for q in range(world) if q != rank)
+        a, b = mine.local_graph(rank), full.local_graph(rank)
+        for name in ("l2g", "index", "dst", "master_worker_index", "master2workers", "mirror2worker"):
+            assert np.array_equal(getattr(a, name), getattr(b, name)), name
+        xa, xb = pt.ExchangePlan(a, 4), pt.ExchangePlan(b, 4)
+        assert all(np.array_equal(p, q) for p, q in zip(xa.lists(), xb.lists()))
+        dist.barrier()
+        ok[rank] = 1
+    finally:
+        dist.destroy_process_group()
+
+
+def test_partition_scatter_over_gloo_ranks():
+    """The hand-out of a partition from rank 0 (what the multi-GPU benchmark does over NCCL) on three CPU ranks."""
+    import torch.multiprocessing as mp
+    world = 3
+    ctx = mp.get_context("spawn")
+    ok = ctx.Array("i", [0] * world)
+    port = 29800 + os.getpid() % 1000
+    procs = [ctx.Process(target=_scatter_rank, args=(r, world, port, ok)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+    assert all(p.exitcode == 0 for p in procs)
+    assert list(ok) == [1] * world
