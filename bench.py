@@ -583,11 +583,15 @@ def pagerank_timing(device):
     t0 = time.perf_counter()
     _, cpu_steps, cpu_msgs = oracle.pr_drone_cpu(n, part.part_u, part.part_v, out_deg, part.owner, eps=0.01, max_steps=200)
     cpu_s = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    oracle.pr_drone_cpu(n, part.part_u, part.part_v, out_deg, part.owner, eps=0.01, max_steps=200, maps=True)
+    cpu_maps_s = time.perf_counter() - t0
     out["rmat16_2parts"] = {
         "vertices": n, "edges": int(len(uh)), "iterations": 20, "ms_total_gpu": e0.elapsed_time(e1),
         "max_rel_err_vs_double_oracle": float(np.max(np.abs(got[touched] - want[touched]) / want[touched])),
         "replication_factor": part.replication_factor(),
-        "cpu_pr_job_restatement": {"seconds": cpu_s, "supersteps": cpu_steps, "messages": int(cpu_msgs), "cores": 1,
+        "cpu_pr_job_restatement": {"seconds": cpu_s, "seconds_hash_map_state": cpu_maps_s, "supersteps": cpu_steps,
+                                   "messages": int(cpu_msgs), "cores": 1,
                                    "note": "C restatement of DRONE's Go job (the Go binary cannot be built here)"}}
     for p_ in prs:
         p_.close()

@@ -124,6 +124,7 @@ def lib():
             build()
         _lib = C.CDLL(_SO)
         _lib.oracle_pr_drone_cpu.restype = C.c_int
+        _lib.oracle_pr_drone_cpu_maps.restype = C.c_int
         _lib.oracle_pr_drone_cuda_f32.restype = C.c_int
         _lib.oracle_pr_drone_cuda_f64.restype = C.c_int
         _lib.oracle_build_graph.restype = C.c_int
@@ -245,12 +246,14 @@ def _parts_args(parts_u, parts_v, out_degree, owner):
     return eoff, eu, ev, _i32(out_degree), _i32(owner)
 
 
-def pr_drone_cpu(global_v, parts_u, parts_v, out_degree, owner, eps=0.01, max_steps=200):
-    """DRONE's CPU job "pr" over a partition (float32).  Returns (pr[global_v], supersteps, messages)."""
+def pr_drone_cpu(global_v, parts_u, parts_v, out_degree, owner, eps=0.01, max_steps=200, maps=False):
+    """DRONE's CPU job "pr" over a partition (float32).  Returns (pr[global_v], supersteps, messages).
+    maps=True keeps every worker's state in hash maps keyed by global id, as the Go program does (same bits)."""
     eoff, eu, ev, od, ow = _parts_args(parts_u, parts_v, out_degree, owner)
     out = np.empty(global_v, np.float32)
     msgs = C.c_longlong(0)
-    steps = lib().oracle_pr_drone_cpu(len(parts_u), global_v, _p(eoff, C.c_int), _p(eu, C.c_int), _p(ev, C.c_int),
+    fn = lib().oracle_pr_drone_cpu_maps if maps else lib().oracle_pr_drone_cpu
+    steps = fn(len(parts_u), global_v, _p(eoff, C.c_int), _p(eu, C.c_int), _p(ev, C.c_int),
                                       _p(od, C.c_int), _p(ow, C.c_int), C.c_float(eps), int(max_steps),
                                       _p(out, C.c_float), C.byref(msgs))
     return out, steps, msgs.value

@@ -198,6 +198,152 @@ int oracle_pr_drone_cpu(int P, int V, const int *eoff, const int *eu, const int 
 }
 
 /* ------------------------------------------------------------------------- */
+/* The same job with every worker's state in hash maps keyed by global vertex  */
+/* id, as the Go program keeps it (map[int]float32 for pr / acc / diff, sets    */
+/* for updated / updateMaster / updateMirror; PRWorker.go:30-60), and loops     */
+/* over a worker's own vertices instead of over all ids.  Same order of         */
+/* operations as oracle_pr_drone_cpu, hence the same bits; it exists to time    */
+/* the job with the data structures of the original.                            */
+/* ------------------------------------------------------------------------- */
+typedef struct { int *keys; float *vals; int cap; } FMap;   /* open addressing, key -1 = empty */
+
+static void fmap_init(FMap *m, int expected) {
+    int cap = 16;
+    while (cap < 2 * expected + 2) cap <<= 1;
+    m->cap = cap;
+    m->keys = (int *)malloc(sizeof(int) * (size_t)cap);
+    m->vals = (float *)calloc((size_t)cap, sizeof(float));
+    for (int i = 0; i < cap; ++i) m->keys[i] = -1;
+}
+static void fmap_free(FMap *m) { free(m->keys); free(m->vals); }
+static inline float *fmap_at(FMap *m, int key) {     /* pointer to the value, inserted as 0 when absent */
+    unsigned h = ((unsigned)key * 2654435761u) & (unsigned)(m->cap - 1);
+    while (m->keys[h] != key) {
+        if (m->keys[h] == -1) { m->keys[h] = key; m->vals[h] = 0.0f; break; }
+        h = (h + 1) & (unsigned)(m->cap - 1);
+    }
+    return &m->vals[h];
+}
+static void fmap_clear_values(FMap *m) { memset(m->vals, 0, sizeof(float) * (size_t)m->cap); }
+
+int oracle_pr_drone_cpu_maps(int P, int V, const int *eoff, const int *eu, const int *ev, const int *outdeg,
+                             const int *owner, float eps, int max_steps, float *pr_out, long long *messages_out) {
+    const float alpha = 0.85f;
+    Parts g;
+    parts_init(&g, P, V, eoff, eu, ev, outdeg, owner);
+    /* every worker's own vertices, ascending */
+    int **mine = (int **)calloc((size_t)P, sizeof(int *));
+    int *n_mine = (int *)calloc((size_t)P, sizeof(int));
+    for (int p = 0; p < P; ++p) {
+        for (int v = 0; v < V; ++v) n_mine[p] += is_present(&g, p, v);
+        mine[p] = (int *)malloc(sizeof(int) * (size_t)(n_mine[p] + 1));
+        int k = 0;
+        for (int v = 0; v < V; ++v)
+            if (is_present(&g, p, v)) mine[p][k++] = v;
+    }
+    enum { PR, ACC, DIFF, UPD, NEXT, UMASTER, UMIRROR, XVAL, XFLAG, NMAPS };
+    FMap *m = (FMap *)calloc((size_t)P * NMAPS, sizeof(FMap));
+    for (int p = 0; p < P; ++p)
+        for (int k = 0; k < NMAPS; ++k) fmap_init(&m[p * NMAPS + k], n_mine[p]);
+#define M(p, which, v) (*fmap_at(&m[(p) * NMAPS + (which)], (v)))
+    long long messages = 0;
+    for (int p = 0; p < P; ++p)
+        for (int i = 0; i < n_mine[p]; ++i) { const int u = mine[p][i]; M(p, PR, u) = 1.0f; M(p, ACC, u) = 0.0f; }
+    for (int p = 0; p < P; ++p)
+        for (int i = 0; i < n_mine[p]; ++i) {
+            const int u = mine[p][i];
+            const float temp = M(p, PR, u) / (float)outdeg[u];
+            for (int k = g.rowptr[p][u]; k < g.rowptr[p][u + 1]; ++k) {
+                const int v = g.col[p][k];
+                M(p, DIFF, v) += temp;
+                M(p, UPD, v) = 1.0f;
+                if (is_mirror(&g, p, v)) M(p, UMIRROR, v) = 1.0f;
+                if (is_master(&g, p, v)) M(p, UMASTER, v) = 1.0f;
+            }
+        }
+    int any_message = 1, step = 0;
+    for (;;) {
+        if (!any_message) break;
+        for (int q = 0; q < P; ++q)
+            for (int i = 0; i < n_mine[q]; ++i) {
+                const int v = mine[q][i];
+                if (M(q, UMIRROR, v) != 0.0f) {
+                    const int o = owner[v];
+                    M(o, DIFF, v) += M(q, DIFF, v);
+                    M(o, UMASTER, v) = 1.0f;
+                    M(o, UPD, v) = 1.0f;
+                    ++messages;
+                }
+            }
+        if (step > 0)
+            for (int p = 0; p < P; ++p) fmap_clear_values(&m[p * NMAPS + UMIRROR]);
+        for (int p = 0; p < P; ++p)
+            for (int i = 0; i < n_mine[p]; ++i) {
+                const int v = mine[p][i];
+                if (M(p, UMASTER, v) != 0.0f) {
+                    for (int q = 0; q < P; ++q)
+                        if (q != p && is_present(&g, q, v)) {
+                            M(q, XFLAG, v) = 1.0f;
+                            M(q, XVAL, v) = M(p, DIFF, v);
+                            ++messages;
+                        }
+                    M(p, UMASTER, v) = 0.0f;
+                }
+            }
+        ++step;
+        if (step == max_steps) break;
+        any_message = 0;
+        for (int p = 0; p < P; ++p) {
+            for (int i = 0; i < n_mine[p]; ++i) {
+                const int v = mine[p][i];
+                if (M(p, XFLAG, v) != 0.0f) { M(p, DIFF, v) = M(p, XVAL, v); M(p, UPD, v) = 1.0f; M(p, XFLAG, v) = 0.0f; }
+            }
+            for (int i = 0; i < n_mine[p]; ++i) {
+                const int u = mine[p][i];
+                if (M(p, UPD, u) != 0.0f) { M(p, ACC, u) += M(p, DIFF, u); M(p, DIFF, u) = 0.0f; }
+            }
+            for (int i = 0; i < n_mine[p]; ++i) {
+                const int u = mine[p][i];
+                if (M(p, UPD, u) == 0.0f) continue;
+                const float prn = alpha * M(p, ACC, u) + 1 - alpha;
+                const float err = fabsf(M(p, PR, u) - prn);
+                if (err > eps) {
+                    const float push = (prn - M(p, PR, u)) / (float)outdeg[u];
+                    for (int k = g.rowptr[p][u]; k < g.rowptr[p][u + 1]; ++k) {
+                        const int v = g.col[p][k];
+                        M(p, NEXT, v) = 1.0f;
+                        M(p, DIFF, v) += push;
+                        if (is_mirror(&g, p, v)) M(p, UMIRROR, v) = 1.0f;
+                        if (is_master(&g, p, v)) M(p, UMASTER, v) = 1.0f;
+                    }
+                }
+                M(p, PR, u) = prn;
+            }
+            for (int i = 0; i < n_mine[p]; ++i) {
+                const int v = mine[p][i];
+                M(p, UPD, v) = M(p, NEXT, v);
+                M(p, NEXT, v) = 0.0f;
+                if (M(p, UMIRROR, v) != 0.0f) any_message = 1;
+            }
+        }
+    }
+    for (int v = 0; v < V; ++v) {
+        pr_out[v] = 0.0f;
+        for (int p = 0; p < P; ++p)
+            if (is_present(&g, p, v) && !is_mirror(&g, p, v)) pr_out[v] = M(p, PR, v);
+    }
+    if (messages_out) *messages_out = messages;
+#undef M
+    for (int p = 0; p < P; ++p) {
+        for (int k = 0; k < NMAPS; ++k) fmap_free(&m[p * NMAPS + k]);
+        free(mine[p]);
+    }
+    free(m); free(mine); free(n_mine);
+    parts_free(&g);
+    return step;
+}
+
+/* ------------------------------------------------------------------------- */
 /* GPU job "pr_cuda".  REAL is float (the reference) or double (same schedule  */
 /* without float rounding).  nvcc contracts alpha*(acc+globalAcc)+(1-alpha)    */
 /* into one fused multiply-add, so fma() is used there; sums that the          */

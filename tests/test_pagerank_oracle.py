@@ -86,3 +86,12 @@ def test_cpu_job_stop_rule_and_accuracy(oracle):
     one = pt.ebv_partition(n, u, v, 1, keep_self_loops=False)
     _, steps1, msgs1 = oracle.pr_drone_cpu(n, one.part_u, one.part_v, out_deg, one.owner, eps=0.01, max_steps=200)
     assert steps1 == 1 and msgs1 == 0
+
+
+@pytest.mark.parametrize("parts", [1, 2, 5])
+def test_cpu_job_with_hash_map_state_gives_the_same_bits(oracle, parts):
+    """State in hash maps keyed by global id (the Go program's layout) against the flat-array restatement."""
+    n, u, v, out_deg, part = pr_case(scale=10, seed=23, parts=parts)
+    flat = oracle.pr_drone_cpu(n, part.part_u, part.part_v, out_deg, part.owner, eps=0.01, max_steps=200)
+    maps = oracle.pr_drone_cpu(n, part.part_u, part.part_v, out_deg, part.owner, eps=0.01, max_steps=200, maps=True)
+    assert np.array_equal(flat[0], maps[0]) and flat[1] == maps[1] and flat[2] == maps[2]
