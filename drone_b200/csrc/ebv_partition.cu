@@ -81,6 +81,24 @@ private:
 
 static inline int pool_slices(int n) { return n >= (1 << 16) ? 64 : 1; }
 
+// Stable sort of a rank's edges by key (ascending): least-significant-digit radix passes of 11 bits, as many as the
+// largest key needs.  Same order as std::stable_sort on the key, several times faster on 10^8 edges.
+static void sort_by_key(std::vector<EbvEdge> &edges, int max_key) {
+    const size_t n = edges.size();
+    if (n < 2) return;
+    constexpr int kBits = 11, kBuckets = 1 << kBits;
+    std::vector<EbvEdge> other(n);
+    EbvEdge *src = edges.data(), *dst = other.data();
+    for (int shift = 0; shift == 0 || (max_key >> shift) != 0; shift += kBits) {
+        size_t count[kBuckets + 1] = {0};
+        for (size_t i = 0; i < n; ++i) ++count[(((unsigned)src[i].key >> shift) & (kBuckets - 1)) + 1];
+        for (int b = 0; b < kBuckets; ++b) count[b + 1] += count[b];
+        for (size_t i = 0; i < n; ++i) dst[count[((unsigned)src[i].key >> shift) & (kBuckets - 1)]++] = src[i];
+        std::swap(src, dst);
+    }
+    if (src != edges.data()) edges.swap(other);
+}
+
 // The partitioner proper.  Mask is an unsigned type of at least n_parts bits: held[v] has bit p set when part p holds
 // vertex v, so that scoring an edge costs two random reads whatever the number of parts.
 template <typename Mask>
@@ -116,9 +134,12 @@ static int ebv_run(int n_vertices, long long n_edges, const int *h_u, const int 
     pool.run(P, [&](int r) {
         std::vector<int> deg((size_t)n_vertices, 0);
         for (const EbvEdge &e : share[r]) { deg[e.u]++; deg[e.v]++; }
-        for (EbvEdge &e : share[r]) e.key = deg[e.u] + deg[e.v];
-        std::stable_sort(share[r].begin(), share[r].end(),
-                         [](const EbvEdge &a, const EbvEdge &b) { return a.key < b.key; });
+        int max_key = 0;
+        for (EbvEdge &e : share[r]) {
+            e.key = deg[e.u] + deg[e.v];
+            max_key = std::max(max_key, e.key);
+        }
+        sort_by_key(share[r], max_key);
     });
     for (int r = 0; r < P; ++r) kept += (long long)share[r].size();
 
