@@ -22,6 +22,21 @@ def test_golden_matches_oracle(oracle):
             assert np.array_equal(gold["%s/bwd_F%d" % (name, f)], oracle.graphsum_backward_f64(x, index, dst, val))
 
 
+def test_jobs_golden_matches_oracle(oracle):
+    """PageRank (power iteration, GPU job in double, CPU job), CC labels, SSSP distances and the per-superstep
+    exchange sizes of the cc / sssp jobs over seeded EBV partitions."""
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "jobs_golden.npz"))
+    for name, scale, ef, seed, parts in make_golden.JOB_CASES:
+        now = make_golden.job_outputs(scale, ef, seed, parts)
+        for k, a in now.items():
+            g = gold["%s/%s" % (name, k)]
+            if k in ("pr_power_f64", "pr_job_f64"):
+                # sums of doubles over in-edges: identical order here, but allow the last bits across compilers
+                assert np.allclose(g, a, rtol=1e-13, atol=0), (name, k)
+            else:
+                assert np.array_equal(g, a), (name, k)
+
+
 def test_seeded_normal_is_standard():
     x = gg.seeded_normal(5, (200000,))
     assert abs(float(x.mean())) < 0.01 and abs(float(x.std()) - 1.0) < 0.01
