@@ -150,7 +150,7 @@ static int ebv_run(int n_vertices, long long n_edges, const int *h_u, const int 
         part_u[p].reserve((size_t)(kept / P + kept / (16 * P) + 1024));
         part_v[p].reserve((size_t)(kept / P + kept / (16 * P) + 1024));
     }
-    // assignment of this round: for each (sender, part) the edges in sender order
+    // assignments of the current scoring step: for each (sender, part) the edges in sender order
     std::vector<std::vector<int>> sent((size_t)P * P);
 
     long long longest = 0;
