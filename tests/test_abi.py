@@ -67,3 +67,32 @@ def test_reference_shaped_shims_export_the_reference_symbols():
     gcn = C.CDLL(os.path.join(libdir, "libdrone_gcn_compat.so"))
     for n in ("create", "forward", "backward", "destroy"):
         assert hasattr(gcn, "drone_compat_graphsum_" + n)
+
+
+def test_header_is_plain_c(tmp_path):
+    """cgo (and any C host) compiles the header as C, not C++."""
+    import shutil
+    import subprocess
+    gcc = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "drone_b200.h"\n'
+                   "int main(void) { drone_pr_response r; drone_plan_stats s; (void)r; (void)s;\n"
+                   "                 return DRONE_OK + DRONE_OP_A + DRONE_PLAN_BOTH * 0 + DRONE_MP_SSSP * 0; }\n")
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only",
+                        "-I", os.path.join(ROOT, "include"), str(src)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
+def test_compat_library_exports_the_cgo_interface():
+    """The symbols DRONE/src/tools/cuda_convert.go binds, by the reference's names."""
+    import drone_b200
+    drone_b200.lib()
+    path = os.path.join(ROOT, "drone_b200", "lib", "libdrone_pr_compat.so")
+    if not os.path.exists(path):
+        pytest.skip("compat library not built")
+    lib = C.CDLL(path)
+    for name in ("build_graph", "addMasterRoute", "addMirrorRoute", "getLocalVertexSize", "getGlobalVertexSize",
+                 "loadOutDegree", "PR_PEVal", "PR_IncEVal", "CC_PEVal", "CC_IncEVal", "SSSP_PEVal", "SSSP_IncEVal"):
+        assert hasattr(lib, name), name
