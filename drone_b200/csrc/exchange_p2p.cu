@@ -320,6 +320,39 @@ int drone_xplan_enable_p2p(drone_xplan *x, drone_comm *c, void *stream) {
 
 namespace drone {
 
+// DRONE_P2P_TIMING=1 in the environment makes every exchange measure its five launches with CUDA events, wait for
+// them and print one line per call on standard error (a diagnosis aid: it serialises the host with the device).
+static bool p2p_timing_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("DRONE_P2P_TIMING");
+        return v && v[0] == '1';
+    }();
+    return on;
+}
+
+struct PhaseTimer {
+    bool on;
+    cudaStream_t st;
+    cudaEvent_t ev[6];
+    int n = 0;
+    PhaseTimer(bool enabled, cudaStream_t stream) : on(enabled), st(stream) {
+        if (on)
+            for (auto &e : ev) cudaEventCreate(&e);
+    }
+    void mark() {
+        if (on && n < 6) cudaEventRecord(ev[n++], st);
+    }
+    void report(int rank, int n_up, int n_m, int F) {
+        if (!on) return;
+        cudaStreamSynchronize(st);
+        float ms[5] = {0, 0, 0, 0, 0};
+        for (int i = 0; i + 1 < n; ++i) cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]);
+        fprintf(stderr, "p2p rank %d: push_up %.3f signal %.3f add_push_down %.3f signal %.3f scatter %.3f ms (n_up %d n_m %d F %d)\n",
+                rank, ms[0], ms[1], ms[2], ms[3], ms[4], n_up, n_m, F);
+        for (auto &e : ev) cudaEventDestroy(e);
+    }
+};
+
 // One exchange over peer memory; called by drone_exchange_sum when the plan has the transport enabled.
 int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t st) {
     drone_p2p *p = x->p2p;
@@ -336,28 +369,36 @@ int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t 
         p->segment + kFlagBytes + align_up(x->down_rows.size() * (size_t)x->max_features * 4, 256));
     const bool vec4 = (F % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_rows) & 15) == 0);
     const int nvec = vec4 ? F / 4 : F;
+    PhaseTimer timer(p2p_timing_enabled(), st);
+    timer.mark();
     if (n_up) {
         const int grid = p2p_grid((long long)n_up * nvec);
         if (vec4) p2p_push_up_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, p->d_up_peer, p->d_up_dest_row, p->d_up_order, n_up, nvec, p->d_peer_up_recv);
         else p2p_push_up_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, p->d_up_peer, p->d_up_dest_row, p->d_up_order, n_up, nvec, p->d_peer_up_recv);
         DRONE_LAUNCH_CHECK("p2p_push_up_kernel");
     }
+    timer.mark();
     p2p_signal_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_up, p->d_need_down, P, epoch);   // to the owners of my mirrors
     DRONE_LAUNCH_CHECK("p2p_signal_kernel");
+    timer.mark();
     if (n_m) {
         const int grid = p2p_grid((long long)n_m * nvec);
         if (vec4) p2p_add_push_down_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, x->d_m_pos, n_m, nvec, my_up_recv, p->d_down_peer, p->d_down_dest_row, p->d_peer_down_recv, my_flags, p->d_need_up, P, epoch, p->d_error, p->d_host_error);
         else p2p_add_push_down_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, x->d_m_pos, n_m, nvec, my_up_recv, p->d_down_peer, p->d_down_dest_row, p->d_peer_down_recv, my_flags, p->d_need_up, P, epoch, p->d_error, p->d_host_error);
         DRONE_LAUNCH_CHECK("p2p_add_push_down_kernel");
     }
+    timer.mark();
     p2p_signal_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_down, p->d_need_up, P, epoch);   // to the holders of my mirrors
     DRONE_LAUNCH_CHECK("p2p_signal_kernel");
+    timer.mark();
     if (n_up) {
         const int grid = p2p_grid((long long)n_up * nvec);
         if (vec4) p2p_scatter_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, n_up, nvec, my_down_recv, my_flags + P, p->d_need_down, P, epoch, p->d_error, p->d_host_error);
         else p2p_scatter_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, n_up, nvec, my_down_recv, my_flags + P, p->d_need_down, P, epoch, p->d_error, p->d_host_error);
         DRONE_LAUNCH_CHECK("p2p_scatter_kernel");
     }
+    timer.mark();
+    timer.report(x->rank, n_up, n_m, F);
     return DRONE_OK;
 }
 
