@@ -9,8 +9,17 @@ nnz·F per second (one multiply-add per stored nonzero per feature).
 
 Workloads (all synthetic, seeded):
   c2       R-MAT scale 20, edge factor 16, symmetrised, +I, F=64   (single-GPU headline)
+  rmat22   R-MAT scale 22, edge factor 16, directed, +I, F=32
   rmat26   R-MAT scale 26, edge factor 16, directed, +I, F=32
   custom   --scale/--edge-factor/--features/--symmetrise
+
+Several GPUs (one process per GPU under torchrun): the graph is EBV-partitioned on rank 0 and handed out; a step is
+the local aggregation plus the mirror/master exchange.  --scaling weak (default: scale + log2 N) | strong,
+--exchange p2p|nccl|dense, --pipeline-groups G, --pagerank-iters K.
+
+Beside the headline the line carries: roofline, e2e (host operands), cusparse (head-to-head), cpu_baseline, clocks,
+gcn_epoch, pagerank, minprop (cc / sssp jobs) and jobs_head_to_head (the reference's own GPU jobs vs the drop-in);
+--no-cusparse / --no-cpu-baseline / --no-gcn leave sections out.
 """
 import argparse
 import json
