@@ -45,6 +45,8 @@ class PlanStats(C.Structure):
         ("n_split_rows", C.c_int * 2),
         ("n_partials", C.c_int * 2),
         ("scratch_bytes", C.c_longlong),
+        ("last_slice_width", C.c_int),
+        ("reserved_", C.c_int),
     ]
 
 
@@ -63,6 +65,7 @@ def _declare(lib):
         "drone_plan_get_stats": (i, [vp, C.POINTER(PlanStats)]),
         "drone_plan_get_csr": (i, [vp, i, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "drone_spmm": (i, [vp, i, i, vp, i, vp, i, vp]),
+        "drone_plan_reserve": (i, [vp, i, i]),
         "drone_plan_set_row_classes": (i, [vp, vp, i, vp]),
         "drone_spmm_rows": (i, [vp, i, i, i, vp, i, vp, i, vp]),
         "drone_spmm_host": (i, [vp, i, i, vp, vp]),

@@ -23,6 +23,10 @@ inline void count_launch(int n = 1) { g_kernel_launches.fetch_add(n, std::memory
 
 inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
+// Device-side check of a CSR given by the caller (defined with the plan builder): DRONE_E_INVALID naming the first
+// bad row pointer or column, DRONE_OK for a well-formed input.  Synchronises `st`.
+int validate_csr(const char *who, const int *d_index, const int *d_col, int n_rows, int n_cols, int nnz, cudaStream_t st);
+
 }  // namespace drone
 
 // Evaluate a CUDA runtime call; on failure record the message and return DRONE_E_CUDA

@@ -418,6 +418,10 @@ int drone_mp_create(drone_mp **out, int kind, int n_local, int nnz, const int *d
                   "drone_mp_create: communicator and exchange plan disagree on rank / size");
     DRONE_REQUIRE(n_local == 0 || (d_index && d_local2global), "drone_mp_create: NULL graph array");
     DRONE_REQUIRE(nnz == 0 || d_dst != nullptr, "drone_mp_create: d_dst is NULL with nnz=%d", nnz);
+    if (n_local > 0) {   // the relax kernels index the value arrays with d_dst: reject what would run out of bounds
+        const int bad = validate_csr("drone_mp_create", d_index, d_dst, n_local, n_local, nnz, nullptr);
+        if (bad) return bad;
+    }
     drone_mp *p = new (std::nothrow) drone_mp();
     if (!p) return set_error(DRONE_E_INVALID, "drone_mp_create: out of host memory");
     p->kind = kind;

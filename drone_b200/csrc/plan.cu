@@ -234,6 +234,26 @@ __global__ void select_wide_kernel(const SplitRow *__restrict__ split, int n, Sp
     }
 }
 
+// Input check of a CSR: bad[0] = 1 + position of the first row pointer that is negative, decreasing or above nnz
+// (position n_rows + 1 reports rowptr[n_rows] != nnz), bad[1] = 1 + position of the first column outside 0..n_cols-1.
+// Both stay 0 for a well-formed input.  Positions are found with atomicMin on (position + 1) stored as unsigned - 1.
+__global__ void check_csr_kernel(const int *__restrict__ rowptr, const int *__restrict__ col, int n_rows, int n_cols,
+                                 int nnz, unsigned *bad) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x; r <= n_rows; r += stride) {
+        const int a = rowptr[r];
+        bool wrong = a < 0 || a > nnz;
+        if (r == 0) wrong = wrong || a != 0;
+        if (r < n_rows) wrong = wrong || rowptr[r + 1] < a;
+        if (r == n_rows) wrong = wrong || a != nnz;
+        if (wrong) atomicMin(bad, (unsigned)r);
+    }
+    for (long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x; k < nnz; k += stride) {
+        const int c = col[k];
+        if (c < 0 || c >= n_cols) atomicMin(bad + 1, (unsigned)k);
+    }
+}
+
 static inline int grid_for(long long n, int block = 256, int cap = 148 * 32) {
     long long g = (n + block - 1) / block;
     if (g < 1) g = 1;
@@ -484,10 +504,38 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
     return DRONE_OK;
 }
 
+// Checks d_index / d_col before anything indexes with them: a column outside the matrix would otherwise become an
+// out-of-bounds access in the histogram of the transpose and in every gather of the aggregation.
+int validate_csr(const char *who, const int *d_index, const int *d_col, int n_rows, int n_cols, int nnz, cudaStream_t st) {
+    unsigned *d_bad = nullptr;
+    unsigned h_bad[2] = {0xffffffffu, 0xffffffffu};
+    DRONE_CUDA(cudaMalloc(&d_bad, sizeof(h_bad)));
+    cudaError_t err = cudaMemcpyAsync(d_bad, h_bad, sizeof(h_bad), cudaMemcpyHostToDevice, st);
+    if (err == cudaSuccess) {
+        check_csr_kernel<<<grid_for((long long)(nnz > n_rows ? nnz : n_rows + 1)), 256, 0, st>>>(d_index, d_col, n_rows, n_cols, nnz, d_bad);
+        err = cudaGetLastError();
+        count_launch();
+    }
+    if (err == cudaSuccess) err = cudaMemcpyAsync(h_bad, d_bad, sizeof(h_bad), cudaMemcpyDeviceToHost, st);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+    cudaFree(d_bad);
+    if (err != cudaSuccess) return set_error(DRONE_E_CUDA, "%s: checking the CSR failed: %s", who, cudaGetErrorString(err));
+    if (h_bad[0] != 0xffffffffu)
+        return set_error(DRONE_E_INVALID, "%s: row pointer %u is not a valid CSR offset (must start at 0, never decrease, "
+                         "and end at nnz=%d)", who, h_bad[0], nnz);
+    if (h_bad[1] != 0xffffffffu)
+        return set_error(DRONE_E_INVALID, "%s: column index at position %u is outside 0..%d", who, h_bad[1], n_cols - 1);
+    return DRONE_OK;
+}
+
 static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_index, const int *d_dst,
                             const float *d_values, const int *d_in_degree, const int *d_out_degree,
                             int orientations, cudaStream_t st) {
     DRONE_CUDA(cudaGetDevice(&p->device));
+    {
+        const int rc = validate_csr("drone_plan_create", d_index, d_dst, n_rows, n_rows, nnz, st);
+        if (rc) return rc;
+    }
     p->n_rows = n_rows;
     p->nnz = nnz;
     p->short_row_limit = env_int("DRONE_SHORT_ROW_LIMIT", 32);
@@ -496,6 +544,8 @@ static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_ind
     // the CSR stream.
     p->chunk_nnz = env_int("DRONE_CHUNK_NNZ", nnz > (1 << 28) ? 1024 : 256);
     if (p->chunk_nnz < p->short_row_limit) p->chunk_nnz = p->short_row_limit;
+    const char *slice = getenv("DRONE_SLICE_WIDTH");       // read per plan, so that one process can hold plans of each kind
+    p->slice_forced = (slice && *slice) ? atoi(slice) : -1;
 
     Side &a = p->side[DRONE_OP_A];
     const size_t nnz_alloc = (size_t)(nnz > 0 ? nnz : 1);
@@ -542,7 +592,7 @@ using namespace drone;
 
 extern "C" {
 
-int drone_version(void) { return 1000; }
+int drone_version(void) { return 1001; }
 
 const char *drone_last_error(void) { return last_error_buffer(); }
 
@@ -689,6 +739,7 @@ int drone_plan_get_stats(const drone_plan *p, drone_plan_stats *out) {
         out->n_partials[o] = p->side[o].n_partials;
     }
     out->scratch_bytes = (long long)p->scratch_bytes;
+    out->last_slice_width = p->last_slice_width;
     return DRONE_OK;
 }
 

@@ -73,6 +73,8 @@ struct drone_plan {
     int nnz = 0;
     int short_row_limit = 0;   // rows with deg <= this are summed by one lane group
     int chunk_nnz = 0;         // nonzeros per chunk of longer rows
+    int last_slice_width = 0;  // what the most recent call used (reported by drone_plan_get_stats)
+    int slice_forced = -1;     // column-slice width of a call: -1 chosen per call, 0 never slice, w > 0 slices of w columns
     drone::Side side[2];       // [DRONE_OP_A], [DRONE_OP_AT]
     // partial sums of split rows, [n_partials, F] floats, grown on demand
     float *scratch = nullptr;

@@ -18,6 +18,7 @@
 // cache hints so that L2 capacity is left to the gathered rows of X.
 #include "plan.cuh"
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -508,7 +509,7 @@ static int ensure_scratch(drone_plan *p, size_t bytes) {
 // n*w*4 bytes of X; when the whole operand does not fit in L2 but a slice does, running the slices one after the
 // other turns HBM gathers into L2 gathers at the price of re-reading the CSR stream once per slice.
 static int slice_width(const drone_plan *p, int F, bool vec4) {
-    static const int forced = tuning_int("DRONE_SLICE_WIDTH", -1);
+    const int forced = p->slice_forced;
     if (forced == 0 || !vec4) return 0;
     if (forced > 0) return (forced % 4 == 0 && forced < F && F % forced == 0) ? forced : 0;
     const double l2_budget = 64e6;                      // about half of the 126 MB L2 for the gathered operand
@@ -527,6 +528,7 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
                       ((reinterpret_cast<uintptr_t>(X) & 15) == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
     const int slice = slice_width(p, F, vec4);
     const int width = slice > 0 ? slice : F;
+    p->last_slice_width = slice;
     if (s.n_partials > 0) {
         const int rc = ensure_scratch(p, sizeof(float) * (size_t)s.n_partials * (size_t)width);
         if (rc) return rc;
@@ -605,6 +607,47 @@ int drone_spmm_rows(drone_plan *p, int orientation, int row_class, int F, const 
     return rc;
 }
 
+// Puts the caller's device back on every way out of an entry point that had to switch to the plan's device.
+struct DeviceGuard {
+    int prev = -1, mine = -1;
+    int enter(int device) {
+        mine = device;
+        DRONE_CUDA(cudaGetDevice(&prev));
+        if (prev != mine) DRONE_CUDA(cudaSetDevice(mine));
+        return DRONE_OK;
+    }
+    ~DeviceGuard() { if (prev >= 0 && prev != mine) cudaSetDevice(prev); }
+};
+
+static int ensure_staging(drone_plan *p, size_t bytes) {
+    if (bytes <= p->stage_bytes) return DRONE_OK;
+    DRONE_CUDA(cudaDeviceSynchronize());
+    cudaFree(p->stage_x);
+    cudaFree(p->stage_y);
+    p->stage_x = p->stage_y = nullptr;
+    p->stage_bytes = 0;
+    DRONE_CUDA(cudaMalloc(&p->stage_x, bytes));
+    DRONE_CUDA(cudaMalloc(&p->stage_y, bytes));
+    p->stage_bytes = bytes;
+    return DRONE_OK;
+}
+
+int drone_plan_reserve(drone_plan *p, int max_features, int host_operands) {
+    DRONE_REQUIRE(p != nullptr, "drone_plan_reserve: plan is NULL");
+    DRONE_REQUIRE(max_features >= 1 && max_features <= 1024, "drone_plan_reserve: max_features=%d outside 1..1024",
+                  max_features);
+    DeviceGuard guard;
+    int rc = guard.enter(p->device);
+    if (rc) return rc;
+    const size_t slots = (size_t)std::max(p->side[0].n_partials, p->side[1].n_partials);
+    if (slots > 0 && (rc = ensure_scratch(p, sizeof(float) * slots * (size_t)max_features))) return rc;
+    if (host_operands) {
+        if ((rc = ensure_staging(p, sizeof(float) * (size_t)p->n_rows * (size_t)max_features))) return rc;
+        if (!p->own_stream) DRONE_CUDA(cudaStreamCreateWithFlags(&p->own_stream, cudaStreamNonBlocking));
+    }
+    return DRONE_OK;
+}
+
 int drone_spmm_host(drone_plan *p, int orientation, int F, const float *h_X, float *h_Y) {
     DRONE_REQUIRE(p != nullptr, "drone_spmm_host: plan is NULL");
     DRONE_REQUIRE(orientation == DRONE_OP_A || orientation == DRONE_OP_AT, "drone_spmm_host: orientation=%d",
@@ -613,26 +656,16 @@ int drone_spmm_host(drone_plan *p, int orientation, int F, const float *h_X, flo
     DRONE_REQUIRE(F >= 1 && F <= 1024, "drone_spmm_host: feature width F=%d outside 1..1024", F);
     if (p->n_rows == 0) return DRONE_OK;
     DRONE_REQUIRE(h_X && h_Y, "drone_spmm_host: NULL operand");
-    int dev = -1;
-    DRONE_CUDA(cudaGetDevice(&dev));
-    if (dev != p->device) DRONE_CUDA(cudaSetDevice(p->device));
+    DeviceGuard guard;
+    int rc = guard.enter(p->device);
+    if (rc) return rc;
     const size_t bytes = sizeof(float) * (size_t)p->n_rows * (size_t)F;
-    if (bytes > p->stage_bytes) {
-        cudaFree(p->stage_x);
-        cudaFree(p->stage_y);
-        p->stage_x = p->stage_y = nullptr;
-        p->stage_bytes = 0;
-        DRONE_CUDA(cudaMalloc(&p->stage_x, bytes));
-        DRONE_CUDA(cudaMalloc(&p->stage_y, bytes));
-        p->stage_bytes = bytes;
-    }
+    if ((rc = ensure_staging(p, bytes))) return rc;      // no-op after drone_plan_reserve(.., host_operands = 1)
     if (!p->own_stream) DRONE_CUDA(cudaStreamCreateWithFlags(&p->own_stream, cudaStreamNonBlocking));
     DRONE_CUDA(cudaMemcpyAsync(p->stage_x, h_X, bytes, cudaMemcpyHostToDevice, p->own_stream));
-    const int rc = spmm_impl(p, orientation, F, p->stage_x, F, p->stage_y, F, p->own_stream);
-    if (rc) return rc;
+    if ((rc = spmm_impl(p, orientation, F, p->stage_x, F, p->stage_y, F, p->own_stream))) return rc;
     DRONE_CUDA(cudaMemcpyAsync(h_Y, p->stage_y, bytes, cudaMemcpyDeviceToHost, p->own_stream));
     DRONE_CUDA(cudaStreamSynchronize(p->own_stream));
-    if (dev != p->device) cudaSetDevice(dev);
     return DRONE_OK;
 }
 

@@ -91,6 +91,12 @@ class AggregationPlan:
                 out.append(_view_device_memory(ptr.value, n, dt, self.device).clone())
         return tuple(out)
 
+    def reserve(self, max_features, host_operands=False):
+        """Allocate now what calls with F <= max_features would allocate on first use (partial sums of split rows;
+        with host_operands the device staging of spmm_host)."""
+        with torch.cuda.device(self.device):
+            check(_lib.lib().drone_plan_reserve(self._h, int(max_features), 1 if host_operands else 0))
+
     def set_row_classes(self, row_class, n_classes, stream=None):
         """Give every row a class in 0..n_classes-1 (int32 CUDA tensor [n_rows]); spmm(..., row_class=c) then
         computes the rows of one class only.  n_classes = 1 removes the classes."""

@@ -94,6 +94,8 @@ typedef struct drone_plan_stats {
     int       n_split_rows[2];   /* rows made of more than one chunk (need partial sums) */
     int       n_partials[2];     /* partial-sum slots = chunks of split rows */
     long long scratch_bytes;     /* bytes of partial-sum scratch currently held */
+    int       last_slice_width;  /* columns per slice of the most recent aggregation call (0: it ran in one piece) */
+    int       reserved_;
 } drone_plan_stats;
 
 int drone_plan_get_stats(const drone_plan *plan, drone_plan_stats *out);
@@ -135,6 +137,16 @@ int drone_spmm(drone_plan *plan, int orientation, int F,
 int drone_plan_set_row_classes(drone_plan *plan, const int *d_row_class, int n_classes, void *stream);
 int drone_spmm_rows(drone_plan *plan, int orientation, int row_class, int F,
                     const float *d_X, int ldx, float *d_Y, int ldy, void *stream);
+
+/*
+ * Allocates, ahead of time, everything later calls of this plan would otherwise allocate on first use: the
+ * partial-sum buffer of split rows for feature widths up to max_features and, with host_operands != 0, the device
+ * staging of drone_spmm_host for [n_rows, max_features] operands.  After it, drone_spmm / drone_spmm_rows /
+ * drone_spmm_host with F <= max_features reach neither cudaMalloc nor a device-wide synchronisation.
+ * Stands where the reference sizes its cuSPARSE workspace on the first training step,
+ * cuda_gcn/src/cuda/cuda_module.cu:234-244 (cusparseSpMM_bufferSize, cudaFree + cudaMalloc of sparseBuffer).
+ */
+int drone_plan_reserve(drone_plan *plan, int max_features, int host_operands);
 
 /*
  * Same operation with HOST operands: copies X to the device, aggregates, and

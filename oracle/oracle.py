@@ -24,7 +24,9 @@ def build(force=False):
 
 
 _REF_SO = os.path.join(_HERE, "_ref", "libref_graphsum.so")
-REFERENCE_ROOT = os.environ.get("DRONE_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: DRONE_REFERENCE_ROOT, else the directory `reference` beside this repository
+REFERENCE_ROOT = os.environ.get("DRONE_REFERENCE_ROOT",
+                                os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference"))
 
 
 def build_ref(force=False):

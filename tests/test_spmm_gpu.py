@@ -126,6 +126,45 @@ def test_many_partials_per_row(cuda_device, oracle):
         check_both_orientations(plan, oracle, index, dst, val, x, cuda_device)
 
 
+@pytest.mark.parametrize("f,width", [(128, 64), (256, 64), (256, 128)])
+def test_forced_column_slices(cuda_device, oracle, f, width):
+    """A call cut into column slices (DRONE_SLICE_WIDTH at plan creation) against the double oracle, both
+    orientations, and bit for bit against the same call in one piece."""
+    n, u, v = gg.rmat_graph(12, 16, seed=36, symmetrise=False, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    x = gg.seeded_normal(60 + f, (n, f))
+    sliced = make_plan(cuda_device, index, dst, in_deg, out_deg, DRONE_SLICE_WIDTH=width)
+    whole = make_plan(cuda_device, index, dst, in_deg, out_deg, DRONE_SLICE_WIDTH=0)
+    assert sliced.stats().n_partials[db.OP_AT] > 0
+    fwd, bwd = check_both_orientations(sliced, oracle, index, dst, val, x, cuda_device)
+    xt = torch.as_tensor(x, device=cuda_device)
+    assert np.array_equal(fwd, whole.spmm(db.OP_AT, xt).cpu().numpy())
+    assert np.array_equal(bwd, whole.spmm(db.OP_A, xt).cpu().numpy())
+    # padded leading dimensions: the slices are column blocks of the caller's own rows
+    xp = torch.zeros((n, f + 8), device=cuda_device)
+    xp[:, :f] = xt
+    yp = torch.full((n, f + 12), 5.0, device=cuda_device)
+    sliced.spmm(db.OP_AT, xp[:, :f], out=yp[:, :f])
+    assert np.array_equal(yp[:, :f].cpu().numpy(), fwd) and (yp[:, f:] == 5.0).all()
+
+
+def test_column_slices_chosen_by_size(cuda_device, oracle):
+    """131,072 rows at F = 128 are 67 MB of gathered operand: above the threshold at which a call is cut into
+    64-column slices by itself.  Checked against the double oracle and against the unsliced call."""
+    n, u, v = gg.rmat_graph(17, 8, seed=37, symmetrise=False, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    f = 128
+    assert n * f * 4 > 64e6
+    x = gg.seeded_normal(61, (n, f))
+    auto = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    whole = make_plan(cuda_device, index, dst, in_deg, out_deg, DRONE_SLICE_WIDTH=0)
+    fwd, bwd = check_both_orientations(auto, oracle, index, dst, val, x, cuda_device)
+    xt = torch.as_tensor(x, device=cuda_device)
+    assert np.array_equal(fwd, whole.spmm(db.OP_AT, xt).cpu().numpy())
+    assert np.array_equal(bwd, whole.spmm(db.OP_A, xt).cpu().numpy())
+    assert auto.stats().last_slice_width == 64 and whole.stats().last_slice_width == 0
+
+
 def test_golden_vectors(cuda_device, oracle):
     gold = np.load(os.path.join(ROOT, "tests", "golden", "spmm_golden.npz"))
     for name, scale, ef, seed, sym, loops, widths in make_golden.CASES:
@@ -206,6 +245,46 @@ def test_argument_errors(cuda_device, oracle):
     assert b"outside 1..1024" in lib.drone_last_error()
     assert lib.drone_spmm(plan.handle, 1, 8, x.data_ptr(), 8, x.data_ptr(), 8, None) == -1
     assert b"alias" in lib.drone_last_error()
+
+
+def test_malformed_csr_is_refused(cuda_device):
+    """Row pointers that decrease or do not end at nnz, and columns outside the matrix, come back as
+    DRONE_E_INVALID naming the first bad entry instead of becoming out-of-bounds accesses."""
+    def create(index, dst):
+        return db.AggregationPlan(torch.tensor(index, dtype=torch.int32, device=cuda_device),
+                                  torch.tensor(dst, dtype=torch.int32, device=cuda_device),
+                                  values=torch.ones(len(dst), device=cuda_device))
+    create([0, 2, 3, 4], [1, 2, 0, 1])                                    # well formed
+    with pytest.raises(db.DroneError, match="column index at position 2 is outside 0..2"):
+        create([0, 2, 3, 4], [1, 2, 3, 1])
+    with pytest.raises(db.DroneError, match="column index at position 0"):
+        create([0, 2, 3, 4], [-1, 2, 0, 1])
+    with pytest.raises(db.DroneError, match="row pointer 1 is not a valid CSR offset"):
+        create([0, 3, 2, 4], [1, 2, 0, 1])
+    with pytest.raises(db.DroneError, match="row pointer 3"):
+        create([0, 2, 3, 3], [1, 2, 0, 1])
+    with pytest.raises(db.DroneError, match="row pointer 0"):
+        create([1, 2, 3, 4], [1, 2, 0, 1])
+
+
+def test_reserve_makes_later_calls_allocation_free(cuda_device, oracle):
+    n, u, v = gg.rmat_graph(12, 16, seed=38, symmetrise=False, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    plan.reserve(64, host_operands=True)
+    st = plan.stats()
+    assert st.scratch_bytes >= 4 * 64 * max(st.n_partials[0], st.n_partials[1]) > 0
+    x = torch.as_tensor(gg.seeded_normal(9, (n, 64)), device=cuda_device)
+    y = torch.empty_like(x)
+    xh, yh = x.cpu().pin_memory(), torch.empty((n, 64)).pin_memory()
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info(cuda_device)[0]
+    plan.spmm(db.OP_AT, x, out=y)
+    plan.spmm(db.OP_A, x, out=y)
+    plan.spmm_host(db.OP_AT, xh, yh)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(cuda_device)[0] == free0
+    assert plan.stats().scratch_bytes == st.scratch_bytes
 
 
 def test_empty_graph(cuda_device):

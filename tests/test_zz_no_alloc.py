@@ -4,7 +4,8 @@ partial sums of split rows in an array built into the library instead of a buffe
 
 Checked here through the C ABI: its output equals drone_spmm's bit for bit on two calls in a row (the shared
 array keeps the previous call's contents, which must not matter), for a vector and a scalar feature width and
-both orientations, and a plan whose partial sums do not fit is refused with DRONE_E_TOO_LARGE.
+both orientations; the free device memory reported by the driver is the same before and after its calls; and a
+plan whose partial sums do not fit is refused with DRONE_E_TOO_LARGE.
 This file sorts last on purpose: a run that stops at the first failure has then run every other test.
 """
 import ctypes as C
@@ -55,6 +56,17 @@ def test_static_scratch_matches_allocating_entry_point(cuda_device):
             torch.cuda.synchronize()
             assert torch.equal(got1, want1)
             assert torch.equal(got2, want2)
+    # the claim itself: no device memory is taken by the calls (the address lookup of the first call is behind us)
+    x = torch.as_tensor(gg.seeded_normal(77, (n, 64)), device=cuda_device)
+    y = torch.empty_like(x)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(cuda_device)[0]
+    held_before = plan.stats().scratch_bytes
+    for op in (db.OP_AT, db.OP_A):
+        assert call_static(plan, op, x, y) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(cuda_device)[0] == free_before
+    assert plan.stats().scratch_bytes == held_before
     # a different plan uses the same array afterwards
     n2, plan2 = make_plan(cuda_device, 11, 72)
     x = torch.as_tensor(gg.seeded_normal(5, (n2, 32)), device=cuda_device)
