@@ -40,9 +40,8 @@ struct drone_p2p {
     // device tables, all indexed as documented in exchange_p2p.cu
     float **d_peer_up_recv = nullptr, **d_peer_down_recv = nullptr;   // [nranks] bases inside peers' segments
     unsigned **d_peer_flag_up = nullptr, **d_peer_flag_down = nullptr;   // [nranks] address of "my" word in the peer's flags
-    int *d_up_peer = nullptr, *d_up_dest_row = nullptr;       // [n_up]   per mirror row: owner, row in owner's up-receive
-    int *d_up_order = nullptr;          // [n_up] order in which push_up walks the mirror rows (interleaves the owners)
-    int *d_down_peer = nullptr, *d_down_dest_row = nullptr;   // [n_down] per (master, mirror) pair: peer, row in its down-receive
+    int4 *d_walk = nullptr;             // [n_up] mirror rows in the order push_up walks them: {local row, owner, row in the owner's up-receive, 0}
+    int4 *d_pairs = nullptr;            // [n_down] (master, mirror) pairs in m_pos order: {row in my up-receive, peer, row in its down-receive, 0}
     int *d_need_up = nullptr, *d_need_down = nullptr;         // [nranks] 1 where a flag from that peer is expected
     int *h_error = nullptr;             // pinned, mapped: set by a kernel whose wait ran out
     int *d_host_error = nullptr;        // device alias of h_error (written only when a wait runs out)

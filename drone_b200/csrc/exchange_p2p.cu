@@ -3,13 +3,16 @@
 // Same result as the NCCL transport of exchange.cu, with the packing, the transfer and the unpacking of each
 // direction fused into one kernel per direction that stores rows straight into the receiver's memory:
 //   push_up:        every mirror row -> the owner's up-receive area (position fixed by the static plan)
-//   add_push_down:  wait for the up flags; master row += its mirrors' rows in ascending rank order; the total goes
-//                   to every mirror's down-receive area
-//   scatter:        wait for the down flags; mirror rows take the totals
+//   add_push_down:  master row += its mirrors' rows in ascending rank order; the total goes to every mirror's
+//                   down-receive area
+//   scatter:        mirror rows take the totals
 // Ordering between GPUs uses one epoch word per (receiver, sender, direction): the sender's signal kernel runs after
-// its stores in stream order, fences, and writes the call's epoch; the receiver polls its own words.  Every wait is
-// bounded: when it runs out the kernel records an error code in pinned host memory, skips its work and returns, and
-// the next call reports DRONE_E_STATE.  Nothing here uses TMA or cluster multicast; peers are reached with plain
+// its stores in stream order, fences, and writes the call's epoch; the receiver polls its own words in a ONE-BLOCK
+// wait kernel launched in front of add_push_down and scatter.  (Waiting inside the row kernels themselves held every
+// SM slot those kernels were given for as long as the slowest peer took, which starved whatever ran beside the
+// exchange.)  Every wait is bounded: when it runs out the kernel records an error code in device memory and in pinned
+// host memory, the kernels behind it skip their work, this rank publishes no further epoch (so that its peers' waits
+// run out too instead of reading rows that were never written), and the next call reports DRONE_E_STATE.  Nothing here uses TMA or cluster multicast; peers are reached with plain
 // loads and stores.
 //
 // Why no host synchronisation is needed between calls: a rank stores into a peer's up-receive area in call k+1 only
@@ -62,48 +65,56 @@ __device__ bool wait_for_peers(const unsigned *flags, const int *need, int nrank
     return failed == 0;
 }
 
+// The wait as a launch of its own: one block polls, the kernel that follows in the stream does the work.
+__global__ void p2p_wait_kernel(const unsigned *flags, const int *need, int nranks, unsigned epoch, int *error,
+                                int *host_error, int code) {
+    wait_for_peers(flags, need, nranks, epoch, error, host_error, code);
+}
+
 template <int VEC> struct PVec;
 template <> struct PVec<4> { using type = float4; };
 template <> struct PVec<1> { using type = float; };
 __device__ __forceinline__ void vadd(float4 &a, const float4 &b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
 __device__ __forceinline__ void vadd(float &a, const float &b) { a += b; }
 
-// rows[up_rows[i], :] -> peer_up_recv[owner][dest_row[i], :]      (nvec = F / VEC vectors per row)
-// The list is walked in the order `order` gives: the mirror rows are grouped by owner, and walking them as they
-// lie would make every rank store to the same owner at the same time, whose NVLink ingress then limits all of them.
+// One mirror row of the walk: {local row, owner, row in the owner's up-receive area}.
+// rows[rec.x, :] -> peer_up_recv[rec.y][rec.z, :]      (nvec = F / VEC vectors per row)
+// The records lie in walk order: the mirror rows are grouped by owner, and walking them as they lie would make every
+// rank store to the same owner at the same time, whose NVLink ingress then limits all of them.
 template <int VEC>
-__global__ void p2p_push_up_kernel(const float *__restrict__ rows, long long ld, const int *__restrict__ up_rows,
-                                   const int *__restrict__ up_peer, const int *__restrict__ up_dest_row,
-                                   const int *__restrict__ order, int n_up, int nvec,
-                                   float *const *__restrict__ peer_up_recv) {
+__global__ void p2p_push_up_kernel(const float *__restrict__ rows, long long ld, const int4 *__restrict__ walk, int n_up,
+                                   int nvec, float *const *__restrict__ peer_up_recv, const int *error) {
     using V = typename PVec<VEC>::type;
+    if (*(volatile const int *)error != 0) return;      // an earlier wait of this rank gave up: stay silent
     const long long total = (long long)n_up * nvec;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int k = (int)(i / nvec), j = (int)(i - (long long)k * nvec);
-        const int r = order[k];
-        V *dst = reinterpret_cast<V *>(peer_up_recv[up_peer[r]]) + (long long)up_dest_row[r] * nvec + j;
-        *dst = *(reinterpret_cast<const V *>(rows + (long long)up_rows[r] * ld) + j);
+        const int4 rec = __ldg(walk + k);
+        V *dst = reinterpret_cast<V *>(peer_up_recv[rec.y]) + (long long)rec.z * nvec + j;
+        *dst = *(reinterpret_cast<const V *>(rows + (long long)rec.x * ld) + j);
     }
 }
 
 // After the stores of the preceding kernel: publish `epoch` in every peer that expects a flag from this rank.
+// A rank whose own wait ran out publishes nothing: its rows of this call were not written.
 __global__ void p2p_signal_kernel(unsigned *const *__restrict__ peer_flag, const int *__restrict__ send_to, int nranks,
-                                  unsigned epoch) {
+                                  unsigned epoch, const int *error) {
+    if (*(volatile const int *)error != 0) return;
     __threadfence_system();
     if ((int)threadIdx.x < nranks && send_to[threadIdx.x]) st_release_sys(peer_flag[threadIdx.x], epoch);
 }
 
 // Master rows: add the mirrors' rows (fixed order), keep the total, and store it into every mirror's down-receive area.
+// pairs[k] = {position of the contribution in my up-receive area, mirroring peer, row in that peer's down-receive area}
+// for the k-th (master, mirror) pair; the pairs of master m are m_off[m] .. m_off[m+1]-1, peers ascending.
 template <int VEC>
 __global__ void p2p_add_push_down_kernel(float *__restrict__ rows, long long ld, const int *__restrict__ m_rows,
-                                         const int *__restrict__ m_off, const int *__restrict__ m_pos, int n_masters,
-                                         int nvec, const float *up_recv, const int *__restrict__ down_peer,
-                                         const int *__restrict__ down_dest_row, float *const *__restrict__ peer_down_recv,
-                                         const unsigned *flags_up, const int *__restrict__ need_up, int nranks,
-                                         unsigned epoch, int *error, int *host_error) {
+                                         const int *__restrict__ m_off, const int4 *__restrict__ pairs, int n_masters,
+                                         int nvec, const float *up_recv, float *const *__restrict__ peer_down_recv,
+                                         const int *error) {
     using V = typename PVec<VEC>::type;
-    if (!wait_for_peers(flags_up, need_up, nranks, epoch, error, host_error, 100)) return;
+    if (*(volatile const int *)error != 0) return;      // the wait in front of this launch gave up
     const V *recv = reinterpret_cast<const V *>(up_recv);
     const long long total = (long long)n_masters * nvec;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -112,11 +123,11 @@ __global__ void p2p_add_push_down_kernel(float *__restrict__ rows, long long ld,
         V *mine = reinterpret_cast<V *>(rows + (long long)m_rows[m] * ld) + j;
         V acc = *mine;
         const int k0 = m_off[m], k1 = m_off[m + 1];
-        for (int k = k0; k < k1; ++k) vadd(acc, __ldcv(recv + (long long)m_pos[k] * nvec + j));
+        for (int k = k0; k < k1; ++k) vadd(acc, __ldcv(recv + (long long)__ldg(pairs + k).x * nvec + j));
         *mine = acc;
         for (int k = k0; k < k1; ++k) {
-            const int p = m_pos[k];
-            *(reinterpret_cast<V *>(peer_down_recv[down_peer[p]]) + (long long)down_dest_row[p] * nvec + j) = acc;
+            const int4 pr = __ldg(pairs + k);
+            *(reinterpret_cast<V *>(peer_down_recv[pr.y]) + (long long)pr.z * nvec + j) = acc;
         }
     }
 }
@@ -124,11 +135,9 @@ __global__ void p2p_add_push_down_kernel(float *__restrict__ rows, long long ld,
 // Mirror rows take the totals their masters stored.
 template <int VEC>
 __global__ void p2p_scatter_kernel(float *__restrict__ rows, long long ld, const int *__restrict__ up_rows, int n_up,
-                                   int nvec, const float *down_recv, const unsigned *flags_down,
-                                   const int *__restrict__ need_down, int nranks, unsigned epoch, int *error,
-                                   int *host_error) {
+                                   int nvec, const float *down_recv, const int *error) {
     using V = typename PVec<VEC>::type;
-    if (!wait_for_peers(flags_down, need_down, nranks, epoch, error, host_error, 200)) return;
+    if (*(volatile const int *)error != 0) return;
     const V *recv = reinterpret_cast<const V *>(down_recv);
     const long long total = (long long)n_up * nvec;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -168,7 +177,7 @@ void p2p_free(drone_p2p *p) {
         if (s) cudaIpcCloseMemHandle(s);
     cudaFree(p->segment);
     cudaFree(p->d_peer_up_recv); cudaFree(p->d_peer_down_recv); cudaFree(p->d_peer_flag_up); cudaFree(p->d_peer_flag_down);
-    cudaFree(p->d_up_peer); cudaFree(p->d_up_dest_row); cudaFree(p->d_up_order); cudaFree(p->d_down_peer); cudaFree(p->d_down_dest_row);
+    cudaFree(p->d_walk); cudaFree(p->d_pairs);
     cudaFree(p->d_need_up); cudaFree(p->d_need_down);
     if (p->h_error) cudaFreeHost(p->h_error);
     cudaFree(p->d_error);
@@ -188,59 +197,11 @@ void xplan_p2p_release(drone_xplan *x) {
 
 extern "C" {
 
-int drone_xplan_enable_p2p(drone_xplan *x, drone_comm *c, void *stream) {
-    DRONE_REQUIRE(x && c, "drone_xplan_enable_p2p: NULL plan or communicator");
-    DRONE_REQUIRE(c->nranks == x->nranks && c->rank == x->rank, "drone_xplan_enable_p2p: plan is rank %d/%d, comm %d/%d",
-                  x->rank, x->nranks, c->rank, c->nranks);
-    DRONE_REQUIRE(x->nranks <= 64, "drone_xplan_enable_p2p: at most 64 ranks");
-    if (x->p2p || x->nranks == 1) return DRONE_OK;
-    int rc = xplan_ensure_device(x);
-    if (rc) return rc;
-    cudaStream_t st = (cudaStream_t)stream;
+// What drone_xplan_enable_p2p does between its two collectives: reads the other ranks' records, maps their segments
+// and uploads this rank's tables.  Returns the first local failure; the caller folds it into the closing collective.
+static int p2p_connect(drone_xplan *x, drone_p2p *p, const std::vector<char> &all, size_t rec_bytes) {
     const int P = x->nranks, me = x->rank;
     const size_t n_up = x->up_rows.size(), n_down = x->down_rows.size();
-    drone_p2p *p = new (std::nothrow) drone_p2p();
-    if (!p) return set_error(DRONE_E_INVALID, "drone_xplan_enable_p2p: out of host memory");
-    x->p2p = p;   // released by drone_xplan_destroy, also after a failure below
-    p->peer_segment.assign(P, nullptr);
-
-    const size_t up_bytes = align_up(n_down * (size_t)x->max_features * 4, 256);
-    const size_t down_bytes = align_up(n_up * (size_t)x->max_features * 4, 256);
-    p->segment_bytes = kFlagBytes + up_bytes + down_bytes;
-    DRONE_CUDA(cudaMalloc(&p->segment, p->segment_bytes));
-    DRONE_CUDA(cudaMemsetAsync(p->segment, 0, p->segment_bytes, st));
-    DRONE_CUDA(cudaHostAlloc(&p->h_error, sizeof(int), cudaHostAllocMapped));
-    *p->h_error = 0;
-    DRONE_CUDA(cudaHostGetDevicePointer(&p->d_host_error, p->h_error, 0));
-    DRONE_CUDA(cudaMalloc(&p->d_error, sizeof(int)));
-    DRONE_CUDA(cudaMemsetAsync(p->d_error, 0, sizeof(int), st));
-
-    // what every rank tells the others: IPC handle, sizes, its two offset tables
-    const size_t ints_per_rank = 4 + 2 * (size_t)(P + 1);
-    const size_t rec_bytes = align_up(sizeof(cudaIpcMemHandle_t) + ints_per_rank * 4, 16);
-    std::vector<char> mine(rec_bytes, 0), all(rec_bytes * P, 0);
-    cudaIpcMemHandle_t handle;
-    DRONE_CUDA(cudaIpcGetMemHandle(&handle, p->segment));
-    memcpy(mine.data(), &handle, sizeof(handle));
-    int *ints = reinterpret_cast<int *>(mine.data() + sizeof(handle));
-    ints[0] = (int)n_down;
-    ints[1] = (int)n_up;
-    ints[2] = x->max_features;
-    ints[3] = 0;
-    for (int q = 0; q <= P; ++q) {
-        ints[4 + q] = x->down_off[q];
-        ints[4 + (P + 1) + q] = x->up_off[q];
-    }
-    char *d_mine = nullptr, *d_all = nullptr;
-    DRONE_CUDA(cudaMalloc(&d_mine, rec_bytes));
-    DRONE_CUDA(cudaMalloc(&d_all, rec_bytes * P));
-    DRONE_CUDA(cudaMemcpyAsync(d_mine, mine.data(), rec_bytes, cudaMemcpyHostToDevice, st));
-    DRONE_NCCL(ncclAllGather(d_mine, d_all, rec_bytes, ncclChar, c->comm, st));
-    DRONE_CUDA(cudaMemcpyAsync(all.data(), d_all, rec_bytes * P, cudaMemcpyDeviceToHost, st));
-    DRONE_CUDA(cudaStreamSynchronize(st));
-    cudaFree(d_mine);
-    cudaFree(d_all);
-
     std::vector<float *> up_base(P, nullptr), down_base(P, nullptr);
     std::vector<unsigned *> flag_up(P, nullptr), flag_down(P, nullptr);
     std::vector<int> need_up(P, 0), need_down(P, 0);
@@ -250,7 +211,6 @@ int drone_xplan_enable_p2p(drone_xplan *x, drone_comm *c, void *stream) {
         const int up_cnt = x->up_off[q + 1] - x->up_off[q], down_cnt = x->down_off[q + 1] - x->down_off[q];
         need_up[q] = down_cnt > 0;     // q holds mirrors of my masters: it sends up to me
         need_down[q] = up_cnt > 0;     // q owns masters of my mirrors: it sends down to me
-        if (!up_cnt && !down_cnt) continue;
         const char *rec = all.data() + rec_bytes * q;
         const int *qi = reinterpret_cast<const int *>(rec + sizeof(cudaIpcMemHandle_t));
         const int q_n_down = qi[0], q_maxf = qi[2];
@@ -260,6 +220,7 @@ int drone_xplan_enable_p2p(drone_xplan *x, drone_comm *c, void *stream) {
                              q_maxf, x->max_features);
         if (q_down_off[me + 1] - q_down_off[me] != up_cnt || q_up_off[me + 1] - q_up_off[me] != down_cnt)
             return set_error(DRONE_E_STATE, "drone_xplan_enable_p2p: plans of rank %d and %d disagree on their row counts", me, q);
+        if (!up_cnt && !down_cnt) continue;
         cudaIpcMemHandle_t qh;
         memcpy(&qh, rec, sizeof(qh));
         void *mapped = nullptr;
@@ -281,38 +242,132 @@ int drone_xplan_enable_p2p(drone_xplan *x, drone_comm *c, void *stream) {
     }
     // Walk order of push_up: runs of kRun rows taken in turn from every owner's group, starting with the rank after
     // this one, so that at any time a rank stores to all owners and no two ranks start on the same one.
-    std::vector<int> up_order;
-    up_order.reserve(n_up);
+    std::vector<int4> walk;
+    walk.reserve(n_up);
     {
         const int kRun = 16;
         std::vector<int> next(P);
         for (int q = 0; q < P; ++q) next[q] = x->up_off[q];
-        while (up_order.size() < n_up)
+        while (walk.size() < n_up)
             for (int d = 1; d <= P; ++d) {
                 const int q = (me + d) % P;
                 const int end = std::min(next[q] + kRun, x->up_off[q + 1]);
-                for (int i = next[q]; i < end; ++i) up_order.push_back(i);
+                for (int i = next[q]; i < end; ++i) walk.push_back(make_int4(x->up_rows[i], up_peer[i], up_dest[i], 0));
                 next[q] = end;
             }
     }
-    if ((rc = upload_vec(&p->d_up_order, up_order))) return rc;
+    std::vector<int4> pairs(x->m_pos.size());
+    for (size_t k = 0; k < pairs.size(); ++k) {
+        const int pos = x->m_pos[k];
+        pairs[k] = make_int4(pos, down_peer[pos], down_dest[pos], 0);
+    }
+    int rc;
+    if ((rc = upload_vec(&p->d_walk, walk))) return rc;
+    if ((rc = upload_vec(&p->d_pairs, pairs))) return rc;
     if ((rc = upload_vec(&p->d_peer_up_recv, up_base))) return rc;
     if ((rc = upload_vec(&p->d_peer_down_recv, down_base))) return rc;
     if ((rc = upload_vec(&p->d_peer_flag_up, flag_up))) return rc;
     if ((rc = upload_vec(&p->d_peer_flag_down, flag_down))) return rc;
-    if ((rc = upload_vec(&p->d_up_peer, up_peer))) return rc;
-    if ((rc = upload_vec(&p->d_up_dest_row, up_dest))) return rc;
-    if ((rc = upload_vec(&p->d_down_peer, down_peer))) return rc;
-    if ((rc = upload_vec(&p->d_down_dest_row, down_dest))) return rc;
     if ((rc = upload_vec(&p->d_need_up, need_up))) return rc;
     if ((rc = upload_vec(&p->d_need_down, need_down))) return rc;
-    // nobody may store into a segment before every rank has mapped what it needs: one more collective
-    float *d_token = nullptr;
-    DRONE_CUDA(cudaMalloc(&d_token, sizeof(float)));
-    DRONE_CUDA(cudaMemsetAsync(d_token, 0, sizeof(float), st));
-    DRONE_NCCL(ncclAllReduce(d_token, d_token, 1, ncclFloat, ncclSum, c->comm, st));
-    DRONE_CUDA(cudaStreamSynchronize(st));
-    cudaFree(d_token);
+    return DRONE_OK;
+}
+
+int drone_xplan_enable_p2p(drone_xplan *x, drone_comm *c, void *stream) {
+    DRONE_REQUIRE(x && c, "drone_xplan_enable_p2p: NULL plan or communicator");
+    DRONE_REQUIRE(c->nranks == x->nranks && c->rank == x->rank, "drone_xplan_enable_p2p: plan is rank %d/%d, comm %d/%d",
+                  x->rank, x->nranks, c->rank, c->nranks);
+    DRONE_REQUIRE(x->nranks <= 64, "drone_xplan_enable_p2p: at most 64 ranks");
+    if (x->p2p || x->nranks == 1) return DRONE_OK;
+    int rc = xplan_ensure_device(x);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int P = x->nranks;
+    const size_t n_up = x->up_rows.size(), n_down = x->down_rows.size();
+
+    // Everything that can fail on this rank alone comes first: a rank that returns from here has started no
+    // collective, so its peers are not left inside one that this rank never joins half-way.
+    struct Temp {
+        char *d_mine = nullptr, *d_all = nullptr;
+        int *d_status = nullptr;
+        ~Temp() { cudaFree(d_mine); cudaFree(d_all); cudaFree(d_status); }
+    } t;
+    const size_t ints_per_rank = 4 + 2 * (size_t)(P + 1);
+    const size_t rec_bytes = align_up(sizeof(cudaIpcMemHandle_t) + ints_per_rank * 4, 16);
+    drone_p2p *p = new (std::nothrow) drone_p2p();
+    if (!p) return set_error(DRONE_E_INVALID, "drone_xplan_enable_p2p: out of host memory");
+    x->p2p = p;
+    p->peer_segment.assign(P, nullptr);
+    const size_t up_bytes = align_up(n_down * (size_t)x->max_features * 4, 256);
+    const size_t down_bytes = align_up(n_up * (size_t)x->max_features * 4, 256);
+    p->segment_bytes = kFlagBytes + up_bytes + down_bytes;
+    std::vector<char> mine(rec_bytes, 0), all(rec_bytes * P, 0);
+    auto local_setup = [&]() -> int {
+        DRONE_CUDA(cudaMalloc(&p->segment, p->segment_bytes));
+        DRONE_CUDA(cudaMemsetAsync(p->segment, 0, p->segment_bytes, st));
+        DRONE_CUDA(cudaHostAlloc(&p->h_error, sizeof(int), cudaHostAllocMapped));
+        *p->h_error = 0;
+        DRONE_CUDA(cudaHostGetDevicePointer(&p->d_host_error, p->h_error, 0));
+        DRONE_CUDA(cudaMalloc(&p->d_error, sizeof(int)));
+        DRONE_CUDA(cudaMemsetAsync(p->d_error, 0, sizeof(int), st));
+        DRONE_CUDA(cudaMalloc(&t.d_mine, rec_bytes));
+        DRONE_CUDA(cudaMalloc(&t.d_all, rec_bytes * P));
+        DRONE_CUDA(cudaMalloc(&t.d_status, sizeof(int)));
+        // what every rank tells the others: IPC handle, sizes, its two offset tables
+        cudaIpcMemHandle_t handle;
+        DRONE_CUDA(cudaIpcGetMemHandle(&handle, p->segment));
+        memcpy(mine.data(), &handle, sizeof(handle));
+        int *ints = reinterpret_cast<int *>(mine.data() + sizeof(handle));
+        ints[0] = (int)n_down;
+        ints[1] = (int)n_up;
+        ints[2] = x->max_features;
+        ints[3] = 0;
+        for (int q = 0; q <= P; ++q) {
+            ints[4 + q] = x->down_off[q];
+            ints[4 + (P + 1) + q] = x->up_off[q];
+        }
+        DRONE_CUDA(cudaMemcpyAsync(t.d_mine, mine.data(), rec_bytes, cudaMemcpyHostToDevice, st));
+        return DRONE_OK;
+    };
+    if ((rc = local_setup())) {
+        xplan_p2p_release(x);
+        return rc;
+    }
+
+    // first collective: everybody's record
+    auto gather = [&]() -> int {
+        DRONE_NCCL(ncclAllGather(t.d_mine, t.d_all, rec_bytes, ncclChar, c->comm, st));
+        DRONE_CUDA(cudaMemcpyAsync(all.data(), t.d_all, rec_bytes * P, cudaMemcpyDeviceToHost, st));
+        DRONE_CUDA(cudaStreamSynchronize(st));
+        return DRONE_OK;
+    };
+    int status = gather();
+    char first_message[512] = "";
+    if (status == DRONE_OK) status = p2p_connect(x, p, all, rec_bytes);
+    if (status != DRONE_OK) snprintf(first_message, sizeof(first_message), "%s", drone_last_error());
+
+    // Closing collective, joined by every rank whatever happened above: nobody may store into a segment before every
+    // rank has mapped what it needs, and a rank that failed must not leave the others waiting inside the collective.
+    // It carries the status: the smallest (most severe) code of any rank comes back on all of them.
+    int agreed = status;
+    auto close = [&]() -> int {
+        DRONE_CUDA(cudaMemcpyAsync(t.d_status, &status, sizeof(int), cudaMemcpyHostToDevice, st));
+        DRONE_NCCL(ncclAllReduce(t.d_status, t.d_status, 1, ncclInt, ncclMin, c->comm, st));
+        DRONE_CUDA(cudaMemcpyAsync(&agreed, t.d_status, sizeof(int), cudaMemcpyDeviceToHost, st));
+        DRONE_CUDA(cudaStreamSynchronize(st));
+        return DRONE_OK;
+    };
+    const int close_rc = close();
+    if (close_rc != DRONE_OK && status == DRONE_OK) {
+        status = agreed = close_rc;
+        snprintf(first_message, sizeof(first_message), "%s", drone_last_error());
+    }
+    if (agreed != DRONE_OK) {
+        xplan_p2p_release(x);     // unmaps the peers' segments, frees this rank's; the plan keeps its NCCL transport
+        if (status != DRONE_OK) return set_error(agreed, "%s", first_message);
+        return set_error(agreed, "drone_xplan_enable_p2p: another rank failed to set the transport up (code %d); "
+                         "it is off on every rank", agreed);
+    }
     return DRONE_OK;
 }
 
@@ -347,7 +402,7 @@ struct PhaseTimer {
         cudaStreamSynchronize(st);
         float ms[5] = {0, 0, 0, 0, 0};
         for (int i = 0; i + 1 < n; ++i) cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]);
-        fprintf(stderr, "p2p rank %d: push_up %.3f signal %.3f add_push_down %.3f signal %.3f scatter %.3f ms (n_up %d n_m %d F %d)\n",
+        fprintf(stderr, "p2p rank %d: push_up %.3f signal %.3f wait+add_push_down %.3f signal %.3f wait+scatter %.3f ms (n_up %d n_m %d F %d)\n",
                 rank, ms[0], ms[1], ms[2], ms[3], ms[4], n_up, n_m, F);
         for (auto &e : ev) cudaEventDestroy(e);
     }
@@ -373,28 +428,32 @@ int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t 
     timer.mark();
     if (n_up) {
         const int grid = p2p_grid((long long)n_up * nvec);
-        if (vec4) p2p_push_up_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, p->d_up_peer, p->d_up_dest_row, p->d_up_order, n_up, nvec, p->d_peer_up_recv);
-        else p2p_push_up_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, p->d_up_peer, p->d_up_dest_row, p->d_up_order, n_up, nvec, p->d_peer_up_recv);
+        if (vec4) p2p_push_up_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error);
+        else p2p_push_up_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error);
         DRONE_LAUNCH_CHECK("p2p_push_up_kernel");
     }
     timer.mark();
-    p2p_signal_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_up, p->d_need_down, P, epoch);   // to the owners of my mirrors
+    p2p_signal_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_up, p->d_need_down, P, epoch, p->d_error);   // to the owners of my mirrors
     DRONE_LAUNCH_CHECK("p2p_signal_kernel");
     timer.mark();
     if (n_m) {
+        p2p_wait_kernel<<<1, 64, 0, st>>>(my_flags, p->d_need_up, P, epoch, p->d_error, p->d_host_error, 100);
+        DRONE_LAUNCH_CHECK("p2p_wait_kernel");
         const int grid = p2p_grid((long long)n_m * nvec);
-        if (vec4) p2p_add_push_down_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, x->d_m_pos, n_m, nvec, my_up_recv, p->d_down_peer, p->d_down_dest_row, p->d_peer_down_recv, my_flags, p->d_need_up, P, epoch, p->d_error, p->d_host_error);
-        else p2p_add_push_down_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, x->d_m_pos, n_m, nvec, my_up_recv, p->d_down_peer, p->d_down_dest_row, p->d_peer_down_recv, my_flags, p->d_need_up, P, epoch, p->d_error, p->d_host_error);
+        if (vec4) p2p_add_push_down_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, p->d_pairs, n_m, nvec, my_up_recv, p->d_peer_down_recv, p->d_error);
+        else p2p_add_push_down_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, p->d_pairs, n_m, nvec, my_up_recv, p->d_peer_down_recv, p->d_error);
         DRONE_LAUNCH_CHECK("p2p_add_push_down_kernel");
     }
     timer.mark();
-    p2p_signal_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_down, p->d_need_up, P, epoch);   // to the holders of my mirrors
+    p2p_signal_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_down, p->d_need_up, P, epoch, p->d_error);   // to the holders of my mirrors
     DRONE_LAUNCH_CHECK("p2p_signal_kernel");
     timer.mark();
     if (n_up) {
+        p2p_wait_kernel<<<1, 64, 0, st>>>(my_flags + P, p->d_need_down, P, epoch, p->d_error, p->d_host_error, 200);
+        DRONE_LAUNCH_CHECK("p2p_wait_kernel");
         const int grid = p2p_grid((long long)n_up * nvec);
-        if (vec4) p2p_scatter_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, n_up, nvec, my_down_recv, my_flags + P, p->d_need_down, P, epoch, p->d_error, p->d_host_error);
-        else p2p_scatter_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, n_up, nvec, my_down_recv, my_flags + P, p->d_need_down, P, epoch, p->d_error, p->d_host_error);
+        if (vec4) p2p_scatter_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, n_up, nvec, my_down_recv, p->d_error);
+        else p2p_scatter_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, n_up, nvec, my_down_recv, p->d_error);
         DRONE_LAUNCH_CHECK("p2p_scatter_kernel");
     }
     timer.mark();

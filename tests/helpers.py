@@ -42,3 +42,35 @@ def graph_case(gg, oracle, n, u, v, clamp_degrees=True):
     index, dst = index.numpy(), dst.numpy()
     val = oracle.csr_values_f32(index, dst, in_deg, out_deg)
     return index, dst, in_deg, out_deg, val
+
+
+def run_ranks(target, world, extra_args=(), timeout=300):
+    """Run target(rank, world, *extra_args, ok) as `world` spawned processes (one per GPU), `ok` being a shared int
+    array every rank sets to 1 at its end.  Ranks still alive at the time limit, or after a sibling has already failed
+    (they may be waiting for it inside a collective on the GPU), are terminated before anything is asserted, so that
+    a failing rank cannot leave its peer behind."""
+    import time
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ok = ctx.Array("i", [0] * world)
+    procs = [ctx.Process(target=target, args=(r, world, *extra_args, ok)) for r in range(world)]
+    try:
+        for p in procs:
+            p.start()
+        deadline = time.time() + timeout
+        while time.time() < deadline and any(p.is_alive() for p in procs):
+            if any(p.exitcode not in (None, 0) for p in procs):
+                time.sleep(5)          # a rank failed: give the others a moment to leave on their own, then stop them
+                break
+            time.sleep(0.2)
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
+    assert [p.exitcode for p in procs] == [0] * world, "exit codes %r" % [p.exitcode for p in procs]
+    assert list(ok) == [1] * world

@@ -11,7 +11,7 @@ import torch
 import drone_b200 as db
 from drone_b200 import graphgen as gg
 from drone_b200 import partition as pt
-from helpers import ROOT, assert_close_to_oracle, graph_case
+from helpers import run_ranks, ROOT, assert_close_to_oracle, graph_case
 from test_pagerank_oracle import pr_case
 
 pytestmark = pytest.mark.gpu
@@ -296,13 +296,4 @@ def _two_workers(rank, world, workdir, ok):
 def test_c_interfaces_two_workers(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    ok = ctx.Array("i", [0, 0])
-    procs = [ctx.Process(target=_two_workers, args=(r, 2, str(tmp_path), ok)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-    assert all(p.exitcode == 0 for p in procs)
-    assert list(ok) == [1, 1]
+    run_ranks(_two_workers, 2, (str(tmp_path),))

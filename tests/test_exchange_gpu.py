@@ -10,7 +10,7 @@ import drone_b200 as db
 from drone_b200 import graphgen as gg
 from drone_b200 import graphsum as gs
 from drone_b200 import partition as pt
-from helpers import assert_close_to_oracle
+from helpers import run_ranks, assert_close_to_oracle
 from test_exchange_cpu import setup_case
 
 pytestmark = pytest.mark.gpu
@@ -209,39 +209,67 @@ def _lonely_rank(rank, world, port, ok):
             with pytest.raises(db.DroneError, match="gave up waiting for rank 1"):
                 gs.exchange_sum(g.xplan, comm, rows)
             assert float(torch.ones(4, device=dev).sum()) == 4.0    # the context is still usable
+        dist.barrier()
+        if rank == 1:
+            # the call rank 0 gave up on, made late: rank 0 published its rows of that call before its wait ran out,
+            # but no totals afterwards, so this rank must not take stale totals for good ones: its own wait runs out
+            t0 = time.time()
+            gs.exchange_sum(g.xplan, comm, rows)
+            torch.cuda.synchronize()
+            assert time.time() - t0 < 30
+            with pytest.raises(db.DroneError, match="gave up waiting for rank 0"):
+                gs.exchange_sum(g.xplan, comm, rows)
+            assert float(torch.ones(4, device=dev).sum()) == 4.0
         ok[rank] = 1
         dist.barrier()
     finally:
         dist.destroy_process_group()
 
 
+def _mismatched_rank(rank, world, port, ok):
+    """The two ranks plan for different feature widths: switching the peer-memory transport on fails with the same
+    code on both (nobody is left inside a collective), and the NCCL transport still works afterwards."""
+    import torch.distributed as dist
+    from oracle import oracle
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        f = 8
+        n, part, in_deg, out_deg, x, want_fwd, _ = setup_case(oracle, world, scale=9, seed=13, f=f, sym=True)
+        comm = gs.Comm(rank, world)
+        g = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, dev, max_features=f if rank == 0 else 2 * f)
+        with pytest.raises(db.DroneError) as err:
+            g.xplan.enable_p2p(comm)
+        assert err.value.code == -1 and "planned for" in str(err.value)
+        dist.barrier()
+        rows = g.plan.spmm(db.OP_AT, torch.as_tensor(x[g.host.l2g], device=dev))
+        gs.exchange_sum(g.xplan, comm, rows)            # grouped send/recv, as before the attempt
+        torch.cuda.synchronize()
+        assert_close_to_oracle(rows.cpu().numpy(), want_fwd[g.host.l2g])
+        ok[rank] = 1
+        dist.barrier()
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_transport_setup_fails_on_every_rank_together():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    run_ranks(_mismatched_rank, 2, (29100 + os.getpid() % 2000,))
+
+
 def test_peer_wait_runs_out_instead_of_hanging():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    ok = ctx.Array("i", [0, 0])
-    port = 29900 + os.getpid() % 2000
-    procs = [ctx.Process(target=_lonely_rank, args=(r, 2, port, ok)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-    assert all(p.exitcode == 0 for p in procs)
-    assert list(ok) == [1, 1]
+    run_ranks(_lonely_rank, 2, (29900 + os.getpid() % 2000,))
+
 
 
 def test_graphsum_over_nccl_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    ok = ctx.Array("i", [0, 0])
-    port = 29600 + os.getpid() % 2000
-    procs = [ctx.Process(target=_nccl_rank, args=(r, 2, port, ok)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-    assert all(p.exitcode == 0 for p in procs)
-    assert list(ok) == [1, 1]
+    run_ranks(_nccl_rank, 2, (29600 + os.getpid() % 2000,))

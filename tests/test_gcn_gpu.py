@@ -8,7 +8,7 @@ import torch
 
 import drone_b200 as db
 from drone_b200 import gcn, graphgen as gg, graphsum as gs, partition as pt
-from helpers import graph_case
+from helpers import run_ranks, graph_case
 from oracle import gcn_oracle
 
 pytestmark = pytest.mark.gpu
@@ -94,14 +94,4 @@ def _rank(rank, world, port, ok):
 def test_gcn_step_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    ok = ctx.Array("i", [0, 0])
-    port = 29800 + os.getpid() % 2000
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, ok)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-    assert all(p.exitcode == 0 for p in procs)
-    assert list(ok) == [1, 1]
+    run_ranks(_rank, 2, (29800 + os.getpid() % 2000,))

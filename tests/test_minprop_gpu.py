@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import drone_b200 as db
+from helpers import run_ranks
 from drone_b200 import graphgen as gg
 from drone_b200 import graphsum as gs
 from drone_b200 import minprop as mp
@@ -158,14 +159,4 @@ def _rank(rank, world, port, ok):
 def test_jobs_over_nccl_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as tmp
-    ctx = tmp.get_context("spawn")
-    ok = ctx.Array("i", [0, 0])
-    port = 29300 + os.getpid() % 2000
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, ok)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-    assert all(p.exitcode == 0 for p in procs)
-    assert list(ok) == [1, 1]
+    run_ranks(_rank, 2, (29300 + os.getpid() % 2000,))

@@ -8,6 +8,7 @@ import pytest
 import torch
 
 import drone_b200 as db
+from helpers import run_ranks
 from drone_b200 import graphgen as gg
 from drone_b200 import graphsum as gs
 from drone_b200 import pagerank as prk
@@ -154,14 +155,4 @@ def _nccl_rank(rank, world, port, ok):
 def test_pagerank_over_nccl_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    ok = ctx.Array("i", [0, 0])
-    port = 29700 + os.getpid() % 2000
-    procs = [ctx.Process(target=_nccl_rank, args=(r, 2, port, ok)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-    assert all(p.exitcode == 0 for p in procs)
-    assert list(ok) == [1, 1]
+    run_ranks(_nccl_rank, 2, (29700 + os.getpid() % 2000,))
