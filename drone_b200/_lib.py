@@ -34,6 +34,16 @@ class PRResponse(C.Structure):
                 self.Master2MirrorSendSize == 0 and self.Master2MirrorRecvSize == 0)
 
 
+class SpmmOpts(C.Structure):
+    """drone_spmm_opts of include/drone_b200.h."""
+    _fields_ = [("epilogue", C.c_int), ("row_class", C.c_int), ("unit_values", C.c_int), ("reserved_", C.c_int),
+                ("d_row_scale", C.c_void_p)]
+
+
+EPILOGUE_NONE = 0
+EPILOGUE_RELU = 1
+
+
 class PlanStats(C.Structure):
     _fields_ = [
         ("n_rows", C.c_int),
@@ -66,6 +76,8 @@ def _declare(lib):
         "drone_plan_get_csr": (i, [vp, i, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
         "drone_spmm": (i, [vp, i, i, vp, i, vp, i, vp]),
         "drone_plan_reserve": (i, [vp, i, i]),
+        "drone_spmm_ex": (i, [vp, i, i, vp, i, vp, i, C.POINTER(SpmmOpts), vp]),
+        "drone_degree_scales": (i, [vp, vp, i, vp, vp, vp]),
         "drone_plan_set_row_classes": (i, [vp, vp, i, vp]),
         "drone_spmm_rows": (i, [vp, i, i, i, vp, i, vp, i, vp]),
         "drone_spmm_host": (i, [vp, i, i, vp, vp]),
@@ -77,6 +89,9 @@ def _declare(lib):
         "drone_comm_adopt": (i, [C.POINTER(vp), vp, i, i]),
         "drone_comm_destroy": (i, [vp]),
         "drone_comm_allreduce_sum": (i, [vp, vp, C.c_size_t, i, vp]),
+        "drone_comm_bcast": (i, [vp, vp, C.c_size_t, i, vp]),
+        "drone_comm_reduce_sum": (i, [vp, vp, C.c_size_t, i, vp]),
+        "drone_clear_mirror_rows": (i, [vp, i, i, i, vp, vp]),
         "drone_xplan_create": (i, [C.POINTER(vp), i, i, i, vp, vp, vp, vp, i]),
         "drone_xplan_destroy": (i, [vp]),
         "drone_xplan_enable_p2p": (i, [vp, vp, vp]),

@@ -23,6 +23,18 @@ int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t 
 void xplan_p2p_release(drone_xplan *x);
 
 // buf[i, 0:F] = rows[list[i], 0:F]
+// rows[r, 0:nvec] = 0 for every row r that is a mirror (mirror2worker[r] != -1); V = float4 or float.
+template <typename V>
+__global__ void clear_mirror_rows_kernel(float *__restrict__ rows, int n_rows, int nvec, long long ld,
+                                         const int *__restrict__ mirror2worker) {
+    const long long total = (long long)n_rows * nvec;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / nvec), j = (int)(i - (long long)r * nvec);
+        if (mirror2worker[r] != -1) reinterpret_cast<V *>(rows + (long long)r * ld)[j] = V{};
+    }
+}
+
 __global__ void gather_rows_kernel(const float *__restrict__ rows, long long ld, const int *__restrict__ list,
                                    int n_list, int F, float *__restrict__ buf) {
     const long long total = (long long)n_list * F;
@@ -168,6 +180,35 @@ int drone_comm_allreduce_sum(drone_comm *c, void *d_buf, size_t count, int is_do
     if (c->nranks == 1 || count == 0) return DRONE_OK;
     DRONE_NCCL(ncclAllReduce(d_buf, d_buf, count, is_double ? ncclDouble : ncclFloat, ncclSum, c->comm,
                              (cudaStream_t)stream));
+    return DRONE_OK;
+}
+
+int drone_comm_bcast(drone_comm *c, float *d_buf, size_t count, int root, void *stream) {
+    DRONE_REQUIRE(c && d_buf, "drone_comm_bcast: NULL argument");
+    DRONE_REQUIRE(root >= 0 && root < c->nranks, "drone_comm_bcast: root %d of %d ranks", root, c->nranks);
+    if (c->nranks == 1 || count == 0) return DRONE_OK;
+    DRONE_NCCL(ncclBroadcast(d_buf, d_buf, count, ncclFloat, root, c->comm, (cudaStream_t)stream));
+    return DRONE_OK;
+}
+
+int drone_comm_reduce_sum(drone_comm *c, float *d_buf, size_t count, int root, void *stream) {
+    DRONE_REQUIRE(c && d_buf, "drone_comm_reduce_sum: NULL argument");
+    DRONE_REQUIRE(root >= 0 && root < c->nranks, "drone_comm_reduce_sum: root %d of %d ranks", root, c->nranks);
+    if (c->nranks == 1 || count == 0) return DRONE_OK;
+    DRONE_NCCL(ncclReduce(d_buf, d_buf, count, ncclFloat, ncclSum, root, c->comm, (cudaStream_t)stream));
+    return DRONE_OK;
+}
+
+int drone_clear_mirror_rows(float *d_rows, int n_rows, int F, int ld, const int *d_mirror2worker, void *stream) {
+    DRONE_REQUIRE(n_rows >= 0 && F >= 1 && ld >= F, "drone_clear_mirror_rows: n_rows=%d F=%d ld=%d", n_rows, F, ld);
+    if (n_rows == 0) return DRONE_OK;
+    DRONE_REQUIRE(d_rows && d_mirror2worker, "drone_clear_mirror_rows: NULL argument");
+    const bool vec4 = (F % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_rows) & 15) == 0);
+    const long long total = (long long)n_rows * (vec4 ? F / 4 : F);
+    const int grid = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+    if (vec4) clear_mirror_rows_kernel<float4><<<grid, 256, 0, (cudaStream_t)stream>>>(d_rows, n_rows, F / 4, ld, d_mirror2worker);
+    else clear_mirror_rows_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(d_rows, n_rows, F, ld, d_mirror2worker);
+    DRONE_LAUNCH_CHECK("clear_mirror_rows_kernel");
     return DRONE_OK;
 }
 

@@ -732,7 +732,7 @@ int drone_pr_create(drone_pr **out, int n_local, int global_v, int nnz, const in
         float *ones = nullptr;
         if (cudaMalloc(&ones, sizeof(float) * (size_t)(nnz > 0 ? nnz : 1)) != cudaSuccess) { rc = set_error(DRONE_E_CUDA, "drone_pr_create: out of device memory"); break; }
         cudaMemset(ones, 0, sizeof(float) * (size_t)(nnz > 0 ? nnz : 1));
-        rc = drone_plan_create(&p->plan, n_local, nnz, d_index, d_dst, ones, nullptr, nullptr, DRONE_PLAN_AT, nullptr);
+        rc = plan_create_untagged(&p->plan, n_local, nnz, d_index, d_dst, ones, nullptr, nullptr, DRONE_PLAN_AT, nullptr);
         cudaFree(ones);
         if (rc) break;
         cudaError_t e = cudaSuccess;

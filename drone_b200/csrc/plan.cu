@@ -254,6 +254,35 @@ __global__ void check_csr_kernel(const int *__restrict__ rowptr, const int *__re
     }
 }
 
+// freq[c] = rowptr[c + 1] - rowptr[c]: how often column c occurs in the other orientation's CSR
+__global__ void row_lengths_kernel(const int *__restrict__ rowptr, int n, int *__restrict__ freq) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        freq[i] = rowptr[i + 1] - rowptr[i];
+}
+
+// position_of[hot_ids[pos]] = pos for pos < n_hot (position_of was filled with -1)
+__global__ void scatter_positions_kernel(const int *__restrict__ hot_ids, int n_hot, int *__restrict__ position_of) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_hot; i += (long long)gridDim.x * blockDim.x)
+        position_of[hot_ids[i]] = (int)i;
+}
+
+// col[k] = kHotTag | position for the columns that have a position in the table of hot rows
+__global__ void tag_columns_kernel(int *__restrict__ col, long long nnz, const int *__restrict__ position_of) {
+    for (long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x; k < nnz; k += (long long)gridDim.x * blockDim.x) {
+        const int pos = __ldg(position_of + col[k]);
+        if (pos >= 0) col[k] = (int)(kHotTag | (unsigned)pos);
+    }
+}
+
+// plain[k] = the column a possibly tagged entry stands for
+__global__ void untag_columns_kernel(const int *__restrict__ col, long long nnz, const int *__restrict__ hot_ids,
+                                     int *__restrict__ plain) {
+    for (long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x; k < nnz; k += (long long)gridDim.x * blockDim.x) {
+        const unsigned c = (unsigned)col[k];
+        plain[k] = (c & kHotTag) ? __ldg(hot_ids + (c & kHotMask)) : (int)c;
+    }
+}
+
 static inline int grid_for(long long n, int block = 256, int cap = 148 * 32) {
     long long g = (n + block - 1) / block;
     if (g < 1) g = 1;
@@ -273,6 +302,8 @@ static int env_int(const char *name, int dflt) {
 }
 
 static void free_side(Side &s) {
+    cudaFree(s.hot_ids);
+    cudaFree(s.col_plain);
     cudaFree(s.rowptr);
     cudaFree(s.col);
     cudaFree(s.val);
@@ -504,6 +535,50 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
     return DRONE_OK;
 }
 
+// Tags the n_hot most often gathered columns of one orientation: col entries become kHotTag | position, hot_ids
+// lists the columns by position (most frequent first, ties by ascending column).  `other_rowptr` is the row pointer of
+// the opposite orientation (its row lengths are this orientation's column frequencies) or NULL (then they are counted).
+static int tag_hot_columns(drone_plan *p, Side &s, const int *other_rowptr, int n_hot, cudaStream_t st) {
+    const int n = p->n_rows;
+    const long long nnz = p->nnz;
+    struct Temp {
+        int *freq = nullptr, *ids = nullptr, *freq_sorted = nullptr, *ids_sorted = nullptr, *position_of = nullptr;
+        void *sort = nullptr;
+        ~Temp() { cudaFree(freq); cudaFree(ids); cudaFree(freq_sorted); cudaFree(ids_sorted); cudaFree(position_of); cudaFree(sort); }
+    } t;
+    const size_t bytes = sizeof(int) * (size_t)(n + 1);
+    DRONE_CUDA(cudaMalloc(&t.freq, bytes));
+    DRONE_CUDA(cudaMalloc(&t.ids, bytes));
+    DRONE_CUDA(cudaMalloc(&t.freq_sorted, bytes));
+    DRONE_CUDA(cudaMalloc(&t.ids_sorted, bytes));
+    DRONE_CUDA(cudaMalloc(&t.position_of, bytes));
+    if (other_rowptr) {
+        row_lengths_kernel<<<grid_for(n), 256, 0, st>>>(other_rowptr, n, t.freq);
+        DRONE_LAUNCH_CHECK("row_lengths_kernel");
+    } else {
+        DRONE_CUDA(cudaMemsetAsync(t.freq, 0, bytes, st));
+        histogram_kernel<<<grid_for(nnz), 256, 0, st>>>(s.col, (int)nnz, t.freq);
+        DRONE_LAUNCH_CHECK("histogram_kernel");
+    }
+    iota_kernel<<<grid_for(n), 256, 0, st>>>(t.ids, n);
+    DRONE_LAUNCH_CHECK("iota_kernel");
+    size_t tmp_bytes = 0;
+    DRONE_CUDA(cub::DeviceRadixSort::SortPairsDescending(nullptr, tmp_bytes, t.freq, t.freq_sorted, t.ids, t.ids_sorted, n, 0, 32, st));
+    DRONE_CUDA(cudaMalloc(&t.sort, tmp_bytes > 0 ? tmp_bytes : 1));
+    DRONE_CUDA(cub::DeviceRadixSort::SortPairsDescending(t.sort, tmp_bytes, t.freq, t.freq_sorted, t.ids, t.ids_sorted, n, 0, 32, st));
+    count_launch();
+    DRONE_CUDA(cudaMalloc(&s.hot_ids, sizeof(int) * (size_t)n_hot));
+    DRONE_CUDA(cudaMemcpyAsync(s.hot_ids, t.ids_sorted, sizeof(int) * (size_t)n_hot, cudaMemcpyDeviceToDevice, st));
+    s.n_hot = n_hot;
+    DRONE_CUDA(cudaMemsetAsync(t.position_of, 0xff, bytes, st));
+    scatter_positions_kernel<<<grid_for(n_hot), 256, 0, st>>>(s.hot_ids, n_hot, t.position_of);
+    DRONE_LAUNCH_CHECK("scatter_positions_kernel");
+    tag_columns_kernel<<<grid_for(nnz), 256, 0, st>>>(s.col, nnz, t.position_of);
+    DRONE_LAUNCH_CHECK("tag_columns_kernel");
+    DRONE_CUDA(cudaStreamSynchronize(st));
+    return DRONE_OK;
+}
+
 // Checks d_index / d_col before anything indexes with them: a column outside the matrix would otherwise become an
 // out-of-bounds access in the histogram of the transpose and in every gather of the aggregation.
 int validate_csr(const char *who, const int *d_index, const int *d_col, int n_rows, int n_cols, int nnz, cudaStream_t st) {
@@ -530,7 +605,7 @@ int validate_csr(const char *who, const int *d_index, const int *d_col, int n_ro
 
 static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_index, const int *d_dst,
                             const float *d_values, const int *d_in_degree, const int *d_out_degree,
-                            int orientations, cudaStream_t st) {
+                            int orientations, cudaStream_t st, bool allow_tags) {
     DRONE_CUDA(cudaGetDevice(&p->device));
     {
         const int rc = validate_csr("drone_plan_create", d_index, d_dst, n_rows, n_rows, nnz, st);
@@ -571,10 +646,34 @@ static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_ind
         DRONE_CUDA(cudaEventCreateWithFlags(&p->fork_event, cudaEventDisableTiming));
         DRONE_CUDA(cudaEventCreateWithFlags(&p->join_event, cudaEventDisableTiming));
     }
+    DRONE_CUDA(cudaMalloc(&p->counter, sizeof(unsigned)));
+    p->chunk_blocks_per_sm = env_int("DRONE_CHUNK_BLOCKS_PER_SM", 0);
     if (orientations & DRONE_PLAN_AT) {
-        int rc = build_transpose(p, st);
+        const int rc = build_transpose(p, st);
         if (rc) return rc;
-        rc = build_work_lists(p, p->side[DRONE_OP_AT], st);
+    }
+    // Table of hot rows: only for graphs whose dense operand is far larger than L2 at the usual widths.  Its size
+    // is DRONE_HOT_TABLE_MB (default 64; 0 switches it off); a position is tagged for as many rows as fit at a width
+    // of 32 floats, calls with wider rows use a prefix of the positions.
+    {
+        const char *mb = getenv("DRONE_HOT_TABLE_MB");
+        const long long table_mb = (mb && *mb) ? atoll(mb) : 64;
+        const int min_rows = env_int("DRONE_HOT_MIN_ROWS", 1 << 22);
+        long long n_hot = table_mb * (1LL << 20) / 128;
+        if (n_hot > n_rows / 4) n_hot = n_rows / 4;
+        if (allow_tags && table_mb > 0 && n_rows >= min_rows && n_rows < (1 << 29) && nnz > 0 && n_hot > 0) {
+            Side &t = p->side[DRONE_OP_AT];
+            int rc = DRONE_OK;
+            if (orientations & DRONE_PLAN_AT) rc = tag_hot_columns(p, t, a.rowptr, (int)n_hot, st);
+            if (rc == DRONE_OK && (orientations & DRONE_PLAN_A))
+                rc = tag_hot_columns(p, a, (orientations & DRONE_PLAN_AT) ? t.rowptr : nullptr, (int)n_hot, st);
+            if (rc) return rc;
+            p->hot_table_bytes = (size_t)table_mb << 20;
+            DRONE_CUDA(cudaMalloc(&p->hot_table, p->hot_table_bytes));
+        }
+    }
+    if (orientations & DRONE_PLAN_AT) {
+        const int rc = build_work_lists(p, p->side[DRONE_OP_AT], st);
         if (rc) return rc;
     }
     if (orientations & DRONE_PLAN_A) {
@@ -589,6 +688,41 @@ static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_ind
 }  // namespace drone
 
 using namespace drone;
+
+extern "C" int drone_plan_destroy(drone_plan *p);
+static int plan_create_checked(drone_plan **out, int n_rows, int nnz, const int *d_index, const int *d_dst,
+                               const float *d_values, const int *d_in_degree, const int *d_out_degree,
+                               int orientations, void *stream, bool allow_tags) {
+    DRONE_REQUIRE(out != nullptr, "drone_plan_create: out is NULL");
+    *out = nullptr;
+    DRONE_REQUIRE(n_rows >= 0 && nnz >= 0, "drone_plan_create: negative size (n_rows=%d, nnz=%d)", n_rows, nnz);
+    DRONE_REQUIRE(n_rows < (1 << 30), "drone_plan_create: n_rows=%d is above the 2^30-1 limit of the column encoding", n_rows);
+    DRONE_REQUIRE(d_index != nullptr, "drone_plan_create: d_index is NULL");
+    DRONE_REQUIRE(nnz == 0 || d_dst != nullptr, "drone_plan_create: d_dst is NULL with nnz=%d", nnz);
+    DRONE_REQUIRE(nnz == 0 || d_values != nullptr || (d_in_degree && d_out_degree),
+                  "drone_plan_create: need d_values or both degree arrays");
+    DRONE_REQUIRE((orientations & DRONE_PLAN_BOTH) != 0 && (orientations & ~DRONE_PLAN_BOTH) == 0,
+                  "drone_plan_create: orientations=%d is not a combination of DRONE_PLAN_A/AT", orientations);
+    drone_plan *p = new (std::nothrow) drone_plan();
+    if (!p) return set_error(DRONE_E_INVALID, "drone_plan_create: out of host memory");
+    const int rc = plan_create_impl(p, n_rows, nnz, d_index, d_dst, d_values, d_in_degree, d_out_degree,
+                                    orientations, (cudaStream_t)stream, allow_tags);
+    if (rc != DRONE_OK) {
+        drone_plan_destroy(p);
+        return rc;
+    }
+    *out = p;
+    return DRONE_OK;
+}
+
+
+namespace drone {
+int plan_create_untagged(drone_plan **out, int n_rows, int nnz, const int *d_index, const int *d_dst, const float *d_values,
+                         const int *d_in_degree, const int *d_out_degree, int orientations, void *stream) {
+    return plan_create_checked(out, n_rows, nnz, d_index, d_dst, d_values, d_in_degree, d_out_degree, orientations,
+                               stream, false);
+}
+}  // namespace drone
 
 extern "C" {
 
@@ -613,26 +747,8 @@ int drone_compute_csr_values(const int *d_index, const int *d_dst, const int *d_
 int drone_plan_create(drone_plan **out, int n_rows, int nnz, const int *d_index, const int *d_dst,
                       const float *d_values, const int *d_in_degree, const int *d_out_degree,
                       int orientations, void *stream) {
-    DRONE_REQUIRE(out != nullptr, "drone_plan_create: out is NULL");
-    *out = nullptr;
-    DRONE_REQUIRE(n_rows >= 0 && nnz >= 0, "drone_plan_create: negative size (n_rows=%d, nnz=%d)", n_rows, nnz);
-    DRONE_REQUIRE(n_rows < (1 << 30), "drone_plan_create: n_rows=%d is above the 2^30-1 limit of the column encoding", n_rows);
-    DRONE_REQUIRE(d_index != nullptr, "drone_plan_create: d_index is NULL");
-    DRONE_REQUIRE(nnz == 0 || d_dst != nullptr, "drone_plan_create: d_dst is NULL with nnz=%d", nnz);
-    DRONE_REQUIRE(nnz == 0 || d_values != nullptr || (d_in_degree && d_out_degree),
-                  "drone_plan_create: need d_values or both degree arrays");
-    DRONE_REQUIRE((orientations & DRONE_PLAN_BOTH) != 0 && (orientations & ~DRONE_PLAN_BOTH) == 0,
-                  "drone_plan_create: orientations=%d is not a combination of DRONE_PLAN_A/AT", orientations);
-    drone_plan *p = new (std::nothrow) drone_plan();
-    if (!p) return set_error(DRONE_E_INVALID, "drone_plan_create: out of host memory");
-    const int rc = plan_create_impl(p, n_rows, nnz, d_index, d_dst, d_values, d_in_degree, d_out_degree,
-                                    orientations, (cudaStream_t)stream);
-    if (rc != DRONE_OK) {
-        drone_plan_destroy(p);
-        return rc;
-    }
-    *out = p;
-    return DRONE_OK;
+    return plan_create_checked(out, n_rows, nnz, d_index, d_dst, d_values, d_in_degree, d_out_degree, orientations,
+                               stream, true);
 }
 
 int drone_plan_destroy(drone_plan *p) {
@@ -643,6 +759,8 @@ int drone_plan_destroy(drone_plan *p) {
     free_side(p->side[0]);
     free_side(p->side[1]);
     cudaFree(p->row_order);
+    cudaFree(p->counter);
+    cudaFree(p->hot_table);
     cudaFree(p->scratch);
     cudaFree(p->stage_x);
     cudaFree(p->stage_y);
@@ -748,10 +866,23 @@ int drone_plan_get_csr(const drone_plan *p, int orientation, const int **d_rowpt
     DRONE_REQUIRE(p != nullptr, "drone_plan_get_csr: plan is NULL");
     DRONE_REQUIRE(orientation == DRONE_OP_A || orientation == DRONE_OP_AT,
                   "drone_plan_get_csr: orientation=%d", orientation);
-    const Side &s = p->side[orientation];
+    Side &s = const_cast<drone_plan *>(p)->side[orientation];
     DRONE_REQUIRE(s.ready, "drone_plan_get_csr: orientation %d was not prepared by drone_plan_create", orientation);
+    if (s.hot_ids && !s.col_plain && p->nnz > 0) {   // tagged plan: the caller gets an untagged copy, made once
+        int prev = -1;
+        DRONE_CUDA(cudaGetDevice(&prev));
+        if (prev != p->device) DRONE_CUDA(cudaSetDevice(p->device));
+        cudaError_t err = cudaMalloc(&s.col_plain, sizeof(int) * (size_t)p->nnz);
+        if (err == cudaSuccess) {
+            untag_columns_kernel<<<grid_for(p->nnz), 256>>>(s.col, p->nnz, s.hot_ids, s.col_plain);
+            err = cudaDeviceSynchronize();
+            count_launch();
+        }
+        if (prev != p->device) cudaSetDevice(prev);
+        if (err != cudaSuccess) return set_error(DRONE_E_CUDA, "drone_plan_get_csr: %s", cudaGetErrorString(err));
+    }
     if (d_rowptr) *d_rowptr = s.rowptr;
-    if (d_col) *d_col = s.col;
+    if (d_col) *d_col = s.col_plain ? s.col_plain : s.col;
     if (d_val) *d_val = s.val;
     return DRONE_OK;
 }

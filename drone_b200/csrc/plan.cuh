@@ -10,6 +10,10 @@ constexpr int kShortRangeNnz = 64;          // stream entries per lane group (pl
 constexpr unsigned kLastInRow = 0x80000000u; // flag on s_col: last entry of its row
 constexpr unsigned kPlaceholder = 0x40000000u; // flag on s_col: row has no nonzeros, entry carries no data
 constexpr unsigned kColMask = 0x3fffffffu;
+// Plans of very large graphs tag their most often gathered columns (bit 29 on the entries of col and s_col): the
+// remaining bits of a tagged entry are the column's position in the plan's table of hot rows instead of the column.
+constexpr unsigned kHotTag = 0x20000000u;
+constexpr unsigned kHotMask = 0x1fffffffu;
 constexpr int kMaxRowClasses = 16;         // row classes a plan can be given (drone_plan_set_row_classes)
 
 // One chunk of a long row: nonzeros [k0, k0+len) of `row`.  slot >= 0 means the
@@ -35,8 +39,13 @@ struct SplitRow {
 struct Side {
     bool ready = false;
     int *rowptr = nullptr;     // [n_rows + 1]
-    int *col = nullptr;        // [nnz]
+    int *col = nullptr;        // [nnz]; in a tagged plan the hot columns carry kHotTag | position
     float *val = nullptr;      // [nnz]
+    // tagged plans only: hot_ids[pos] = column that position pos of the table of hot rows stands for, most often
+    // gathered first; col_plain = untagged copy of col, made when a caller asks for the CSR arrays
+    int *hot_ids = nullptr;    // [n_hot]
+    int n_hot = 0;
+    int *col_plain = nullptr;  // [nnz] or NULL
     Chunk *chunks = nullptr;   // [n_chunks]
     SplitRow *split = nullptr; // [n_split_rows]
     SplitRow *wide = nullptr;  // [n_wide_rows] the split rows with more than kWideSlots slots (any order)
@@ -67,6 +76,14 @@ struct Side {
 
 }  // namespace drone
 
+struct drone_plan;
+namespace drone {
+// drone_plan_create for users inside the library that read the plan's lists with kernels of their own (the
+// PageRank pull): never tags columns.
+int plan_create_untagged(drone_plan **out, int n_rows, int nnz, const int *d_index, const int *d_dst, const float *d_values,
+                         const int *d_in_degree, const int *d_out_degree, int orientations, void *stream);
+}  // namespace drone
+
 struct drone_plan {
     int device = 0;
     int n_rows = 0;
@@ -86,6 +103,12 @@ struct drone_plan {
     int *row_order = nullptr;  // [n_rows]
     int n_classes = 1;
     int class_start[drone::kMaxRowClasses + 1] = {0};
+    // one word: the chunk kernel's work counter (set to 0 in front of every launch)
+    unsigned *counter = nullptr;
+    // tagged plans: the table of hot rows, refilled from X by every call
+    float *hot_table = nullptr;
+    size_t hot_table_bytes = 0;
+    int chunk_blocks_per_sm = 0;   // cap on resident blocks of the chunk kernel per SM (0: as many as fit)
     cudaStream_t own_stream = nullptr;
     // second stream and fork/join events: the short-row kernel runs beside the chunk kernels of the same call
     cudaStream_t side_stream = nullptr;

@@ -1,0 +1,13 @@
+// The aggregation kernels for one combination of the template switches of spmm_kernels.cuh
+// (UNIT = true, HOT = false); a translation unit of its own so that the combinations compile side by side.
+#include "spmm_kernels.cuh"
+
+#include <algorithm>
+
+namespace drone {
+
+int spmm_dispatch_unit(const SpmmArgs &a, bool vec4) {
+    return vec4 ? dispatch_width<4, true, false>(a) : dispatch_width<1, true, false>(a);
+}
+
+}  // namespace drone

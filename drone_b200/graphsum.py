@@ -58,6 +58,15 @@ class Comm:
         check(_lib.lib().drone_comm_allreduce_sum(self._h, C.c_void_p(t.data_ptr()), t.numel(),
                                                   int(t.dtype == torch.float64), _stream_ptr(stream)))
 
+    def bcast(self, t, root=0, stream=None):
+        """weight_broadcast_value_nccl (cuda_gcn/src/cuda/cuda_communicate.cu:99-105): rank `root`'s floats to all."""
+        check(_lib.lib().drone_comm_bcast(self._h, C.c_void_p(t.data_ptr()), t.numel(), int(root), _stream_ptr(stream)))
+
+    def reduce_sum(self, t, root=0, stream=None):
+        """weight_reduce_grad_nccl (cuda_communicate.cu:107-115): the sum over ranks lands on `root`."""
+        check(_lib.lib().drone_comm_reduce_sum(self._h, C.c_void_p(t.data_ptr()), t.numel(), int(root),
+                                               _stream_ptr(stream)))
+
     def close(self):
         if self._h.value:
             _lib.lib().drone_comm_destroy(self._h)
@@ -80,6 +89,16 @@ class DeviceGraph:
         self.mirror2worker = torch.as_tensor(g.mirror2worker, device=device)
         self.xplan = ExchangePlan(g, max_features)
         self.plan = AggregationPlan(self.index, self.dst, in_degree=self.in_degree, out_degree=self.out_degree)
+
+
+def clear_mirror_rows(rows, mirror2worker, stream=None):
+    """clear_mirror_grad (cuda_gcn/src/cuda/cuda_module.cu:50-61): zero the rows of mirror vertices, in place."""
+    f = rows.shape[1]
+    ld = rows.stride(0) if rows.shape[0] > 1 else max(f, rows.stride(0))
+    with torch.cuda.device(rows.device):
+        check(_lib.lib().drone_clear_mirror_rows(C.c_void_p(rows.data_ptr()), rows.shape[0], f, int(ld),
+                                                 C.c_void_p(mirror2worker.data_ptr()), _stream_ptr(stream)))
+    return rows
 
 
 def exchange_sum(xplan, comm, rows, stream=None):

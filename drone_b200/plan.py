@@ -8,7 +8,7 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import OP_A, OP_AT, PLAN_A, PLAN_AT, PLAN_BOTH, PlanStats, check
+from ._lib import OP_A, OP_AT, PLAN_A, PLAN_AT, PLAN_BOTH, EPILOGUE_NONE, EPILOGUE_RELU, PlanStats, SpmmOpts, check
 
 
 def _stream_ptr(stream=None):
@@ -37,6 +37,18 @@ def compute_csr_values(index, dst, in_degree, out_degree, stream=None):
         check(_lib.lib().drone_compute_csr_values(_ptr(index), _ptr(dst), _ptr(in_degree), _ptr(out_degree),
                                                   index.numel() - 1, _ptr(values), _stream_ptr(stream)))
     return values
+
+
+def degree_scales(in_degree, out_degree, stream=None):
+    """(in_degree^-1/2, out_degree^-1/2) as float32 tensors: the two factors of the reference's edge coefficient
+    (cuda_gcn/src/cuda/cuda_kernel.cu:144-155), for the value-free form of the aggregation."""
+    in_degree, out_degree = _dev_i32(in_degree, "in_degree"), _dev_i32(out_degree, "out_degree")
+    n = in_degree.numel()
+    a = torch.empty(n, dtype=torch.float32, device=in_degree.device)
+    b = torch.empty(n, dtype=torch.float32, device=in_degree.device)
+    with torch.cuda.device(in_degree.device):
+        check(_lib.lib().drone_degree_scales(_ptr(in_degree), _ptr(out_degree), n, _ptr(a), _ptr(b), _stream_ptr(stream)))
+    return a, b
 
 
 class AggregationPlan:
@@ -108,9 +120,10 @@ class AggregationPlan:
                                                         int(n_classes), _stream_ptr(stream)))
         self.n_classes = int(n_classes)
 
-    def spmm(self, orientation, x, out=None, stream=None, row_class=None):
+    def spmm(self, orientation, x, out=None, stream=None, row_class=None, relu=False, row_scale=None, unit_values=False):
         """out[r,:] = sum_k val[k]*x[col[k],:] (rows of the chosen orientation).  x: [n_rows, F] float32.
-        With row_class only the rows of that class are written."""
+        With row_class only the rows of that class are written.  relu / row_scale / unit_values are the options of
+        drone_spmm_ex: out = max(row_scale[r] * sum, 0), and every coefficient taken as 1."""
         if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1):
             raise ValueError("x must be a 2-D float32 CUDA tensor with unit inner stride")
         if x.shape[0] != self.n_rows:
@@ -123,7 +136,15 @@ class AggregationPlan:
         ldx = x.stride(0) if self.n_rows > 1 else max(f, x.stride(0))
         ldy = out.stride(0) if self.n_rows > 1 else max(f, out.stride(0))
         with torch.cuda.device(self.device):
-            if row_class is None:
+            if relu or row_scale is not None or unit_values:
+                if row_scale is not None and not (row_scale.is_cuda and row_scale.dtype == torch.float32 and
+                                                  row_scale.is_contiguous() and row_scale.numel() == self.n_rows):
+                    raise ValueError("row_scale must be a contiguous float32 CUDA tensor with one entry per row")
+                opts = SpmmOpts(EPILOGUE_RELU if relu else EPILOGUE_NONE, -1 if row_class is None else int(row_class),
+                                1 if unit_values else 0, 0, row_scale.data_ptr() if row_scale is not None else None)
+                check(_lib.lib().drone_spmm_ex(self._h, int(orientation), f, _ptr(x), int(ldx), _ptr(out), int(ldy),
+                                               C.byref(opts), _stream_ptr(stream)))
+            elif row_class is None:
                 check(_lib.lib().drone_spmm(self._h, int(orientation), f, _ptr(x), int(ldx), _ptr(out), int(ldy),
                                             _stream_ptr(stream)))
             else:

@@ -123,6 +123,43 @@ int drone_spmm(drone_plan *plan, int orientation, int F,
                const float *d_X, int ldx, float *d_Y, int ldy, void *stream);
 
 /*
+ * drone_spmm with options, for the element-wise step the reference runs as a pass of its own right after the
+ * aggregation and for the coefficient stream:
+ *   epilogue = DRONE_EPILOGUE_RELU   Y is stored as max(Y, 0): CUDAReLU::forward in place on the layer's output
+ *                                    (cuda_gcn/src/cuda/cuda_module.cu:498-511, kernel cuda_kernel.cu:384-391) done in
+ *                                    the store of the aggregation.  The mask the reference keeps for the backward
+ *                                    pass is (Y > 0) of the stored result.
+ *   d_row_scale                      Y[r,:] is multiplied by d_row_scale[r] before the epilogue (NULL: not scaled).
+ *   unit_values = 1                  every stored coefficient counts as 1 and the coefficient stream is not read
+ *                                    (4 bytes per nonzero instead of 8).  With the reference's coefficients
+ *                                    1/sqrt(outDegree[u]*inDegree[v]) (cuda_kernel.cu:144-155), which are a product
+ *                                    of a per-row and a per-column factor, the layer becomes
+ *                                      Y = diag(row factor) · pattern · (diag(column factor) · X):
+ *                                    the caller scales X's rows (or folds the factor into what produces X) and passes
+ *                                    the row factor as d_row_scale; drone_degree_scales computes both factors.
+ *                                    Results differ from the stored-coefficient path by rounding only.
+ *   row_class                        -1: all rows; >= 0: as drone_spmm_rows.
+ * opts == NULL is drone_spmm.  Zero-initialise the struct, set row_class = -1, then set what is needed.
+ */
+#define DRONE_EPILOGUE_NONE 0
+#define DRONE_EPILOGUE_RELU 1
+typedef struct drone_spmm_opts {
+    int          epilogue;
+    int          row_class;
+    int          unit_values;
+    int          reserved_;
+    const float *d_row_scale;
+} drone_spmm_opts;
+int drone_spmm_ex(drone_plan *plan, int orientation, int F,
+                  const float *d_X, int ldx, float *d_Y, int ldy,
+                  const drone_spmm_opts *opts, void *stream);
+
+/* in_scale[i] = inDegree[i]^-1/2, out_scale[i] = outDegree[i]^-1/2 (0 where the degree is 0): the per-row and
+ * per-column factors of cuda_compute_csr_values, cuda_gcn/src/cuda/cuda_kernel.cu:144-155. */
+int drone_degree_scales(const int *d_in_degree, const int *d_out_degree, int n_rows,
+                        float *d_in_scale, float *d_out_scale, void *stream);
+
+/*
  * Row classes: a way to compute the aggregation a group of output rows at a time, so that what follows the
  * aggregation for a group (the mirror/master exchange of those rows, cuda_gcn/src/cuda/cuda_module.cu:267-272)
  * can run on another stream while the next group is still being aggregated.
@@ -219,6 +256,24 @@ int drone_comm_destroy(drone_comm *comm);
 /* In-place sum over ranks of `count` floats (is_double = 0) or doubles (1).
  * Replaces ncclAllReduce(globalDiff), DRONE/src/cuda/algorithm/pr.cu:365. */
 int drone_comm_allreduce_sum(drone_comm *comm, void *d_buf, size_t count, int is_double, void *stream);
+
+/*
+ * The data-parallel treatment of the dense layers' weights around the aggregation, in place on `count` floats:
+ * drone_comm_bcast copies rank `root`'s buffer to every rank (weight_broadcast_value_nccl,
+ * cuda_gcn/src/cuda/cuda_communicate.cu:99-105, called with root 0 at the start of every forward pass);
+ * drone_comm_reduce_sum leaves the sum over ranks on `root` (weight_reduce_grad_nccl, :107-115; the other ranks'
+ * buffers are unspecified afterwards, as with ncclReduce).  Asynchronous on `stream`.
+ */
+int drone_comm_bcast(drone_comm *comm, float *d_buf, size_t count, int root, void *stream);
+int drone_comm_reduce_sum(drone_comm *comm, float *d_buf, size_t count, int root, void *stream);
+
+/*
+ * Zeroes the rows of a [n_rows, F] row-major matrix (leading dimension ld) that belong to mirror vertices
+ * (d_mirror2worker[row] != -1), so that the weight gradient dW = X^T · dY that follows counts every replicated
+ * vertex once.  Replaces clear_mirror_grad, cuda_gcn/src/cuda/cuda_module.cu:50-61 (launched at :88-91 between
+ * the two cublasSgemm calls of CUDAMatmul::backward).
+ */
+int drone_clear_mirror_rows(float *d_rows, int n_rows, int F, int ld, const int *d_mirror2worker, void *stream);
 
 /*
  * Routing plan of one rank, from the reference's routing tables (host arrays,

@@ -165,6 +165,70 @@ def test_column_slices_chosen_by_size(cuda_device, oracle):
     assert auto.stats().last_slice_width == 64 and whole.stats().last_slice_width == 0
 
 
+@pytest.mark.parametrize("f", [3, 32, 41, 64, 256])
+def test_relu_and_row_scale_in_the_store(cuda_device, oracle, f):
+    """drone_spmm_ex: Y = max(row_scale * (A x), 0) equals the same steps applied to drone_spmm's output, bit for
+    bit, for short rows, single-chunk rows and split rows alike."""
+    n, u, v = gg.rmat_graph(12, 16, seed=39, symmetrise=False, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    assert plan.stats().n_partials[db.OP_AT] > 0
+    x = torch.as_tensor(gg.seeded_normal(70 + f, (n, f)), device=cuda_device)
+    scale = torch.as_tensor(gg.seeded_normal(71, (n,)), device=cuda_device).abs() + 0.5
+    for op in (db.OP_AT, db.OP_A):
+        base = plan.spmm(op, x)
+        assert torch.equal(plan.spmm(op, x, relu=True), torch.clamp_min(base, 0.0))
+        assert torch.equal(plan.spmm(op, x, row_scale=scale), base * scale[:, None])
+        assert torch.equal(plan.spmm(op, x, relu=True, row_scale=scale), torch.clamp_min(base * scale[:, None], 0.0))
+
+
+@pytest.mark.parametrize("f", [1, 32, 41, 128])
+def test_value_free_form(cuda_device, oracle, f):
+    """unit_values: the coefficient stream is not read.  Y = diag(in^-1/2) P (diag(out^-1/2) X) with P the 0/1
+    pattern is the layer with the reference's coefficients, up to rounding: checked against the double oracle."""
+    n, u, v = gg.rmat_graph(12, 16, seed=40, symmetrise=False, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    xh = gg.seeded_normal(80 + f, (n, f))
+    x = torch.as_tensor(xh, device=cuda_device)
+    in_s, out_s = db.degree_scales(torch.as_tensor(in_deg, device=cuda_device), torch.as_tensor(out_deg, device=cuda_device))
+    np.testing.assert_allclose(in_s.cpu().numpy(), 1.0 / np.sqrt(in_deg.astype(np.float64)), rtol=1e-6)
+    t = oracle.transpose_csr(n, n, index, dst, val)
+    w_f, a_f = oracle.spmm_csr_f64(*t, xh, with_abs=True)
+    w_b, a_b = oracle.spmm_csr_f64(index, dst, val, xh, with_abs=True)
+    # forward: rows are destinations (factor in^-1/2), gathered rows are sources (factor out^-1/2)
+    fwd = plan.spmm(db.OP_AT, x * out_s[:, None], unit_values=True, row_scale=in_s)
+    bwd = plan.spmm(db.OP_A, x * in_s[:, None], unit_values=True, row_scale=out_s)
+    assert_close_to_oracle(fwd.cpu().numpy(), w_f, a_f)
+    assert_close_to_oracle(bwd.cpu().numpy(), w_b, a_b)
+    # pattern only: every coefficient 1
+    ones = np.ones_like(val)
+    w1, a1 = oracle.spmm_csr_f64(index, dst, ones, xh, with_abs=True)
+    assert_close_to_oracle(plan.spmm(db.OP_A, x, unit_values=True).cpu().numpy(), w1, a1)
+
+
+@pytest.mark.parametrize("f", [1, 32, 41, 64, 128])
+def test_table_of_hot_rows(cuda_device, oracle, f):
+    """A plan that tags its most gathered columns (forced on a small graph; a quarter of the rows at most, here with
+    a table so small that wide rows only fit in part) gives the bits of an untagged plan, for every kernel, and hands
+    out untagged CSR arrays."""
+    n, u, v = gg.rmat_graph(14, 16, seed=41, symmetrise=False, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plain = make_plan(cuda_device, index, dst, in_deg, out_deg, DRONE_HOT_TABLE_MB=0)
+    tagged = make_plan(cuda_device, index, dst, in_deg, out_deg, DRONE_HOT_MIN_ROWS=1, DRONE_HOT_TABLE_MB=1)
+    x = torch.as_tensor(gg.seeded_normal(90 + f, (n, f)), device=cuda_device)
+    for op in (db.OP_AT, db.OP_A):
+        want = plain.spmm(op, x)
+        assert torch.equal(tagged.spmm(op, x), want)
+        assert torch.equal(tagged.spmm(op, x), want)          # the table is refilled by every call
+        assert torch.equal(tagged.spmm(op, x, relu=True), torch.clamp_min(want, 0.0))
+        for a, b in zip(tagged.csr(op), plain.csr(op)):
+            assert torch.equal(a, b)
+    check_both_orientations(tagged, oracle, index, dst, val, x.cpu().numpy(), cuda_device)
+    x2 = torch.as_tensor(gg.seeded_normal(91 + f, (n, f)), device=cuda_device)
+    assert torch.equal(tagged.spmm(db.OP_AT, x2), plain.spmm(db.OP_AT, x2))   # other operand: no stale table rows
+
+
 def test_golden_vectors(cuda_device, oracle):
     gold = np.load(os.path.join(ROOT, "tests", "golden", "spmm_golden.npz"))
     for name, scale, ef, seed, sym, loops, widths in make_golden.CASES:
