@@ -5,7 +5,9 @@
 
 One "step" is one pass of the path over the workload's graph: Y = Â·H (the forward
 aggregation of a GraphSum layer).  Rank 0 prints ONE JSON line.  Throughput is in
-nnz·F per second (one multiply-add per stored nonzero per feature).
+nnz·F per second (one multiply-add per stored nonzero per feature).  The K steps are
+timed as one block between CUDA events; the block is repeated until half a second has
+been timed and the median block is reported.
 
 Workloads (all synthetic, seeded):
   c2       R-MAT scale 20, edge factor 16, symmetrised, +I, F=64   (single-GPU headline)
@@ -15,11 +17,11 @@ Workloads (all synthetic, seeded):
 
 Several GPUs (one process per GPU under torchrun): the graph is EBV-partitioned on rank 0 and handed out; a step is
 the local aggregation plus the mirror/master exchange.  --scaling weak (default: scale + log2 N) | strong,
---exchange p2p|nccl|dense, --pipeline-groups G, --pagerank-iters K.
+--exchange p2p|nccl|dense, --pipeline-groups G (0 = measure 1, 2 and 4 groups and keep the fastest).
 
-Beside the headline the line carries: roofline, e2e (host operands), cusparse (head-to-head), cpu_baseline, clocks,
-gcn_epoch, pagerank, minprop (cc / sssp jobs) and jobs_head_to_head (the reference's own GPU jobs vs the drop-in);
---no-cusparse / --no-cpu-baseline / --no-gcn leave sections out.
+Beside the headline the line carries sections (--sections a,b,... or "all" / "none"):
+  one GPU:      parity, cusparse, e2e, rmat26, gcn_epoch, gcn_c4, pagerank, minprop, jobs, cpu
+  several GPUs: parity, gcn_epoch, gcn_c4, strong, e2e
 """
 import argparse
 import json
@@ -37,13 +39,70 @@ import torch  # noqa: E402
 WORKLOADS = {
     "c2": dict(scale=20, edge_factor=16, features=64, symmetrise=True, seed=20261127),
     "rmat26": dict(scale=26, edge_factor=16, features=32, symmetrise=False, seed=20261130),
+    "rmat24": dict(scale=24, edge_factor=16, features=32, symmetrise=False, seed=20261132),
     "rmat22": dict(scale=22, edge_factor=16, features=32, symmetrise=False, seed=20261131),
 }
 
+# the GCN configurations: vertices, undirected pairs drawn, layer widths (input, hidden..., classes)
+GCN_CONFIGS = {
+    "c3": dict(vertices=232965, pairs=57_200_000, dims=[602, 128, 41], seed=20261203,
+               descr="Reddit-shaped power-law graph, 2 layers 602-128-41"),
+    "c4": dict(vertices=2449029, pairs=61_900_000, dims=[100, 256, 256, 47], seed=20261204,
+               descr="products-shaped power-law graph, 3 layers 100-256-256-47"),
+}
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the kernels of ONE drone_spmm call, from an ncu capture of this
-# program on the named workload (profiles/spmm_c2_f64.md gives the command and the per-kernel split).
-NCU_DRAM_BYTES_PER_CALL = {"c2": 1.544e9}
+SECTIONS_ONE = ["parity", "cusparse", "e2e", "rmat26", "gcn_epoch", "gcn_c4", "pagerank", "minprop", "jobs", "cpu"]
+SECTIONS_MULTI = ["parity", "gcn_epoch", "gcn_c4", "strong", "e2e"]
+MIN_TIMED_SECONDS = 0.5
+
+
+def measured_traffic(workload):
+    """DRAM bytes of one aggregation call from the ncu capture recorded under profiles/ for this workload (written by
+    `bench.py --record-traffic`), with the commit it was taken at; None when there is no record."""
+    path = os.path.join(ROOT, "profiles", "spmm_%s_dram_traffic.txt" % workload)
+    if not os.path.exists(path):
+        return None, None
+    rec = {}
+    for line in open(path):
+        if ":" in line and not line.startswith("#"):
+            k, v = line.split(":", 1)
+            rec[k.strip()] = v.strip()
+    try:
+        return float(rec["dram_bytes_per_call"]), rec.get("commit")
+    except (KeyError, ValueError):
+        return None, None
+
+
+def record_traffic(csv_path, workload):
+    """Turns the CSV of `ncu --metrics gpu__time_duration.sum,dram__bytes_read.sum,dram__bytes_write.sum --csv` taken
+    over whole aggregation calls of `bench.py --workload <workload>` into profiles/spmm_<workload>_dram_traffic.txt."""
+    import csv
+    import subprocess
+    per_kernel, calls = {}, 0
+    with open(csv_path) as fh:
+        rows = [r for r in csv.reader(fh) if len(r) > 5]
+    head = next(r for r in rows if "Metric Name" in r)
+    ki, mi, vi, ui = head.index("Kernel Name"), head.index("Metric Name"), head.index("Metric Value"), head.index("Metric Unit")
+    for r in rows:
+        if r is head or len(r) <= vi or not r[mi].startswith("dram__bytes"):
+            continue
+        mult = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}.get(r[ui], 1.0)
+        name = r[ki].split("(")[0].split("<")[0]
+        per_kernel.setdefault(name, [0.0, 0])
+        per_kernel[name][0] += float(r[vi].replace(",", "")) * mult
+        if r[mi] == "dram__bytes_read.sum":
+            per_kernel[name][1] += 1
+    calls = max(1, max((c for n, (b, c) in per_kernel.items() if "chunks" in n), default=1))
+    total = sum(b for b, c in per_kernel.values()) / calls
+    commit = subprocess.run(["git", "-C", ROOT, "rev-parse", "--short", "HEAD"], capture_output=True, text=True).stdout.strip()
+    out = os.path.join(ROOT, "profiles", "spmm_%s_dram_traffic.txt" % workload)
+    with open(out, "w") as fh:
+        fh.write("# dram__bytes_read.sum + dram__bytes_write.sum of the kernels of ONE aggregation call, from an ncu capture\n")
+        fh.write("# of `python bench.py --workload %s --sections none` (see the profile summary of the same workload).\n" % workload)
+        fh.write("workload: %s\ncalls_captured: %d\ndram_bytes_per_call: %.6e\ncommit: %s\n" % (workload, calls, total, commit or "unknown"))
+        for n, (b, c) in sorted(per_kernel.items()):
+            fh.write("kernel %s: %.6e bytes over %d launches\n" % (n, b, c))
+    print("wrote", out)
 
 
 def parse_args():
@@ -58,19 +117,41 @@ def parse_args():
     ap.add_argument("--features", type=int)
     ap.add_argument("--symmetrise", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--sections", default="all", help='comma-separated section names, "all" or "none"')
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cusparse", action="store_true")
-    ap.add_argument("--no-gcn", action="store_true")
+    ap.add_argument("--no-gcn", action="store_true", help="leave out gcn_epoch, gcn_c4, pagerank, minprop, jobs, rmat26")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl", "dense"],
                     help="transport of the mirror/master exchange on several GPUs")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="several GPUs: weak = the graph grows with the GPU count (default), strong = the named graph is cut")
-    ap.add_argument("--pipeline-groups", type=int, default=1,
+    ap.add_argument("--pipeline-groups", type=int, default=0,
                     help="several GPUs: aggregate and exchange the rows in this many groups, group g's exchange "
-                         "overlapping group g+1's aggregation (1 = aggregation, then exchange)")
+                         "overlapping group g+1's aggregation (1 = aggregation, then exchange; 0 = time 1, 2 and 4 "
+                         "and keep the fastest)")
     ap.add_argument("--pagerank-iters", type=int, default=0,
-                    help="several GPUs: also time this many PageRank power iterations (F=1) over the same partition")
-    return ap.parse_args()
+                    help="also time this many PageRank power iterations (F=1) over the workload's graph / partition")
+    ap.add_argument("--strong-workload", default="auto", help="several GPUs, section strong: rmat26 | rmat24 | auto")
+    ap.add_argument("--record-traffic", metavar="CSV", help="write profiles/spmm_<workload>_dram_traffic.txt from an ncu CSV and exit")
+    args = ap.parse_args()
+    names = SECTIONS_ONE + SECTIONS_MULTI
+    if args.sections == "all":
+        chosen = set(names)
+    elif args.sections == "none":
+        chosen = set()
+    else:
+        chosen = set(x for x in args.sections.split(",") if x)
+        bad = chosen - set(names)
+        if bad:
+            ap.error("unknown section(s): %s" % ", ".join(sorted(bad)))
+    if args.no_cpu_baseline:
+        chosen.discard("cpu")
+    if args.no_cusparse:
+        chosen.discard("cusparse")
+    if args.no_gcn:
+        chosen -= {"gcn_epoch", "gcn_c4", "pagerank", "minprop", "jobs", "rmat26", "strong"}
+    args.chosen = chosen
+    return args
 
 
 def workload_config(args):
@@ -241,6 +322,57 @@ def workload_descr(args, cfg, n, nnz):
         "l2_policy": "operands rotate over 3 buffer sets; CSR + H + Y exceed the 126 MB L2"}
 
 
+def time_blocks(step, steps, sync, min_seconds=MIN_TIMED_SECONDS, max_blocks=400):
+    """Times blocks of exactly `steps` calls of step(i) between two CUDA events on the current stream, block after
+    block until min_seconds have been timed (at least one block).  sync() is called on both sides of every block (device
+    synchronisation, plus a barrier on several GPUs).  Returns the list of block times in ms."""
+    blocks, total = [], 0.0
+    i = 0
+    while len(blocks) < max_blocks and (not blocks or total < min_seconds * 1e3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync()
+        e0.record()
+        for _ in range(steps):
+            step(i)
+            i += 1
+        e1.record()
+        sync()
+        blocks.append(e0.elapsed_time(e1))
+        total += blocks[-1]
+    return blocks
+
+
+def hbm_peak():
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        return float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def small_case_parity(device):
+    """The library against the double-precision oracle on a seeded R-MAT-13 graph, both orientations, F = 32 and 41:
+    largest error relative to the largest element of the result."""
+    import drone_b200 as db
+    from drone_b200 import graphgen as gg
+    from oracle import oracle
+    oracle.build()
+    n, u, v = gg.rmat_graph(13, 16, seed=20261141, symmetrise=False, self_loops="add")
+    index, dst = gg.csr_by_source(u, v, n)
+    in_deg, out_deg = gg.degrees(u, v, n)
+    plan = db.AggregationPlan(index.to(device), dst.to(device), in_degree=in_deg.to(device), out_degree=out_deg.to(device))
+    val = oracle.csr_values_f32(index.numpy(), dst.numpy(), in_deg.numpy(), out_deg.numpy())
+    worst = 0.0
+    for f in (32, 41):
+        x = gg.seeded_normal(f, (n, f))
+        xt = torch.as_tensor(x, device=device)
+        for op, want in ((db.OP_AT, oracle.graphsum_forward_f64(x, index.numpy(), dst.numpy(), val)),
+                         (db.OP_A, oracle.graphsum_backward_f64(x, index.numpy(), dst.numpy(), val))):
+            got = plan.spmm(op, xt).cpu().numpy()
+            worst = max(worst, float(np.abs(got - want).max() / np.abs(want).max()))
+    plan.close()
+    return worst
+
+
 def run_ours(args, cfg):
     import drone_b200 as db
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -252,10 +384,12 @@ def run_ours(args, cfg):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     lib = db.lib()
+    chosen = args.chosen
 
     n, index, dst, in_deg, out_deg = build_graph(cfg, device)
     nnz, f = dst.numel(), cfg["features"]
     plan = db.AggregationPlan(index, dst, in_degree=in_deg, out_degree=out_deg, orientations=db.PLAN_AT)
+    plan.reserve(f, host_operands="e2e" in chosen)
     st = plan.stats()
     nbuf = 3
     gen = torch.Generator(device=device)
@@ -263,76 +397,89 @@ def run_ours(args, cfg):
     xs = [torch.randn((n, f), device=device, generator=gen) for _ in range(nbuf)]
     ys = [torch.empty((n, f), device=device) for _ in range(nbuf)]
 
-    for i in range(max(args.warmup, 3)):
+    def step(i):
         plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
+
+    warmup = max(args.warmup, 3)
+    for i in range(warmup):
+        step(i)
     torch.cuda.synchronize()
 
     sampler = ClockSampler(index=local_rank)
     sampler.start()
     launches0 = lib.drone_kernel_launch_count()
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    torch.cuda.synchronize()
-    evs[0].record()
-    for i in range(args.steps):
-        plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
-        evs[i + 1].record()
-    torch.cuda.synchronize()
-    launches = lib.drone_kernel_launch_count() - launches0
-    total_ms = evs[0].elapsed_time(evs[-1])
-    per_step = np.array([evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)])
-    sampler.keep_loaded(lambda i: plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf]))
+    blocks = time_blocks(step, args.steps, torch.cuda.synchronize)
+    launches = (lib.drone_kernel_launch_count() - launches0) // len(blocks)
+    sampler.in_timed_region = False
     clocks = sampler.finish()
 
-    ms = total_ms / args.steps
+    block_ms = float(np.median(blocks))
+    ms = block_ms / args.steps
     value = nnz * f / (ms * 1e-3)
     b_alg = algorithmic_bytes(n, nnz, f)
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(peaks_path):
-        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
-    else:
-        peak, peak_src = 6650.0, "fallback"
+    peak, peak_src = hbm_peak()
     achieved = b_alg / (ms * 1e-3) / 1e9
-    traffic = NCU_DRAM_BYTES_PER_CALL.get(args.workload) if cfg == dict(WORKLOADS.get(args.workload, {})) else None
-
-    # end to end: host operands through the C ABI, copies inside the timed region
-    xh = torch.empty((n, f), dtype=torch.float32).pin_memory()
-    yh = torch.empty((n, f), dtype=torch.float32).pin_memory()
-    xh.copy_(xs[0])
-    plan.spmm_host(db.OP_AT, xh, yh)
-    t0 = time.perf_counter()
-    for _ in range(args.e2e_steps):
-        plan.spmm_host(db.OP_AT, xh, yh)
-    e2e_s = (time.perf_counter() - t0) / args.e2e_steps
-    checksum = float(yh[:1024].double().sum())
-    e2e = {"value": nnz * f / e2e_s, "unit": "nnz*F/s", "h2d_bytes_per_step": 4 * n * f,
-           "d2h_bytes_per_step": 4 * n * f, "ms_per_step": 1e3 * e2e_s, "steps": args.e2e_steps,
-           "checksum": checksum}
+    traffic, traffic_commit = (None, None)
+    if cfg == dict(WORKLOADS.get(args.workload, {})):
+        traffic, traffic_commit = measured_traffic(args.workload)
 
     line = {
         "metric": "spmm_nnzF_per_s", "value": value, "unit": "nnz*F/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_descr(args, cfg, n, nnz),
-        "ms_per_step_median": float(np.median(per_step)), "ms_per_step_min": float(per_step.min()),
+        "timed_blocks": len(blocks), "timed_ms_total": float(np.sum(blocks)),
+        "ms_per_step_min_block": float(np.min(blocks)) / args.steps,
+        "ms_per_step_max_block": float(np.max(blocks)) / args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes": b_alg,
+                     "traffic": traffic, "traffic_commit": traffic_commit, "peak_source": peak_src,
+                     "algorithmic_bytes": b_alg,
                      "kernel": "one drone_spmm call = spmm_short_stream + spmm_chunks + spmm_reduce_partials"},
-        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        "gpu_launches": int(launches), "clocks": clocks,
         "plan": {"short_row_limit": st.short_row_limit, "chunk_nnz": st.chunk_nnz,
                  "long_rows": st.n_long_rows[1], "chunks": st.n_chunks[1], "split_rows": st.n_split_rows[1],
                  "partials": st.n_partials[1]},
     }
 
-    if not args.no_cusparse:
+    if "e2e" in chosen:
+        # end to end: host operands through the C ABI, copies inside the timed region
+        xh = torch.empty((n, f), dtype=torch.float32).pin_memory()
+        yh = torch.empty((n, f), dtype=torch.float32).pin_memory()
+        xh.copy_(xs[0])
+        plan.spmm_host(db.OP_AT, xh, yh)
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            plan.spmm_host(db.OP_AT, xh, yh)
+        e2e_s = (time.perf_counter() - t0) / args.e2e_steps
+        line["e2e"] = {"value": nnz * f / e2e_s, "unit": "nnz*F/s", "h2d_bytes_per_step": 4 * n * f,
+                       "d2h_bytes_per_step": 4 * n * f, "ms_per_step": 1e3 * e2e_s, "steps": args.e2e_steps,
+                       "checksum": float(yh[:1024].double().sum()),
+                       "equals_device_call": bool(torch.equal(yh[:4096], plan.spmm(db.OP_AT, xs[0])[:4096].cpu()))}
+        del xh, yh
+
+    parity = {}
+    if "parity" in chosen:
+        try:
+            parity["oracle_rmat13_max_rel_err"] = small_case_parity(device)
+        except Exception as e:
+            parity["oracle_error"] = repr(e)
+
+    if "cusparse" in chosen:
         try:
             from baseline import cusparse_ref
             rp, co, va = plan.csr(db.OP_AT)
             res = {}
             for alg, name in ((0, "ALG_DEFAULT"), (2, "CSR_ALG2"), (3, "CSR_ALG3")):
-                ref = cusparse_ref.CusparseSpmm(rp, co, va, xs[0], ys[0], alg=alg)
+                y_ref = torch.empty_like(ys[0])
+                ref = cusparse_ref.CusparseSpmm(rp, co, va, xs[0], y_ref, alg=alg)
                 for _ in range(3):
                     ref.run()
                 torch.cuda.synchronize()
+                if alg == 0:       # same operands, same call the reference makes: largest difference to this library
+                    y_ours = plan.spmm(db.OP_AT, xs[0])
+                    parity["cusparse_max_rel_diff"] = float((y_ours - y_ref).abs().max() / y_ref.abs().max())
+                    parity["cusparse_workload"] = args.workload
+                    del y_ours
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 reps = max(3, min(args.steps, 10))
                 e0.record()
@@ -343,9 +490,15 @@ def run_ours(args, cfg):
                 t = e0.elapsed_time(e1) / reps
                 res[name] = {"ms": t, "nnzF_per_s": nnz * f / (t * 1e-3), "buffer_bytes": ref.buffer_bytes()}
                 ref.close()
+                del y_ref
             line["cusparse"] = res
+            del rp, co, va
         except Exception as e:  # the head-to-head is informative, never fatal
             line["cusparse"] = {"error": repr(e)}
+    if parity:
+        parity["tolerance"] = 1e-5
+        parity["ok"] = all(v <= 1e-5 for k, v in parity.items() if k.endswith("_err") or k.endswith("_diff"))
+        line["parity"] = parity
 
     if args.pagerank_iters > 0:      # the path at F = 1 on the workload's own graph, for comparison with several GPUs
         try:
@@ -353,44 +506,128 @@ def run_ours(args, cfg):
         except Exception as e:
             line["pagerank_workload_graph"] = {"error": repr(e)}
 
-    if not args.no_gcn:
-        del xs, ys, xh, yh
+    cpu_csr = None
+    if "cpu" in chosen:
+        cpu_csr = [t.cpu().numpy() for t in plan.csr(db.OP_AT)]
+    del xs, ys, plan, index, dst, in_deg, out_deg
+    torch.cuda.empty_cache()
+
+    def section(name, fn):
+        if name not in chosen:
+            return
+        try:
+            line[name] = fn()
+        except Exception as e:
+            line[name] = {"error": repr(e)}
         torch.cuda.empty_cache()
-        try:
-            line["gcn_epoch"] = gcn_epoch_timing(device)
-        except Exception as e:
-            line["gcn_epoch"] = {"error": repr(e)}
-        torch.cuda.empty_cache()
-        try:
-            line["pagerank"] = pagerank_timing(device)
-        except Exception as e:
-            line["pagerank"] = {"error": repr(e)}
-        try:
-            line["minprop"] = minprop_timing(device)
-        except Exception as e:
-            line["minprop"] = {"error": repr(e)}
+
+    section("rmat26", lambda: large_graph_timing(device, "rmat26"))
+    section("gcn_epoch", lambda: gcn_epoch_timing(device, "c3", with_cusparse=True))
+    section("gcn_c4", lambda: gcn_epoch_timing(device, "c4", with_cusparse=False))
+    section("pagerank", lambda: pagerank_timing(device))
+    section("minprop", lambda: minprop_timing(device))
+    if "jobs" in chosen:
         line["jobs_head_to_head"] = jobs_head_to_head()
 
-    if not args.no_cpu_baseline:
-        from oracle import oracle
-        index_h, dst_h = index.cpu().numpy(), dst.cpu().numpy()
-        val_h = plan.csr(db.OP_AT)
-        times, threads = cpu_spmm_baseline(val_h[0].cpu().numpy(), val_h[1].cpu().numpy(), val_h[2].cpu().numpy(), f,
-                                           cfg["seed"])
+    if cpu_csr is not None:
+        times, threads = cpu_spmm_baseline(cpu_csr[0], cpu_csr[1], cpu_csr[2], f, cfg["seed"])
         best = min(times)
         line["cpu_baseline"] = {"value": nnz * f / best, "unit": "nnz*F/s", "cores": threads, "kind": "port",
                                 "sample": "whole workload, best of %d runs of the oracle's OpenMP float CSR SpMM"
                                           % len(times), "ms": 1e3 * best}
     print(json.dumps(line), flush=True)
+    if parity and not parity.get("ok", True):
+        raise SystemExit("bench.py: parity check failed: %r" % parity)
 
 
-def gcn_epoch_timing(device, epochs=5):
-    """Forward + backward of the reference's 2-layer GCN on a graph with the shape its tooling names for Reddit
-    (232,965 vertices, ~114.6 M directed edges incl. self-loops, 602 -> 128 -> 41): once with this library's
-    aggregation, once with cuSPARSE called as the reference calls it; the dense layers are the same cuBLAS calls."""
+def large_graph_timing(device, workload, steps=10):
+    """The aggregation on one of the large directed R-MAT graphs (the workload the roofline target is stated on),
+    one GPU, device-resident operands rotating over two buffer sets; plus 20 PageRank power iterations (F = 1) on the
+    same graph."""
+    import drone_b200 as db
+    cfg = dict(WORKLOADS[workload])
+    n, index, dst, in_deg, out_deg = build_graph(cfg, device)
+    nnz, f = dst.numel(), cfg["features"]
+    plan = db.AggregationPlan(index, dst, in_degree=in_deg, out_degree=out_deg, orientations=db.PLAN_AT)
+    plan.reserve(f)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(cfg["seed"])
+    xs = [torch.randn((n, f), device=device, generator=gen) for _ in range(2)]
+    ys = [torch.empty((n, f), device=device) for _ in range(2)]
+
+    def step(i):
+        plan.spmm(db.OP_AT, xs[i % 2], out=ys[i % 2])
+    for i in range(3):
+        step(i)
+    blocks = time_blocks(step, steps, torch.cuda.synchronize)
+    ms = float(np.median(blocks)) / steps
+    b_alg = algorithmic_bytes(n, nnz, f)
+    peak, peak_src = hbm_peak()
+    out = {"workload": "%s: R-MAT scale %d ef %d directed +I, F=%d" % (workload, cfg["scale"], cfg["edge_factor"], f),
+           "vertices": n, "nnz": nnz, "ms_per_step": ms, "steps": steps, "timed_blocks": len(blocks),
+           "nnzF_per_s": nnz * f / (ms * 1e-3), "algorithmic_bytes": b_alg,
+           "algorithmic_GBps": b_alg / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": b_alg / (ms * 1e-3) / 1e9 / peak,
+           "peak": peak, "peak_source": peak_src, "hot_row_table": bool(plan.stats().hot_rows_tagged)}
+    del xs, ys
+    plan.close()
+    torch.cuda.empty_cache()
+    out["pagerank"] = one_part_pagerank(device, n, index, dst, out_deg, 20)
+    return out
+
+
+def glorot_weights(dims, device, seed=7):
+    """(U - 0.5) * 2 * sqrt(6 / (in + out)) per layer (cuda_gcn/src/cuda/cuda_kernel.cu:469-474), same on every rank."""
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(seed)
+    return [((torch.rand((a, b), generator=gen) - 0.5) * 2 * (6.0 / (a + b)) ** 0.5).to(device)
+            for a, b in zip(dims[:-1], dims[1:])]
+
+
+def hashed_normal(global_ids, f, seed, device):
+    """N(0,1) features that depend only on (seed, global vertex id, column): every rank that holds a vertex makes the
+    same row.  Counter hash (splitmix64 on int64, wrapping) + Box-Muller, on the device."""
+    ids = torch.as_tensor(np.asarray(global_ids).astype(np.int64), device=device)
+    ctr = (ids[:, None] * f + torch.arange(f, device=device, dtype=torch.int64)[None, :]) * 2 + seed * 0x5851F42D
+
+    def mix(x):
+        x = x + (-7046029254386353131)              # 0x9E3779B97F4A7C15 as a signed 64-bit value
+        x = (x ^ ((x >> 30) & 0x3FFFFFFFF)) * (-4658895280553007687)
+        x = (x ^ ((x >> 27) & 0x1FFFFFFFFF)) * (-7723592293110705685)
+        return x ^ ((x >> 31) & 0x1FFFFFFFF)
+    u1 = ((mix(ctr) >> 11) & 0x1FFFFFFFFFFFFF).double() / 9007199254740992.0
+    u2 = ((mix(ctr + 1) >> 11) & 0x1FFFFFFFFFFFFF).double() / 9007199254740992.0
+    z = torch.sqrt(-2.0 * torch.log(u1.clamp_(min=1e-300))) * torch.cos(2.0 * np.pi * u2)
+    return z.float()
+
+
+def hashed_labels(global_ids, classes, seed, device):
+    ids = torch.as_tensor(np.asarray(global_ids).astype(np.int64), device=device)
+    h = (ids * 2654435761 + seed * 40503) & 0x7FFFFFFF
+    return (h % classes).to(torch.int32)
+
+
+def time_epochs(step, epochs, sync):
+    """ms per epoch of broadcast + forward + backward + gradient reduce, events around `epochs` of them."""
+    def one(_):
+        step.broadcast_weights()
+        step.forward()
+        step.backward()
+        step.reduce_gradients()
+    for i in range(2):
+        one(i)
+    blocks = time_blocks(one, epochs, sync)
+    return float(np.median(blocks)) / epochs, len(blocks)
+
+
+def gcn_epoch_timing(device, cfg_name, with_cusparse, epochs=5):
+    """Forward + backward of the GCN of configuration `cfg_name` on one GPU: once with this library's aggregation
+    (ReLU in the aggregation's store), once with the ReLU as a pass of its own, and (with_cusparse) once with cuSPARSE
+    called as the reference calls it; the dense layers are the same cuBLAS calls in every arm."""
     import drone_b200 as db
     from drone_b200 import gcn, graphgen as gg
-    n, u, v = gg.powerlaw_graph(232965, 57_200_000, seed=20261203, device=device)
+    cfg = GCN_CONFIGS[cfg_name]
+    dims = cfg["dims"]
+    n, u, v = gg.powerlaw_graph(cfg["vertices"], cfg["pairs"], seed=cfg["seed"], device=device)
     index, dst = gg.csr_by_source(u, v, n)
     in_deg, out_deg = gg.degrees(u, v, n)
     del u, v
@@ -399,78 +636,140 @@ def gcn_epoch_timing(device, epochs=5):
         pass
     g = G()
     g.plan = db.AggregationPlan(index, dst, in_degree=in_deg, out_degree=out_deg)
+    g.plan.reserve(max(dims[1:]))
     g.mirror2worker = None
-    gen = torch.Generator(device=device)
-    gen.manual_seed(7)
-    x = torch.randn((n, 602), device=device, generator=gen)
-    truth = torch.randint(0, 41, (n,), device=device, generator=gen, dtype=torch.int32)
-    w1 = (torch.rand((602, 128), device=device, generator=gen) - 0.5) * 2 * (6.0 / (602 + 128)) ** 0.5
-    w2 = (torch.rand((128, 41), device=device, generator=gen) - 0.5) * 2 * (6.0 / (128 + 41)) ** 0.5
+    ids = np.arange(n)
+    x = hashed_normal(ids, dims[0], 7, device)
+    truth = hashed_labels(ids, dims[-1], 7, device)
+    weights = glorot_weights(dims, device)
     torch.backends.cuda.matmul.allow_tf32 = False
-    out = {"vertices": n, "nnz": int(dst.numel()), "dims": [602, 128, 41], "epochs_timed": epochs}
+    out = {"config": cfg["descr"], "vertices": n, "nnz": int(dst.numel()), "dims": dims, "epochs_per_block": epochs}
 
-    def time_step(step):
-        for _ in range(2):
-            step.forward()
-            step.backward()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(epochs):
-            step.forward()
-            step.backward()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / epochs
-
-    step = gcn.GCNStep(g, x, truth, w1, w2)
-    out["ms_drone_b200"] = time_step(step)
+    step = gcn.GCN(g, x, truth, weights, fuse_relu=True)
+    out["ms_drone_b200"], out["timed_blocks"] = time_epochs(step, epochs, torch.cuda.synchronize)
     loss_ours = float(step.loss)
-    # aggregation alone, both orientations and widths of one epoch
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(epochs):
-        g.plan.spmm(db.OP_AT, step.h1, out=step.z1)
-        g.plan.spmm(db.OP_AT, step.h2, out=step.logits)
-        g.plan.spmm(db.OP_A, step.d_logits, out=step.d_h2)
-        g.plan.spmm(db.OP_A, step.d_z1, out=step.d_h1)
-    e1.record()
-    torch.cuda.synchronize()
-    out["ms_aggregation_only_drone_b200"] = e0.elapsed_time(e1) / epochs
-    try:
-        from baseline import cusparse_ref
-        csr = {db.OP_A: g.plan.csr(db.OP_A), db.OP_AT: g.plan.csr(db.OP_AT)}
-        cache = {}
+    out["loss"] = loss_ours
+    unfused = gcn.GCN(g, x, truth, weights, fuse_relu=False)
+    out["ms_drone_b200_relu_as_own_pass"], _ = time_epochs(unfused, epochs, torch.cuda.synchronize)
+    out["loss_rel_diff_fused_vs_own_pass"] = abs(float(unfused.loss) - loss_ours) / max(abs(loss_ours), 1e-30)
+    del unfused
 
-        def cusparse_aggregate(op, src, dst_t):
-            key = (op, src.data_ptr(), dst_t.data_ptr())
-            if key not in cache:
-                rp, co, va = csr[op]
-                cache[key] = cusparse_ref.CusparseSpmm(rp, co, va, src, dst_t)
-            cache[key].run()
-            return dst_t
+    # aggregation alone: every GraphSum call of one epoch, both orientations, at the widths of this model
+    def aggregations(_):
+        for l in range(step.n_layers):
+            g.plan.spmm(db.OP_AT, step.h[l], out=step.z[l])
+        for l in range(step.n_layers - 1, -1, -1):
+            g.plan.spmm(db.OP_A, step.d_logits if l == step.n_layers - 1 else step.d_a[l], out=step.d_h[l])
+    blocks = time_blocks(aggregations, epochs, torch.cuda.synchronize)
+    agg_ms = float(np.median(blocks)) / epochs
+    nnz = int(dst.numel())
+    b_alg = sum(2 * algorithmic_bytes(n, nnz, d) for d in dims[1:])
+    peak, _ = hbm_peak()
+    out["aggregation_only"] = {"ms": agg_ms, "calls": 2 * step.n_layers, "algorithmic_bytes": b_alg,
+                               "algorithmic_GBps": b_alg / (agg_ms * 1e-3) / 1e9,
+                               "frac_of_hbm_peak": b_alg / (agg_ms * 1e-3) / 1e9 / peak}
+    per_width = {}
+    for d in sorted(set(dims[1:])):
+        xs = [torch.randn((n, d), device=device) for _ in range(2)]
+        ys = [torch.empty((n, d), device=device) for _ in range(2)]
+        blocks = time_blocks(lambda i: g.plan.spmm(db.OP_AT, xs[i % 2], out=ys[i % 2]), 5, torch.cuda.synchronize, 0.1)
+        per_width["F=%d" % d] = float(np.median(blocks)) / 5
+        del xs, ys
+    out["aggregation_ms_by_width"] = per_width
 
-        ref_step = gcn.GCNStep(g, x, truth, w1, w2, aggregate=cusparse_aggregate)
-        ref_step.backward_needs = None
-        # d_z1 is a fresh tensor every backward in GCNStep; give cuSPARSE a stable buffer
-        orig_backward = ref_step.backward
-        stable = torch.empty_like(ref_step.z1)
+    if with_cusparse:
+        try:
+            from baseline import cusparse_ref
+            csr = {db.OP_A: g.plan.csr(db.OP_A), db.OP_AT: g.plan.csr(db.OP_AT)}
+            cache = {}
 
-        def backward_stable():
-            ref_step.aggregate(db.OP_A, ref_step.d_logits, ref_step.d_h2)
-            d_a1 = ref_step.d_h2 @ ref_step.w2.t()
-            ref_step.d_w2 = ref_step.z1.t() @ ref_step.d_h2
-            torch.mul(d_a1, ref_step.mask, out=stable)
-            ref_step.aggregate(db.OP_A, stable, ref_step.d_h1)
-            ref_step.d_w1 = ref_step.x.t() @ ref_step.d_h1
-        ref_step.backward = backward_stable
-        out["ms_cusparse_aggregation"] = time_step(ref_step)
-        out["loss_rel_diff"] = abs(float(ref_step.loss) - loss_ours) / max(abs(loss_ours), 1e-30)
-        for c in cache.values():
-            c.close()
-    except Exception as e:
-        out["ms_cusparse_aggregation"] = None
-        out["cusparse_error"] = repr(e)
+            def cusparse_aggregate(op, src, dst_t):
+                key = (op, src.data_ptr(), dst_t.data_ptr())
+                if key not in cache:
+                    rp, co, va = csr[op]
+                    cache[key] = cusparse_ref.CusparseSpmm(rp, co, va, src, dst_t)
+                cache[key].run()
+                return dst_t
+
+            ref_step = gcn.GCN(g, x, truth, weights, aggregate=cusparse_aggregate)
+            out["ms_cusparse_aggregation"], _ = time_epochs(ref_step, epochs, torch.cuda.synchronize)
+            out["loss_rel_diff_vs_cusparse"] = abs(float(ref_step.loss) - loss_ours) / max(abs(loss_ours), 1e-30)
+            out["cusparse_note"] = ("the same step with cusparseSpMM (ALG_DEFAULT, row-major, as at "
+                                    "cuda_gcn/src/cuda/cuda_module.cu:233-246 / 323-336) in place of this library's "
+                                    "aggregation; not the reference's own epoch loop")
+            for c in cache.values():
+                c.close()
+        except Exception as e:
+            out["ms_cusparse_aggregation"] = None
+            out["cusparse_error"] = repr(e)
+    g.plan.close()
+    return out
+
+
+def distribute_graph(n, make_edges, world, rank, device, keep_self_loops=True):
+    """Rank 0 makes the edge list (make_edges() -> (u, v) int32 CUDA tensors), EBV-partitions it and hands every rank
+    its own edges and the global tables.  Returns (partition, in_degree, out_degree, total_edges, partition_seconds)."""
+    from drone_b200 import graphgen as gg, partition as pt
+    part, extra, part_s = None, (), 0.0
+    if rank == 0:
+        u, v = make_edges()
+        in_deg, out_deg = gg.degrees(u, v, n)
+        uh, vh = u.cpu().numpy(), v.cpu().numpy()
+        del u, v
+        torch.cuda.empty_cache()
+        t0 = time.perf_counter()
+        part = pt.ebv_partition(n, uh, vh, world, keep_self_loops=keep_self_loops)
+        part_s = time.perf_counter() - t0
+        del uh, vh
+        extra = (in_deg.cpu().numpy(), out_deg.cpu().numpy())
+        del in_deg, out_deg
+    part, (in_deg, out_deg), total_e = pt.scatter_partition(part, n, world, device, extra=extra, n_extra=2)
+    return part, in_deg, out_deg, total_e, part_s
+
+
+def gcn_epoch_multi(device, cfg_name, rank, world, comm, sync, epochs=5):
+    """The GCN epoch of configuration `cfg_name` over WORLD_SIZE EBV parts: weight broadcast, forward (aggregation +
+    mirror/master exchange per layer), backward (same, on the gradients), gradient reduce to rank 0."""
+    import torch.distributed as dist
+    from drone_b200 import gcn, graphgen as gg, graphsum as gs
+    cfg = GCN_CONFIGS[cfg_name]
+    dims = cfg["dims"]
+    n = cfg["vertices"]
+
+    def make_edges():
+        _, u, v = gg.powerlaw_graph(n, cfg["pairs"], seed=cfg["seed"], device=device)
+        return u, v
+    part, in_deg, out_deg, total_e, part_s = distribute_graph(n, make_edges, world, rank, device)
+    graph = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, device, max_features=max(dims[1:]))
+    graph.plan.reserve(max(dims[1:]))
+    graph.xplan.enable_p2p(comm)
+    l2g = graph.host.l2g
+    x = hashed_normal(l2g, dims[0], 7, device)
+    truth = hashed_labels(l2g, dims[-1], 7, device)
+    weights = glorot_weights(dims, device)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    step = gcn.GCN(graph, x, truth, weights, comm=comm, worker_num=world)
+    ms, nblocks = time_epochs(step, epochs, sync)
+    t = torch.tensor([ms], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    # the loss over the master copies of all ranks (every labelled vertex once)
+    logits = step.z[-1]
+    zmax = logits.max(dim=1, keepdim=True).values
+    lse = torch.log(torch.exp(logits - zmax).sum(dim=1)) + zmax.squeeze(1)
+    per_row = lse - logits.gather(1, truth.long().unsqueeze(1)).squeeze(1)
+    masters = graph.mirror2worker == -1
+    acc = torch.stack([(per_row * masters).double().sum(), masters.double().sum()])
+    dist.all_reduce(acc)
+    up, down, _ = graph.xplan.counts()
+    stats = torch.tensor([graph.n_local, int(up.sum() + down.sum())], device=device, dtype=torch.int64)
+    dist.all_reduce(stats)
+    out = {"config": cfg["descr"], "vertices": n, "nnz": int(total_e), "dims": dims, "parts": world,
+           "ms_per_epoch": float(t), "epochs_per_block": epochs, "timed_blocks": nblocks,
+           "loss_over_masters": float(acc[0] / acc[1]), "replication_factor": float(stats[0]) / n,
+           "mirror_sync_bytes_per_epoch_all_ranks": int(stats[1]) * 4 * 2 * sum(dims[1:]),
+           "partition_seconds": part_s,
+           "step": "weight bcast + forward + backward + gradient reduce; exchange over peer memory after every aggregation"}
+    graph.plan.close()
     return out
 
 
@@ -614,9 +913,90 @@ def pagerank_timing(device):
     return out
 
 
+class MultiStep:
+    """Local aggregation + mirror/master exchange of one rank, plain or in row groups (PipelinedAggregation)."""
+
+    def __init__(self, graph, comm, f, exchange, dense=None):
+        self.graph, self.comm, self.f, self.exchange_kind, self.dense = graph, comm, f, exchange, dense
+        self.piped = {}
+
+    def exchange(self, rows):
+        from drone_b200 import graphsum as gs
+        if self.dense is not None:
+            gs.exchange_sum_dense(self.dense, self.comm, rows)
+        else:
+            gs.exchange_sum(self.graph.xplan, self.comm, rows)
+
+    def use_groups(self, groups):
+        """Switch to `groups` row groups (1 = aggregation, then exchange).  Rebuilds the plan's work lists."""
+        from drone_b200 import graphsum as gs
+        self.groups = groups
+        for p in self.piped.values():
+            p.close()
+        self.piped = {}
+        if groups > 1:
+            self.piped[groups] = gs.PipelinedAggregation(self.graph, self.comm, self.f, n_groups=groups,
+                                                         p2p=self.exchange_kind == "p2p")
+        else:
+            self.graph.plan.set_row_classes(None, 1)
+
+    def __call__(self, op, x, y):
+        if self.groups > 1:
+            self.piped[self.groups](op, x, y)
+        else:
+            self.graph.plan.spmm(op, x, out=y)
+            self.exchange(y)
+
+
+def multi_parity(device, rank, world, comm, exchange, groups):
+    """Aggregation + exchange over WORLD_SIZE EBV parts of a seeded R-MAT-13 graph (F = 32, both orientations)
+    against the double-precision oracle of the whole graph, compared by global vertex id on every rank: the largest
+    error relative to the largest element, maximum over ranks."""
+    import torch.distributed as dist
+    import drone_b200 as db
+    from drone_b200 import graphgen as gg, graphsum as gs
+    n, f = 1 << 13, 32
+
+    def make_edges():
+        _, u, v = gg.rmat_graph(13, 16, seed=20261142, device=device, symmetrise=False, self_loops="add")
+        return u, v
+    part, in_deg, out_deg, _, _ = distribute_graph(n, make_edges, world, rank, device)
+    x = gg.seeded_normal(5, (n, f))
+    want = torch.zeros((2, n, f), dtype=torch.float64, device=device)
+    if rank == 0:
+        from oracle import oracle
+        oracle.build()
+        _, u, v = gg.rmat_graph(13, 16, seed=20261142, symmetrise=False, self_loops="add")
+        index, dst = gg.csr_by_source(u, v, n)
+        val = oracle.csr_values_f32(index.numpy(), dst.numpy(), in_deg, out_deg)
+        want[0] = torch.as_tensor(oracle.graphsum_forward_f64(x, index.numpy(), dst.numpy(), val), device=device)
+        want[1] = torch.as_tensor(oracle.graphsum_backward_f64(x, index.numpy(), dst.numpy(), val), device=device)
+    dist.broadcast(want, 0)
+    graph = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, device, max_features=f)
+    if exchange == "p2p":
+        graph.xplan.enable_p2p(comm)
+    step = MultiStep(graph, comm, f, exchange)
+    l2g = torch.as_tensor(graph.host.l2g.astype(np.int64), device=device)
+    xl = torch.as_tensor(x, device=device)[l2g]
+    worst = torch.zeros(1, dtype=torch.float64, device=device)
+    for g_ in sorted({1, groups}):
+        step.use_groups(g_)
+        for k, op in enumerate((db.OP_AT, db.OP_A)):
+            y = torch.full((graph.n_local, f), float("nan"), device=device)
+            step(op, xl, y)
+            torch.cuda.synchronize()
+            ref = want[k][l2g]
+            err = (y.double() - ref).abs().max() / want[k].abs().max()
+            worst = torch.maximum(worst, torch.nan_to_num(err, nan=1e30).reshape(1))
+    step.use_groups(1)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    graph.plan.close()
+    return float(worst)
+
+
 def run_ours_multi(args, cfg):
     """One process per GPU: R-MAT graph EBV-partitioned into WORLD_SIZE parts, every step is the local
-    aggregation Y_p = A_p^T X_p followed by the mirror/master exchange over NCCL."""
+    aggregation Y_p = A_p^T X_p followed by the mirror/master exchange."""
     import torch.distributed as dist
     import drone_b200 as db
     from drone_b200 import graphgen as gg
@@ -630,25 +1010,80 @@ def run_ours_multi(args, cfg):
     device = torch.device("cuda", local_rank)
     dist.init_process_group("nccl", device_id=device)
     lib = db.lib()
+    chosen = args.chosen
+    comm = gs.Comm(rank, world)
+    t_start = time.perf_counter()
+
+    def sync():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    line_extra = {}
+    if "parity" in chosen:
+        err = multi_parity(device, rank, world, comm, args.exchange, 2)
+        line_extra["parity"] = {"max_rel_err": err, "ranks": world, "tolerance": 1e-5, "ok": err <= 1e-5,
+                                "case": "R-MAT-13 +I over %d EBV parts, F=32, aggregation + exchange (%s transport; one "
+                                        "piece and in 2 row groups), both orientations, against the double oracle by "
+                                        "global id" % (world, args.exchange)}
+        if not err <= 1e-5:
+            if rank == 0:
+                print(json.dumps({"metric": "spmm_nnzF_per_s", "n_gpus": world, "parity": line_extra["parity"],
+                                  "error": "parity check failed"}), flush=True)
+            raise SystemExit("bench.py: multi-GPU parity check failed: %g" % err)
+
+    line = run_partitioned_workload(args, cfg, device, rank, world, comm, sync, headline=True)
+    if rank == 0:
+        line.update(line_extra)
+
+    def section(name, fn):
+        if name not in chosen:
+            return
+        try:
+            res = fn()
+        except Exception as e:
+            res = {"error": repr(e)}
+        if rank == 0:
+            line[name] = res
+        torch.cuda.empty_cache()
+
+    section("gcn_epoch", lambda: gcn_epoch_multi(device, "c3", rank, world, comm, sync))
+    section("gcn_c4", lambda: gcn_epoch_multi(device, "c4", rank, world, comm, sync, epochs=3))
+    if "strong" in chosen and args.scaling != "strong":
+        name = args.strong_workload
+        if name == "auto":       # the 2^26-vertex graph takes about two minutes of set-up (generation + partitioning)
+            name = "rmat26"
+        sargs = argparse.Namespace(**vars(args))
+        sargs.workload, sargs.scaling, sargs.pagerank_iters = name, "strong", 20
+        scfg = dict(WORKLOADS[name])
+        section("strong", lambda: run_partitioned_workload(sargs, scfg, device, rank, world, comm, sync, headline=False))
+    if rank == 0:
+        line["wall_seconds"] = time.perf_counter() - t_start
+        print(json.dumps(line), flush=True)
+    comm.close()
+    dist.destroy_process_group()
+
+
+def run_partitioned_workload(args, cfg, device, rank, world, comm, sync, headline):
+    """Times aggregation + exchange over the EBV parts of the workload's graph.  Returns the JSON line (headline) or
+    a section (same keys, without the end-to-end part) on rank 0; other ranks get a dict they do not use."""
+    import torch.distributed as dist
+    import drone_b200 as db
+    from drone_b200 import graphgen as gg
+    from drone_b200 import graphsum as gs
+    from drone_b200 import partition as pt
+    lib = db.lib()
     f = cfg["features"]
     n = 1 << cfg["scale"]
-
-    # rank 0 builds and partitions the graph; every rank receives its own edges and the global tables
     t_setup = time.perf_counter()
-    part, extra = None, ()
-    if rank == 0:
+
+    def make_edges():
         _, u, v = gg.rmat_graph(cfg["scale"], cfg["edge_factor"], seed=cfg["seed"], device=device,
                                 symmetrise=cfg["symmetrise"], self_loops="add")
-        in_deg, out_deg = gg.degrees(u, v, n)
-        uh, vh = u.cpu().numpy(), v.cpu().numpy()
-        del u, v
-        part = pt.ebv_partition(n, uh, vh, world, keep_self_loops=True)
-        del uh, vh
-        extra = (in_deg.cpu().numpy(), out_deg.cpu().numpy())
-        del in_deg, out_deg
-    part, (in_deg, out_deg), total_e = pt.scatter_partition(part, n, world, device, extra=extra, n_extra=2)
+        return u, v
+    part, in_deg, out_deg, total_e, part_s = distribute_graph(n, make_edges, world, rank, device)
     graph = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, device, max_features=f)
-    comm = gs.Comm(rank, world)
+    graph.plan.reserve(f)
     if args.exchange == "p2p":
         graph.xplan.enable_p2p(comm)
     dense = pt.DenseExchangePlan(part, graph.host, f) if args.exchange == "dense" else None
@@ -663,64 +1098,47 @@ def run_ours_multi(args, cfg):
     gen.manual_seed(cfg["seed"] + rank)
     xs = [torch.randn((graph.n_local, f), device=device, generator=gen) for _ in range(nbuf)]
     ys = [torch.empty((graph.n_local, f), device=device) for _ in range(nbuf)]
-
-    def exchange(rows):
-        if dense is not None:
-            gs.exchange_sum_dense(dense, comm, rows)
-        else:
-            gs.exchange_sum(graph.xplan, comm, rows)
-
-    piped = None
-    if args.pipeline_groups > 1 and dense is None:
-        piped = gs.PipelinedAggregation(graph, comm, f, n_groups=args.pipeline_groups, p2p=args.exchange == "p2p")
+    mstep = MultiStep(graph, comm, f, args.exchange, dense)
 
     def step(i):
-        if piped is not None:
-            piped(db.OP_AT, xs[i % nbuf], ys[i % nbuf])
-            return
-        graph.plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
-        exchange(ys[i % nbuf])
+        mstep(db.OP_AT, xs[i % nbuf], ys[i % nbuf])
 
-    for i in range(max(args.warmup, 3)):
+    # row groups: as asked, or the fastest of 1 / 2 / 4 (every rank takes the same decision from the reduced times)
+    candidates = [args.pipeline_groups] if args.pipeline_groups > 0 else ([1] if dense is not None else [1, 2, 4])
+    trial = {}
+    for g_ in candidates:
+        mstep.use_groups(g_)
+        for i in range(3):
+            step(i)
+        if len(candidates) > 1:
+            blocks = time_blocks(step, max(5, min(args.steps, 10)), sync, min_seconds=0.05)
+            t = torch.tensor([float(np.median(blocks))], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            trial[g_] = float(t) / max(5, min(args.steps, 10))
+    groups = min(trial, key=trial.get) if trial else candidates[0]
+    if groups != mstep.groups:
+        mstep.use_groups(groups)
+    warmup = max(args.warmup, 3)
+    for i in range(warmup):
         step(i)
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(index=local_rank)
+    sampler = ClockSampler(index=device.index)
     sampler.start()
     launches0 = lib.drone_kernel_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    launches = lib.drone_kernel_launch_count() - launches0
-    t_ms = torch.tensor([e0.elapsed_time(e1)], device=device)
-    dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    ms = float(t_ms) / args.steps
+    blocks = time_blocks(step, args.steps, sync)
+    launches = (lib.drone_kernel_launch_count() - launches0) // len(blocks)
     sampler.in_timed_region = False
-    for i in range(max(10, min(2000, int(400.0 / max(ms, 0.05))))):   # from the reduced time: same count on every rank
-        step(i)
-    torch.cuda.synchronize()
     clocks = sampler.finish()
+    t_ms = torch.tensor(blocks, device=device)
+    dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)          # per block: the slowest rank
+    ms = float(t_ms.median()) / args.steps
 
     # local aggregation alone (for the roofline of the kernel) and exchange alone
-    e0.record()
-    for i in range(args.steps):
-        graph.plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf])
-    e1.record()
-    torch.cuda.synchronize()
-    spmm_ms = e0.elapsed_time(e1) / args.steps
-    dist.barrier()
-    e0.record()
-    for i in range(args.steps):
-        exchange(ys[i % nbuf])
-    e1.record()
-    torch.cuda.synchronize()
-    xchg = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device)
+    mstep.use_groups(1)
+    blocks_a = time_blocks(lambda i: graph.plan.spmm(db.OP_AT, xs[i % nbuf], out=ys[i % nbuf]), args.steps,
+                           torch.cuda.synchronize, min_seconds=0.1)
+    spmm_ms = float(np.median(blocks_a)) / args.steps
+    blocks_x = time_blocks(lambda i: mstep.exchange(ys[i % nbuf]), args.steps, sync, min_seconds=0.1)
+    xchg = torch.tensor([float(np.median(blocks_x)) / args.steps, spmm_ms], device=device)
     dist.all_reduce(xchg, op=dist.ReduceOp.MAX)
 
     # PageRank power iterations (F = 1) over the same partition: pull along in-edges + the same exchange per iteration
@@ -729,8 +1147,8 @@ def run_ours_multi(args, cfg):
         from drone_b200 import pagerank as prm
         pr = prm.PageRank(graph, n, comm=comm, use_double=False)
         pr.power_iterate(3)
-        torch.cuda.synchronize()
-        dist.barrier()
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         pr.power_iterate(args.pagerank_iters)
         e1.record()
@@ -742,66 +1160,76 @@ def run_ours_multi(args, cfg):
         dist.all_reduce(mass)
         pr_result = {"iterations": args.pagerank_iters, "ms_per_iteration": float(pr_ms),
                      "nnz_per_s": nnz_total / (float(pr_ms) * 1e-3), "sum_over_masters": float(mass),
-                     "dtype": "f32", "exchange": "grouped ncclSend/ncclRecv of all boundary vertices + scalar all-reduce"}
+                     "mirror_sync_bytes_per_iteration_all_ranks": None,
+                     "dtype": "f32", "exchange": pr.transport_name() if hasattr(pr, "transport_name") else
+                     "grouped ncclSend/ncclRecv of all boundary vertices + scalar all-reduce"}
         pr.close()
 
-    # end to end: host operands in, host result out, every step
-    xh = torch.empty((graph.n_local, f), dtype=torch.float32).pin_memory()
-    yh = torch.empty((graph.n_local, f), dtype=torch.float32).pin_memory()
-    xh.copy_(xs[0])
-    dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(args.e2e_steps):
-        xs[0].copy_(xh, non_blocking=True)
-        step(0)
-        yh.copy_(ys[0], non_blocking=True)
-        torch.cuda.synchronize()
-    e2e_t = torch.tensor([(time.perf_counter() - t0) / args.e2e_steps], device=device, dtype=torch.float64)
-    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
-    stats = torch.tensor([graph.n_local, nnz_local, sync_bytes, launches], device=device, dtype=torch.int64)
+    e2e = None
+    if headline and "e2e" in args.chosen:
+        # end to end: host operands in, host result out, every step
+        xh = torch.empty((graph.n_local, f), dtype=torch.float32).pin_memory()
+        yh = torch.empty((graph.n_local, f), dtype=torch.float32).pin_memory()
+        xh.copy_(xs[0])
+        sync()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            xs[0].copy_(xh, non_blocking=True)
+            step(0)
+            yh.copy_(ys[0], non_blocking=True)
+            torch.cuda.synchronize()
+        e2e_t = torch.tensor([(time.perf_counter() - t0) / args.e2e_steps], device=device, dtype=torch.float64)
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+        e2e = float(e2e_t)
+    stats = torch.tensor([graph.n_local, nnz_local, sync_bytes, launches, int(up.sum() + down.sum())], device=device,
+                         dtype=torch.int64)
     gathered = [torch.zeros_like(stats) for _ in range(world)]
     dist.all_gather(gathered, stats)
-
-    if rank == 0:
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.exists(peaks_path):
-            peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
-        else:
-            peak, peak_src = 6650.0, "fallback"
-        b_alg = algorithmic_bytes(graph.n_local, nnz_local, f)
-        achieved = b_alg / (spmm_ms * 1e-3) / 1e9
-        g = torch.stack(gathered).cpu().numpy()
-        line = {
-            "metric": "spmm_nnzF_per_s", "value": nnz_total * f / (ms * 1e-3), "unit": "nnz*F/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": dict(workload_descr(args, cfg, n, nnz_total), parts=world, partitioner="EBV",
-                           pipeline_groups=args.pipeline_groups if piped is not None else 1,
-                           replication_factor=float(g[:, 0].sum()) / n,
-                           edge_imbalance=float(g[:, 1].max() * world / g[:, 1].sum())),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "algorithmic_bytes": b_alg,
-                         "kernel": "rank 0's local drone_spmm call, timed alone", "ms": spmm_ms},
-            "exchange": {"ms": float(xchg), "mirror_sync_bytes_per_step_all_ranks": int(g[:, 2].sum()),
-                         "mirror_sync_bytes_per_step_rank0": sync_bytes, "collective": {"p2p": "peer-memory stores + epoch flags (3 fused kernels)",
-                                        "nccl": "grouped ncclSend/ncclRecv x2",
-                                        "dense": "ncclReduceScatter + ncclAllGather over the boundary"}[args.exchange],
-                         "dense_boundary_rows": dense.boundary_rows() if dense is not None else None},
-            "e2e": {"value": nnz_total * f / float(e2e_t), "unit": "nnz*F/s", "h2d_bytes_per_step": int(g[:, 0].sum()) * f * 4,
-                    "d2h_bytes_per_step": int(g[:, 0].sum()) * f * 4, "ms_per_step": 1e3 * float(e2e_t),
-                    "steps": args.e2e_steps},
-            "gpu_launches": int(g[:, 3].sum()), "clocks": clocks, "setup_s": setup_s,
-        }
-        if pr_result is not None:
-            line["pagerank"] = pr_result
-        print(json.dumps(line), flush=True)
-    comm.close()
-    dist.destroy_process_group()
+    g = torch.stack(gathered).cpu().numpy()
+    peak, peak_src = hbm_peak()
+    b_alg = algorithmic_bytes(graph.n_local, nnz_local, f)
+    achieved = b_alg / (spmm_ms * 1e-3) / 1e9
+    if pr_result is not None:
+        pr_result["mirror_sync_bytes_per_iteration_all_ranks"] = int(g[:, 4].sum()) * 8     # {value, flag} per boundary vertex
+    line = {
+        "metric": "spmm_nnzF_per_s", "value": nnz_total * f / (ms * 1e-3), "unit": "nnz*F/s", "n_gpus": world,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": dict(workload_descr(args, cfg, n, nnz_total), parts=world, partitioner="EBV",
+                       pipeline_groups=groups, pipeline_trial_ms={str(k): v for k, v in trial.items()},
+                       replication_factor=float(g[:, 0].sum()) / n,
+                       edge_imbalance=float(g[:, 1].max() * world / g[:, 1].sum())),
+        "timed_blocks": len(blocks), "timed_ms_total": float(np.sum(blocks)),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_src, "algorithmic_bytes": b_alg,
+                     "kernel": "rank 0's local drone_spmm call, timed alone", "ms": spmm_ms},
+        "exchange": {"ms": float(xchg[0]), "aggregation_ms_slowest_rank": float(xchg[1]),
+                     "mirror_sync_bytes_per_step_all_ranks": int(g[:, 2].sum()),
+                     "mirror_sync_bytes_per_step_rank0": sync_bytes,
+                     "collective": {"p2p": "peer-memory stores + epoch flags (push_up, add_push_down, scatter; waits in one-block kernels)",
+                                    "nccl": "grouped ncclSend/ncclRecv x2",
+                                    "dense": "ncclReduceScatter + ncclAllGather over the boundary"}[args.exchange],
+                     "dense_boundary_rows": dense.boundary_rows() if dense is not None else None},
+        "gpu_launches": int(g[:, 3].sum()), "clocks": clocks, "setup_s": setup_s, "partition_seconds": part_s,
+    }
+    if e2e is not None:
+        line["e2e"] = {"value": nnz_total * f / e2e, "unit": "nnz*F/s", "h2d_bytes_per_step": int(g[:, 0].sum()) * f * 4,
+                       "d2h_bytes_per_step": int(g[:, 0].sum()) * f * 4, "ms_per_step": 1e3 * e2e, "steps": args.e2e_steps}
+    if pr_result is not None:
+        line["pagerank"] = pr_result
+    for p_ in mstep.piped.values():
+        p_.close()
+    graph.plan.close()
+    del xs, ys, graph
+    torch.cuda.empty_cache()
+    return line
 
 
 def main():
     args = parse_args()
+    if args.record_traffic:
+        record_traffic(args.record_traffic, args.workload)
+        return
     cfg = workload_config(args)
     if args.impl == "reference":
         run_reference(args, cfg)

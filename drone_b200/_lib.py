@@ -56,7 +56,7 @@ class PlanStats(C.Structure):
         ("n_partials", C.c_int * 2),
         ("scratch_bytes", C.c_longlong),
         ("last_slice_width", C.c_int),
-        ("reserved_", C.c_int),
+        ("hot_rows_tagged", C.c_int),
     ]
 
 

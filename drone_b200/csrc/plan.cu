@@ -4,6 +4,7 @@
 #include "plan.cuh"
 
 #include <cub/cub.cuh>
+#include <algorithm>
 #include <cstdlib>
 #include <new>
 
@@ -652,13 +653,15 @@ static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_ind
         const int rc = build_transpose(p, st);
         if (rc) return rc;
     }
-    // Table of hot rows: only for graphs whose dense operand is far larger than L2 at the usual widths.  Its size
-    // is DRONE_HOT_TABLE_MB (default 64; 0 switches it off); a position is tagged for as many rows as fit at a width
-    // of 32 floats, calls with wider rows use a prefix of the positions.
+    // Table of hot rows: only for graphs whose dense operand is far larger than L2 at the usual widths (at least
+    // DRONE_HOT_MIN_ROWS rows, default 2^23: measured on R-MAT graphs with 32 features, the table gains 10 % at 2^26
+    // rows and loses 10 % at 2^22, where most gathers hit L2 anyway).  Its size is DRONE_HOT_TABLE_MB (default 64;
+    // 0 switches it off); a position is tagged for as many rows as fit at a width of 32 floats, calls with wider rows
+    // use a prefix of the positions.
     {
         const char *mb = getenv("DRONE_HOT_TABLE_MB");
         const long long table_mb = (mb && *mb) ? atoll(mb) : 64;
-        const int min_rows = env_int("DRONE_HOT_MIN_ROWS", 1 << 22);
+        const int min_rows = env_int("DRONE_HOT_MIN_ROWS", 1 << 23);
         long long n_hot = table_mb * (1LL << 20) / 128;
         if (n_hot > n_rows / 4) n_hot = n_rows / 4;
         if (allow_tags && table_mb > 0 && n_rows >= min_rows && n_rows < (1 << 29) && nnz > 0 && n_hot > 0) {
@@ -858,6 +861,7 @@ int drone_plan_get_stats(const drone_plan *p, drone_plan_stats *out) {
     }
     out->scratch_bytes = (long long)p->scratch_bytes;
     out->last_slice_width = p->last_slice_width;
+    out->hot_rows_tagged = std::max(p->side[0].n_hot, p->side[1].n_hot);
     return DRONE_OK;
 }
 

@@ -137,17 +137,27 @@ struct Gather {
     int hot_rows = 0;                   // tagged positions below this are served from the table
 };
 
-// Address of the row a (possibly tagged) column stands for.  The table is written by the fill kernel that precedes
-// the gathering kernels of the same call in stream order, so the read-only load path is safe for it as well.
+// Tagged columns whose position lies beyond the rows the table holds at this call's width are turned back into
+// plain columns (one look-up in hot_ids).  Done on the freshly loaded (col) registers of a lane, before they are
+// handed around, so that the gathers themselves need no branch and no dependent load.
+template <bool HOT>
+__device__ __forceinline__ unsigned resolve_column(const Gather &g, unsigned c) {
+    if (HOT && (c & kHotTag) && (int)(c & kHotMask) >= g.hot_rows) c = (unsigned)__ldg(g.hot_ids + (c & kHotMask));
+    return c;
+}
+
+// Address of the row a resolved column stands for: a row of the table for a tagged column, a row of X otherwise.
+// Branch-free, so that the gathers of a batch stay independent loads in flight together.  The table is written by
+// the fill kernel that precedes the gathering kernels of the same call in stream order, so the read-only load path
+// is safe for it as well.
 template <int VEC, bool HOT>
 __device__ __forceinline__ const typename Vec<VEC>::type *row_address(const Gather &g, unsigned c, int gl, int nvec) {
     using V = typename Vec<VEC>::type;
-    if (HOT && (c & kHotTag)) {
-        const unsigned pos = c & kHotMask;
-        if ((int)pos < g.hot_rows) return reinterpret_cast<const V *>(g.hot) + (long long)pos * nvec + gl;
-        c = (unsigned)__ldg(g.hot_ids + pos);   // tagged for a longer table than this call's feature width allows
-    }
-    return reinterpret_cast<const V *>(g.X) + (long long)c * g.ldv + gl;
+    if (!HOT) return reinterpret_cast<const V *>(g.X) + (long long)c * g.ldv + gl;
+    const bool tagged = (c & kHotTag) != 0;
+    const V *base = reinterpret_cast<const V *>(tagged ? g.hot : g.X);
+    const long long stride = tagged ? (long long)nvec : g.ldv;
+    return base + (long long)(c & kHotMask) * stride + gl;
 }
 
 // ---------------------------------------------------------------------------
@@ -208,7 +218,7 @@ spmm_short_stream_kernel(const int *__restrict__ s_range_row, int n_ranges, cons
         if (!UNIT) v_next = ld_stream(s_val + k + gl, pol_stream);
     }
     for (int base = 0; base < maxlen; base += G) {
-        const unsigned c = c_next;
+        const unsigned c = (c_next & ~kColMask) | resolve_column<HOT>(g, c_next & kColMask);
         const float v = v_next;
         c_next = 0;
         if (!UNIT) v_next = 0.f;
@@ -297,6 +307,7 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
                 c = ld_stream(col + k0 + lane, pol_stream);
                 if (!UNIT) v = ld_stream(val + k0 + lane, pol_stream);
             }
+            c = (int)resolve_column<HOT>(g, (unsigned)c);
         }
         for (int j = 0; j < in_group; ++j) {
             const int row = __shfl_sync(0xffffffffu, desc.x, j), k0 = __shfl_sync(0xffffffffu, desc.y, j);
@@ -349,7 +360,7 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
 #pragma unroll
                         for (int p = 0; p < VPL; ++p) Vec<VEC>::fma(acc[p], vv[u], x[u][p]);
                 }
-                c = c_next;
+                c = (int)resolve_column<HOT>(g, (unsigned)c_next);
                 v = v_next;
             }
             // last, partial batch (entries beyond the chunk were loaded as zeros)
@@ -402,7 +413,7 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
                         if (EXACT || gl + p * G < nvec) out[p * G] = acc[p];
                 }
             }
-            c = c_ahead;
+            c = (int)resolve_column<HOT>(g, (unsigned)c_ahead);
             v = v_ahead;
         }  // chunks of the group
         group = __shfl_sync(0xffffffffu, next_group, 0);

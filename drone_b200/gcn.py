@@ -1,55 +1,98 @@
-"""Host-side mirror of the reference's 2-layer GCN step around the aggregation path (CUDAGCN::forward / backward,
-cuda_gcn/src/cuda/cuda_gcn.cu:44-83,119-170).  Only the GraphSum layers are this library's kernels; the dense
-layers either side stay on cuBLAS (torch.matmul) and the element-wise layers on torch, as in the reference they stay
-on cuBLAS and small element-wise kernels.  Used to time an epoch and to check gradients end to end.
+"""Host-side mirror of the reference's GCN step around the aggregation path (CUDAGCN::forward / backward,
+cuda_gcn/src/cuda/cuda_gcn.cu:44-83,119-170), for any number of layers.  Only the GraphSum layers, the masking of
+mirror rows and the weight broadcast / gradient reduce are this library's kernels and NCCL calls; the dense layers
+either side stay on cuBLAS (torch.matmul) and cross-entropy on torch, as in the reference they stay on cuBLAS and
+small element-wise kernels.  Used to time an epoch and to check gradients end to end.
+
+Layer l = 1..L:  H_l = A_{l-1} · W_l  (Matmul)  ->  Z_l = Â^T-aggregation of H_l + mirror/master sync (GraphSum)
+                 ->  A_l = ReLU(Z_l) for l < L, logits = Z_L.
+The reference's module list is this with L = 2 (cuda_gcn.cu:44-83); its layer interface allows more.
 """
 import torch
 
 from ._lib import OP_A, OP_AT
-from .graphsum import exchange_sum
+from .graphsum import clear_mirror_rows, exchange_sum
 
 
-class GCNStep:
-    """forward + backward of Matmul -> GraphSum -> ReLU -> Matmul -> GraphSum -> cross-entropy on one rank.
+class GCN:
+    """forward + backward of [Matmul -> GraphSum -> ReLU] x (L-1) -> Matmul -> GraphSum -> cross-entropy on one rank.
 
-    aggregate(op, x, out): the sparse aggregation (default: graph.plan.spmm); sync(rows): the mirror/master
-    exchange (default: over `comm` when worker_num > 1)."""
+    weights: list of L tensors [d_{l-1}, d_l].
+    aggregate(op, x, out, relu): the sparse aggregation (default: graph.plan.spmm with the ReLU done in the store
+    when fuse_relu is set); sync(rows): the mirror/master exchange (default: over `comm` when worker_num > 1).
+    With fuse_relu = False the ReLU runs as its own pass, as CUDAReLU::forward does (cuda_module.cu:498-511)."""
 
-    def __init__(self, graph, x, truth, w1, w2, comm=None, worker_num=1, aggregate=None):
-        self.g, self.x, self.truth, self.w1, self.w2 = graph, x, truth, w1, w2
+    def __init__(self, graph, x, truth, weights, comm=None, worker_num=1, aggregate=None, fuse_relu=True, sync=None):
+        self.g, self.x, self.truth = graph, x, truth
+        self.weights = list(weights)
+        self.n_layers = len(self.weights)
         self.comm, self.worker_num = comm, worker_num
-        self.aggregate = aggregate or (lambda op, src, out: graph.plan.spmm(op, src, out=out))
+        self.fuse_relu = bool(fuse_relu) and aggregate is None
+        self.aggregate = aggregate or (lambda op, src, out, relu=False: graph.plan.spmm(op, src, out=out, relu=relu))
+        self._custom_aggregate = aggregate is not None
+        self._sync = sync
         n, dev = x.shape[0], x.device
-        hid, out = w1.shape[1], w2.shape[1]
-        self.h1 = torch.empty((n, hid), device=dev)
-        self.z1 = torch.empty((n, hid), device=dev)
-        self.h2 = torch.empty((n, out), device=dev)
-        self.logits = torch.empty((n, out), device=dev)
-        self.d_h2 = torch.empty((n, out), device=dev)
-        self.d_h1 = torch.empty((n, hid), device=dev)
-        self.not_mirror = (graph.mirror2worker == -1).unsqueeze(1) if worker_num > 1 else None
+        dims = [w.shape[1] for w in self.weights]
+        self.h = [torch.empty((n, d), device=dev) for d in dims]        # Matmul outputs
+        self.z = [torch.empty((n, d), device=dev) for d in dims]        # GraphSum outputs (after ReLU for l < L)
+        self.d_h = [torch.empty((n, d), device=dev) for d in dims]      # gradients w.r.t. the Matmul outputs
+        self.d_a = [torch.empty((n, d), device=dev) for d in dims[:-1]] # gradients w.r.t. the ReLU outputs (masked in place)
+        self.mirror2worker = graph.mirror2worker if worker_num > 1 else None
         self.labelled = truth >= 0
         self.safe_truth = truth.clamp(min=0).long()
+        self.d_w = [None] * self.n_layers
+        self.loss = None
 
+    # ----- pieces -----
     def sync(self, rows):
-        if self.worker_num > 1:
+        if self._sync is not None:
+            self._sync(rows)
+        elif self.worker_num > 1:
             exchange_sum(self.g.xplan, self.comm, rows)
 
+    def _aggregate(self, op, src, out, relu=False):
+        if self._custom_aggregate:
+            self.aggregate(op, src, out)
+            if relu:
+                out.clamp_(min=0)
+        else:
+            self.aggregate(op, src, out, relu)
+        return out
+
+    def broadcast_weights(self):
+        """weight_broadcast_value_nccl at the start of every forward pass (cuda_communicate.cu:99-105)."""
+        if self.worker_num > 1:
+            for w in self.weights:
+                self.comm.bcast(w, root=0)
+
+    def reduce_gradients(self):
+        """weight_reduce_grad_nccl after the backward pass (cuda_communicate.cu:107-115): sums land on rank 0."""
+        if self.worker_num > 1:
+            for dw in self.d_w:
+                self.comm.reduce_sum(dw, root=0)
+
+    # ----- the step -----
     def forward(self):
-        torch.matmul(self.x, self.w1, out=self.h1)                     # CUDAMatmul::forward
-        self.aggregate(OP_AT, self.h1, self.z1)                        # CUDAGraphSum::forward
-        self.sync(self.z1)
-        self.mask = self.z1 > 0                                        # CUDAReLU::forward, in place
-        self.z1.mul_(self.mask)
-        torch.matmul(self.z1, self.w2, out=self.h2)
-        self.aggregate(OP_AT, self.h2, self.logits)
-        self.sync(self.logits)
+        a = self.x
+        last = self.n_layers - 1
+        for l, w in enumerate(self.weights):
+            torch.matmul(a, w, out=self.h[l])                              # CUDAMatmul::forward
+            relu = l < last
+            # The mirror/master sync adds partial sums, so the ReLU can sit in the aggregation's store only when there
+            # is nothing to add afterwards (one worker); with several workers it follows the sync.
+            fused = relu and self.fuse_relu and self.worker_num == 1 and self._sync is None
+            self._aggregate(OP_AT, self.h[l], self.z[l], relu=fused)       # CUDAGraphSum::forward
+            self.sync(self.z[l])
+            if relu and not fused:
+                self.z[l].clamp_(min=0)                                    # CUDAReLU::forward, in place
+            a = self.z[l]
+        logits = self.z[last]
         # CUDACrossEntropyLoss::forward: loss = mean over labelled rows; gradient not divided by the count
-        zmax = self.logits.max(dim=1, keepdim=True).values
-        e = torch.exp(self.logits - zmax)
+        zmax = logits.max(dim=1, keepdim=True).values
+        e = torch.exp(logits - zmax)
         s = e.sum(dim=1, keepdim=True)
         self.d_logits = e / s
-        picked = self.logits.gather(1, self.safe_truth.unsqueeze(1))
+        picked = logits.gather(1, self.safe_truth.unsqueeze(1))
         per_row = (torch.log(s) - (picked - zmax)).squeeze(1)
         count = self.labelled.sum().clamp(min=1)
         self.loss = (per_row * self.labelled).sum() / count
@@ -58,15 +101,37 @@ class GCNStep:
         return self.loss
 
     def backward(self):
-        self.aggregate(OP_A, self.d_logits, self.d_h2)                 # CUDAGraphSum::backward
-        self.sync(self.d_h2)
-        d_a1 = self.d_h2 @ self.w2.t()                                 # CUDAMatmul::backward: dA first ...
-        dc = self.d_h2 * self.not_mirror if self.not_mirror is not None else self.d_h2   # ... clear_mirror_grad ...
-        self.d_w2 = self.z1.t() @ dc                                   # ... then dW
-        d_z1 = d_a1 * self.mask                                        # CUDAReLU::backward
-        self.aggregate(OP_A, d_z1, self.d_h1)
-        self.sync(self.d_h1)
-        dc = self.d_h1 * self.not_mirror if self.not_mirror is not None else self.d_h1
-        self.d_w1 = self.x.t() @ dc
-        self.d_z1 = d_z1
-        return self.d_w1, self.d_w2
+        g = self.d_logits
+        for l in range(self.n_layers - 1, -1, -1):
+            self._aggregate(OP_A, g, self.d_h[l])                          # CUDAGraphSum::backward
+            self.sync(self.d_h[l])
+            a_prev = self.z[l - 1] if l > 0 else self.x
+            if l > 0:
+                d_a = torch.matmul(self.d_h[l], self.weights[l].t(), out=self.d_a[l - 1])   # CUDAMatmul::backward: dA first ...
+            if self.mirror2worker is not None:
+                clear_mirror_rows(self.d_h[l], self.mirror2worker)         # ... clear_mirror_grad (in place) ...
+            self.d_w[l] = a_prev.t() @ self.d_h[l]                         # ... then dW
+            if l > 0:
+                g = d_a.mul_(self.z[l - 1] > 0)                            # CUDAReLU::backward: the mask is (output > 0)
+                if l == 1:
+                    self.d_z1 = g
+        return tuple(self.d_w)
+
+
+class GCNStep(GCN):
+    """The reference's own two-layer model, with the names its variables carry (cuda_gcn.cu:44-83)."""
+
+    def __init__(self, graph, x, truth, w1, w2, comm=None, worker_num=1, aggregate=None, fuse_relu=True):
+        super().__init__(graph, x, truth, [w1, w2], comm=comm, worker_num=worker_num, aggregate=aggregate,
+                         fuse_relu=fuse_relu)
+
+    w1 = property(lambda self: self.weights[0])
+    w2 = property(lambda self: self.weights[1])
+    h1 = property(lambda self: self.h[0])
+    z1 = property(lambda self: self.z[0])
+    h2 = property(lambda self: self.h[1])
+    logits = property(lambda self: self.z[1])
+    d_h1 = property(lambda self: self.d_h[0])
+    d_h2 = property(lambda self: self.d_h[1])
+    d_w1 = property(lambda self: self.d_w[0])
+    d_w2 = property(lambda self: self.d_w[1])

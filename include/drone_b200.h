@@ -95,7 +95,7 @@ typedef struct drone_plan_stats {
     int       n_partials[2];     /* partial-sum slots = chunks of split rows */
     long long scratch_bytes;     /* bytes of partial-sum scratch currently held */
     int       last_slice_width;  /* columns per slice of the most recent aggregation call (0: it ran in one piece) */
-    int       reserved_;
+    int       hot_rows_tagged;   /* columns tagged for the table of hot rows (0: the plan has no such table) */
 } drone_plan_stats;
 
 int drone_plan_get_stats(const drone_plan *plan, drone_plan_stats *out);
