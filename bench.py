@@ -80,7 +80,7 @@ def record_traffic(csv_path, workload):
     import subprocess
     per_kernel, calls = {}, 0
     with open(csv_path) as fh:
-        rows = [r for r in csv.reader(fh) if len(r) > 5]
+        rows = [r for r in csv.reader(l for l in fh if not l.startswith("==")) if len(r) > 5]
     head = next(r for r in rows if "Metric Name" in r)
     ki, mi, vi, ui = head.index("Kernel Name"), head.index("Metric Name"), head.index("Metric Value"), head.index("Metric Unit")
     for r in rows:
@@ -106,6 +106,7 @@ def record_traffic(csv_path, workload):
 
 
 def parse_args():
+    global MIN_TIMED_SECONDS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
@@ -132,6 +133,8 @@ def parse_args():
     ap.add_argument("--pagerank-iters", type=int, default=0,
                     help="also time this many PageRank power iterations (F=1) over the workload's graph / partition")
     ap.add_argument("--strong-workload", default="auto", help="several GPUs, section strong: rmat26 | rmat24 | auto")
+    ap.add_argument("--min-timed-seconds", type=float, default=MIN_TIMED_SECONDS,
+                    help="repeat the block of --steps steps until this much has been timed (0: one block; for profiler runs)")
     ap.add_argument("--record-traffic", metavar="CSV", help="write profiles/spmm_<workload>_dram_traffic.txt from an ncu CSV and exit")
     args = ap.parse_args()
     names = SECTIONS_ONE + SECTIONS_MULTI
@@ -151,6 +154,7 @@ def parse_args():
     if args.no_gcn:
         chosen -= {"gcn_epoch", "gcn_c4", "pagerank", "minprop", "jobs", "rmat26", "strong"}
     args.chosen = chosen
+    MIN_TIMED_SECONDS = args.min_timed_seconds
     return args
 
 
@@ -322,10 +326,13 @@ def workload_descr(args, cfg, n, nnz):
         "l2_policy": "operands rotate over 3 buffer sets; CSR + H + Y exceed the 126 MB L2"}
 
 
-def time_blocks(step, steps, sync, min_seconds=MIN_TIMED_SECONDS, max_blocks=400):
+def time_blocks(step, steps, sync, min_seconds=None, max_blocks=400):
     """Times blocks of exactly `steps` calls of step(i) between two CUDA events on the current stream, block after
     block until min_seconds have been timed (at least one block).  sync() is called on both sides of every block (device
     synchronisation, plus a barrier on several GPUs).  Returns the list of block times in ms."""
+    if min_seconds is None:
+        min_seconds = MIN_TIMED_SECONDS
+    min_seconds = min(min_seconds, MIN_TIMED_SECONDS)
     blocks, total = [], 0.0
     i = 0
     while len(blocks) < max_blocks and (not blocks or total < min_seconds * 1e3):

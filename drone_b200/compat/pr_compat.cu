@@ -8,6 +8,8 @@
 #include <cstring>
 #include <vector>
 
+#include <ctime>
+#include <sys/stat.h>
 #include <unistd.h>
 
 #include "../../include/drone_b200.h"
@@ -23,6 +25,7 @@ struct GraphImpl {
     std::vector<int> g2l, l2g;
     std::vector<int> master_vertex, mirror_number, mirror_workers, mirror_vertex, master_worker;
     bool routes_built = false;
+    bool have_master_route = false, have_mirror_route = false;   // addMasterRoute / addMirrorRoute were called
     drone_xplan *xplan = nullptr;
     drone_comm *dcomm = nullptr;
     drone_pr *pr = nullptr;
@@ -120,7 +123,11 @@ Graph *build_graph(int globalVertexSize, int edgeSize, int *u, int *v, int worke
 
     // communicator: worker 0 publishes the id through ./nccl.id, the others wait for the file
     unsigned char id[DRONE_UNIQUE_ID_BYTES];
+    // A file left by an earlier run must not be taken for this run's id: worker 0 removes it before it makes the new
+    // one, and the others only accept a file written less than a minute before they got here.
+    const time_t entered = time(nullptr);
     if (workerId == 0) {
+        unlink("./nccl.id");
         check(drone_comm_unique_id(id, sizeof(id)), "drone_comm_unique_id");
         FILE *fp = fopen("./nccl.id.tmp", "wb");
         if (!fp || fwrite(id, sizeof(id), 1, fp) != 1) { printf("Failed: cannot write ./nccl.id\n"); exit(EXIT_FAILURE); }
@@ -128,7 +135,11 @@ Graph *build_graph(int globalVertexSize, int edgeSize, int *u, int *v, int worke
         rename("./nccl.id.tmp", "./nccl.id");
     } else {
         FILE *fp = nullptr;
-        for (int tries = 0; tries < 600 && !(fp = fopen("./nccl.id", "rb")); ++tries) usleep(100000);
+        for (int tries = 0; tries < 600 && !fp; ++tries) {
+            struct stat info;
+            if (stat("./nccl.id", &info) == 0 && info.st_mtime >= entered - 60) fp = fopen("./nccl.id", "rb");
+            if (!fp) usleep(100000);
+        }
         if (!fp || fread(id, sizeof(id), 1, fp) != 1) { printf("Failed: cannot read ./nccl.id\n"); exit(EXIT_FAILURE); }
         fclose(fp);
     }
@@ -163,6 +174,7 @@ void addMasterRoute(Graph *gp, int *masterVertex, int *mirrorNumber, int *mirror
     cudaSetDevice(gp->GID);
     gp->MasterSize = masterSize;
     gp->MirrorWorkerSize = mirrorWorkerSize;
+    g->have_master_route = true;
     g->master_vertex.assign(masterVertex, masterVertex + masterSize);
     g->mirror_number.assign(mirrorNumber, mirrorNumber + masterSize);
     g->mirror_workers.assign(mirrorWorkers, mirrorWorkers + mirrorWorkerSize);
@@ -172,8 +184,28 @@ void addMirrorRoute(Graph *gp, int *mirrorVertex, int *masterWorker, int mirrorS
     GraphImpl *g = impl_of(gp);
     cudaSetDevice(gp->GID);
     gp->MirrorSize = mirrorSize;
+    g->have_mirror_route = true;
     g->mirror_vertex.assign(mirrorVertex, mirrorVertex + mirrorSize);
     g->master_worker.assign(masterWorker, masterWorker + mirrorSize);
+}
+
+// The PageRank job of a graph: transposed graph, work lists and state arrays.  Made when the out-degrees arrive
+// (the routes are known by then in the order the Go worker calls: build_graph, addMasterRoute, addMirrorRoute,
+// loadOutDegree), so that the first PR_PEVal only runs its superstep.
+static void ensure_pr_job(GraphImpl *g, Graph *gp, PRValues *values) {
+    if (g->pr) return;
+    build_routes(g);
+    check(drone_pr_create(&g->pr, g->n_local, g->global_v, g->n_edges, gp->index, gp->dst, values->outDegree,
+                          gp->Mirror2Worker, g->xplan, g->dcomm, /*use_double*/ 0, /*eps*/ 1e-6),
+          "drone_pr_create");
+    void *p = nullptr, *a = nullptr, *d = nullptr;
+    check(drone_pr_device_arrays(g->pr, &p, &a, &d, &gp->active, &gp->updateByMessage), "drone_pr_device_arrays");
+    values->prValue = (float *)p;
+    values->accValue = (float *)a;
+    values->diffValue = (float *)d;
+    values->sendID = values->recvID = nullptr;
+    values->sendDiff = values->recvDiff = nullptr;
+    values->globalAcc = values->globalDiff = nullptr;
 }
 
 void loadOutDegree(Graph *gp, PRValues *values, int *globalOutDegree) {
@@ -182,6 +214,7 @@ void loadOutDegree(Graph *gp, PRValues *values, int *globalOutDegree) {
     std::vector<int> local((size_t)g->n_local);
     for (int i = 0; i < g->n_local; ++i) local[i] = globalOutDegree[g->l2g[i]];
     values->outDegree = to_device(local);
+    if (g->have_master_route && g->have_mirror_route) ensure_pr_job(g, gp, values);
 }
 
 static Response run_step(Graph *gp, PRValues *values, int workerId, int workerNum, Comm *comm, bool peval) {
@@ -189,20 +222,7 @@ static Response run_step(Graph *gp, PRValues *values, int workerId, int workerNu
     check_cuda(cudaSetDevice(gp->GID), "cudaSetDevice");   // calls arrive on arbitrary OS threads
     (void)workerId;
     (void)workerNum;
-    if (!g->pr) {
-        build_routes(g);
-        check(drone_pr_create(&g->pr, g->n_local, g->global_v, g->n_edges, gp->index, gp->dst, values->outDegree,
-                              gp->Mirror2Worker, g->xplan, g->dcomm, /*use_double*/ 0, /*eps*/ 1e-6),
-              "drone_pr_create");
-        void *p = nullptr, *a = nullptr, *d = nullptr;
-        check(drone_pr_device_arrays(g->pr, &p, &a, &d, &gp->active, &gp->updateByMessage), "drone_pr_device_arrays");
-        values->prValue = (float *)p;
-        values->accValue = (float *)a;
-        values->diffValue = (float *)d;
-        values->sendID = values->recvID = nullptr;
-        values->sendDiff = values->recvDiff = nullptr;
-        values->globalAcc = values->globalDiff = nullptr;
-    }
+    ensure_pr_job(g, gp, values);      // only when the degrees were loaded before the routes
     drone_pr_response r;
     check(peval ? drone_pr_peval(g->pr, &r, comm->s) : drone_pr_inceval(g->pr, &r, comm->s),
           peval ? "drone_pr_peval" : "drone_pr_inceval");
