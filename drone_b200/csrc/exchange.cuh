@@ -46,6 +46,7 @@ struct drone_p2p {
     int *h_error = nullptr;             // pinned, mapped: set by a kernel whose wait ran out
     int *d_host_error = nullptr;        // device alias of h_error (written only when a wait runs out)
     int *d_error = nullptr;             // the same word in device memory: what the kernels poll
+    unsigned *d_done = nullptr;         // [2] blocks of push_up / add_push_down that have finished (last one publishes the flags)
 };
 
 #define DRONE_NCCL(call)                                                                 \

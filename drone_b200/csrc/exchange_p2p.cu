@@ -6,8 +6,9 @@
 //   add_push_down:  master row += its mirrors' rows in ascending rank order; the total goes to every mirror's
 //                   down-receive area
 //   scatter:        mirror rows take the totals
-// Ordering between GPUs uses one epoch word per (receiver, sender, direction): the sender's signal kernel runs after
-// its stores in stream order, fences, and writes the call's epoch; the receiver polls its own words in a ONE-BLOCK
+// Ordering between GPUs uses one epoch word per (receiver, sender, direction): the last block of the sender's store
+// kernel to finish (every block fences its stores and counts itself) writes the call's epoch; the receiver polls its
+// own words in a ONE-BLOCK
 // wait kernel launched in front of add_push_down and scatter.  (Waiting inside the row kernels themselves held every
 // SM slot those kernels were given for as long as the slowest peer took, which starved whatever ran beside the
 // exchange.)  Every wait is bounded: when it runs out the kernel records an error code in device memory and in pinned
@@ -71,6 +72,27 @@ __global__ void p2p_wait_kernel(const unsigned *flags, const int *need, int nran
     wait_for_peers(flags, need, nranks, epoch, error, host_error, code);
 }
 
+// End of a kernel that stored rows into peers' memory: every block fences its stores and counts itself; the last
+// one to arrive publishes `epoch` in every peer that expects a flag from this rank (and resets the counter for the
+// next launch).  Saves the one-block signal launch that would otherwise sit between the store kernel and the
+// peers' waits.
+__device__ void publish_when_all_blocks_done(unsigned *done, unsigned *const *peer_flag, const int *send_to, int nranks,
+                                             unsigned epoch) {
+    __shared__ int last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned arrived = atomicAdd(done, 1u);
+        last = arrived == gridDim.x - 1;
+        if (last) *done = 0;
+    }
+    __syncthreads();
+    if (last) {
+        __threadfence_system();
+        if ((int)threadIdx.x < nranks && send_to[threadIdx.x]) st_release_sys(peer_flag[threadIdx.x], epoch);
+    }
+}
+
 template <int VEC> struct PVec;
 template <> struct PVec<4> { using type = float4; };
 template <> struct PVec<1> { using type = float; };
@@ -83,7 +105,9 @@ __device__ __forceinline__ void vadd(float &a, const float &b) { a += b; }
 // rank store to the same owner at the same time, whose NVLink ingress then limits all of them.
 template <int VEC>
 __global__ void p2p_push_up_kernel(const float *__restrict__ rows, long long ld, const int4 *__restrict__ walk, int n_up,
-                                   int nvec, float *const *__restrict__ peer_up_recv, const int *error) {
+                                   int nvec, float *const *__restrict__ peer_up_recv, const int *error, unsigned *done,
+                                   unsigned *const *__restrict__ peer_flag, const int *__restrict__ send_to, int nranks,
+                                   unsigned epoch) {
     using V = typename PVec<VEC>::type;
     if (*(volatile const int *)error != 0) return;      // an earlier wait of this rank gave up: stay silent
     const long long total = (long long)n_up * nvec;
@@ -94,15 +118,7 @@ __global__ void p2p_push_up_kernel(const float *__restrict__ rows, long long ld,
         V *dst = reinterpret_cast<V *>(peer_up_recv[rec.y]) + (long long)rec.z * nvec + j;
         *dst = *(reinterpret_cast<const V *>(rows + (long long)rec.x * ld) + j);
     }
-}
-
-// After the stores of the preceding kernel: publish `epoch` in every peer that expects a flag from this rank.
-// A rank whose own wait ran out publishes nothing: its rows of this call were not written.
-__global__ void p2p_signal_kernel(unsigned *const *__restrict__ peer_flag, const int *__restrict__ send_to, int nranks,
-                                  unsigned epoch, const int *error) {
-    if (*(volatile const int *)error != 0) return;
-    __threadfence_system();
-    if ((int)threadIdx.x < nranks && send_to[threadIdx.x]) st_release_sys(peer_flag[threadIdx.x], epoch);
+    publish_when_all_blocks_done(done, peer_flag, send_to, nranks, epoch);
 }
 
 // Master rows: add the mirrors' rows (fixed order), keep the total, and store it into every mirror's down-receive area.
@@ -112,7 +128,8 @@ template <int VEC>
 __global__ void p2p_add_push_down_kernel(float *__restrict__ rows, long long ld, const int *__restrict__ m_rows,
                                          const int *__restrict__ m_off, const int4 *__restrict__ pairs, int n_masters,
                                          int nvec, const float *up_recv, float *const *__restrict__ peer_down_recv,
-                                         const int *error) {
+                                         const int *error, unsigned *done, unsigned *const *__restrict__ peer_flag,
+                                         const int *__restrict__ send_to, int nranks, unsigned epoch) {
     using V = typename PVec<VEC>::type;
     if (*(volatile const int *)error != 0) return;      // the wait in front of this launch gave up
     const V *recv = reinterpret_cast<const V *>(up_recv);
@@ -130,6 +147,7 @@ __global__ void p2p_add_push_down_kernel(float *__restrict__ rows, long long ld,
             *(reinterpret_cast<V *>(peer_down_recv[pr.y]) + (long long)pr.z * nvec + j) = acc;
         }
     }
+    publish_when_all_blocks_done(done, peer_flag, send_to, nranks, epoch);
 }
 
 // Mirror rows take the totals their masters stored.
@@ -181,6 +199,7 @@ void p2p_free(drone_p2p *p) {
     cudaFree(p->d_need_up); cudaFree(p->d_need_down);
     if (p->h_error) cudaFreeHost(p->h_error);
     cudaFree(p->d_error);
+    cudaFree(p->d_done);
     delete p;
 }
 
@@ -310,6 +329,8 @@ int drone_xplan_enable_p2p(drone_xplan *x, drone_comm *c, void *stream) {
         DRONE_CUDA(cudaHostGetDevicePointer(&p->d_host_error, p->h_error, 0));
         DRONE_CUDA(cudaMalloc(&p->d_error, sizeof(int)));
         DRONE_CUDA(cudaMemsetAsync(p->d_error, 0, sizeof(int), st));
+        DRONE_CUDA(cudaMalloc(&p->d_done, 2 * sizeof(unsigned)));
+        DRONE_CUDA(cudaMemsetAsync(p->d_done, 0, 2 * sizeof(unsigned), st));
         DRONE_CUDA(cudaMalloc(&t.d_mine, rec_bytes));
         DRONE_CUDA(cudaMalloc(&t.d_all, rec_bytes * P));
         DRONE_CUDA(cudaMalloc(&t.d_status, sizeof(int)));
@@ -428,25 +449,21 @@ int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t 
     timer.mark();
     if (n_up) {
         const int grid = p2p_grid((long long)n_up * nvec);
-        if (vec4) p2p_push_up_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error);
-        else p2p_push_up_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error);
+        if (vec4) p2p_push_up_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error, p->d_done, p->d_peer_flag_up, p->d_need_down, P, epoch);
+        else p2p_push_up_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error, p->d_done, p->d_peer_flag_up, p->d_need_down, P, epoch);
         DRONE_LAUNCH_CHECK("p2p_push_up_kernel");
     }
-    timer.mark();
-    p2p_signal_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_up, p->d_need_down, P, epoch, p->d_error);   // to the owners of my mirrors
-    DRONE_LAUNCH_CHECK("p2p_signal_kernel");
+    timer.mark();   // (the up flags go to the owners of my mirrors from the last block of push_up)
     timer.mark();
     if (n_m) {
         p2p_wait_kernel<<<1, 64, 0, st>>>(my_flags, p->d_need_up, P, epoch, p->d_error, p->d_host_error, 100);
         DRONE_LAUNCH_CHECK("p2p_wait_kernel");
         const int grid = p2p_grid((long long)n_m * nvec);
-        if (vec4) p2p_add_push_down_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, p->d_pairs, n_m, nvec, my_up_recv, p->d_peer_down_recv, p->d_error);
-        else p2p_add_push_down_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, p->d_pairs, n_m, nvec, my_up_recv, p->d_peer_down_recv, p->d_error);
+        if (vec4) p2p_add_push_down_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, p->d_pairs, n_m, nvec, my_up_recv, p->d_peer_down_recv, p->d_error, p->d_done + 1, p->d_peer_flag_down, p->d_need_up, P, epoch);
+        else p2p_add_push_down_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, p->d_pairs, n_m, nvec, my_up_recv, p->d_peer_down_recv, p->d_error, p->d_done + 1, p->d_peer_flag_down, p->d_need_up, P, epoch);
         DRONE_LAUNCH_CHECK("p2p_add_push_down_kernel");
     }
-    timer.mark();
-    p2p_signal_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_down, p->d_need_up, P, epoch, p->d_error);   // to the holders of my mirrors
-    DRONE_LAUNCH_CHECK("p2p_signal_kernel");
+    timer.mark();   // (the down flags go to the holders of my mirrors from the last block of add_push_down)
     timer.mark();
     if (n_up) {
         p2p_wait_kernel<<<1, 64, 0, st>>>(my_flags + P, p->d_need_down, P, epoch, p->d_error, p->d_host_error, 200);

@@ -649,6 +649,10 @@ static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_ind
     }
     DRONE_CUDA(cudaMalloc(&p->counter, sizeof(unsigned)));
     p->chunk_blocks_per_sm = env_int("DRONE_CHUNK_BLOCKS_PER_SM", 0);
+    {
+        const char *w = getenv("DRONE_WINDOW_CHUNKS");
+        p->window_chunks = !(w && w[0] == '0');
+    }
     if (orientations & DRONE_PLAN_AT) {
         const int rc = build_transpose(p, st);
         if (rc) return rc;

@@ -108,6 +108,7 @@ struct drone_plan {
     // tagged plans: the table of hot rows, refilled from X by every call
     float *hot_table = nullptr;
     size_t hot_table_bytes = 0;
+    bool window_chunks = true;     // long rows of unaligned operands through the aligned-window kernel (DRONE_WINDOW_CHUNKS=0: scalar kernel)
     int chunk_blocks_per_sm = 0;   // cap on resident blocks of the chunk kernel per SM (0: as many as fit)
     cudaStream_t own_stream = nullptr;
     // second stream and fork/join events: the short-row kernel runs beside the chunk kernels of the same call

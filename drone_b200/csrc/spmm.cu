@@ -114,6 +114,7 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
     a.join = p->join_event;
     a.row_class = opt.row_class;
     a.resident_per_sm = p->chunk_blocks_per_sm;
+    a.window_chunks = p->window_chunks;
     a.gather.ldv = vec4 ? ldx / 4 : ldx;
     for (int c0 = 0; c0 < F; c0 += width) {
         a.gather.X = X + c0;
@@ -342,6 +343,7 @@ extern "C" int drone_spmm_static_scratch(drone_plan *p, int orientation, int F, 
         a.counter = p->counter;
         a.st = (cudaStream_t)stream;
         a.resident_per_sm = p->chunk_blocks_per_sm;
+        a.window_chunks = p->window_chunks;
         const bool vec4 = drone::operands_allow_vec4(F, ldx, ldy, d_X, d_Y);
         a.gather.ldv = vec4 ? ldx / 4 : ldx;
         rc = drone::run_variant(p, s, a, vec4, F, false);

@@ -238,6 +238,42 @@ def test_table_of_hot_rows(cuda_device, oracle, f):
     assert torch.equal(tagged.spmm(db.OP_AT, x2), plain.spmm(db.OP_AT, x2))   # other operand: no stale table rows
 
 
+@pytest.mark.parametrize("f,lead,shift", [(41, 41, 0), (47, 47, 0), (33, 36, 0), (32, 40, 1), (64, 72, 3), (125, 125, 0), (9, 11, 2)])
+def test_rows_that_do_not_start_on_16_bytes(cuda_device, oracle, f, lead, shift):
+    """Operands whose rows start 0..3 floats past a 16-byte boundary (odd widths, odd leading dimensions, a view that
+    starts inside a row): the long rows go through the aligned-window kernel.  Against the double oracle, bit for
+    bit against the scalar kernel's plan being repeatable, and rows that are never gathered must not leak into the
+    result even when they hold NaN (the windows of their neighbours overlap them)."""
+    n, u, v = gg.rmat_graph(11, 16, seed=42, symmetrise=False, self_loops="drop")
+    u, v = u.numpy(), v.numpy()
+    keep = u != 7                                        # vertex 7 has no out-edge: X[7] is never gathered by A^T x
+    u, v = u[keep], v[keep]
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u, v)
+    xh = gg.seeded_normal(100 + f, (n, f))
+    big = torch.zeros((n + 1, lead + shift), device=cuda_device)
+    x = big[:n, shift:shift + f]
+    x.copy_(torch.as_tensor(xh))
+    x[7] = float("nan")
+    t = oracle.transpose_csr(n, n, index, dst, val)
+    xz = xh.copy()
+    xz[7] = 0.0
+    want, mag = oracle.spmm_csr_f64(*t, xz, with_abs=True)
+    for env in ({}, {"DRONE_SHORT_ROW_LIMIT": 4, "DRONE_CHUNK_NNZ": 16}, {"DRONE_WINDOW_CHUNKS": 0}):
+        plan = make_plan(cuda_device, index, dst, in_deg, out_deg, **env)
+        ybig = torch.full((n + 1, lead + shift), 3.0, device=cuda_device)
+        y = ybig[:n, shift:shift + f]
+        plan.spmm(db.OP_AT, x, out=y)
+        got = y.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert_close_to_oracle(got, want, mag)
+        keep_cols = torch.ones(lead + shift, dtype=torch.bool)
+        keep_cols[shift:shift + f] = False
+        assert (ybig[:, keep_cols] == 3.0).all() and (ybig[n] == 3.0).all()      # nothing outside the rows was written
+        y2 = torch.empty_like(ybig)[:n, shift:shift + f]
+        plan.spmm(db.OP_AT, x, out=y2)
+        assert torch.equal(y2, y)
+
+
 def test_golden_vectors(cuda_device, oracle):
     gold = np.load(os.path.join(ROOT, "tests", "golden", "spmm_golden.npz"))
     for name, scale, ef, seed, sym, loops, widths in make_golden.CASES:
