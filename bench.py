@@ -643,7 +643,7 @@ def gcn_epoch_timing(device, cfg_name, with_cusparse, epochs=5):
         pass
     g = G()
     g.plan = db.AggregationPlan(index, dst, in_degree=in_deg, out_degree=out_deg)
-    g.plan.reserve(max(dims[1:]))
+    g.plan.reserve(max(dims[1:]), padded_rows=True)
     g.mirror2worker = None
     ids = np.arange(n)
     x = hashed_normal(ids, dims[0], 7, device)
@@ -748,7 +748,7 @@ def gcn_epoch_multi(device, cfg_name, rank, world, comm, sync, epochs=5):
         return u, v
     part, in_deg, out_deg, total_e, part_s = distribute_graph(n, make_edges, world, rank, device)
     graph = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, device, max_features=max(dims[1:]))
-    graph.plan.reserve(max(dims[1:]))
+    graph.plan.reserve(max(dims[1:]), padded_rows=True)
     graph.xplan.enable_p2p(comm)
     l2g = graph.host.l2g
     x = hashed_normal(l2g, dims[0], 7, device)

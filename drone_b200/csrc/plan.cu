@@ -649,10 +649,6 @@ static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_ind
     }
     DRONE_CUDA(cudaMalloc(&p->counter, sizeof(unsigned)));
     p->chunk_blocks_per_sm = env_int("DRONE_CHUNK_BLOCKS_PER_SM", 0);
-    {
-        const char *w = getenv("DRONE_WINDOW_CHUNKS");
-        p->window_chunks = !(w && w[0] == '0');
-    }
     if (orientations & DRONE_PLAN_AT) {
         const int rc = build_transpose(p, st);
         if (rc) return rc;
@@ -768,6 +764,8 @@ int drone_plan_destroy(drone_plan *p) {
     cudaFree(p->row_order);
     cudaFree(p->counter);
     cudaFree(p->hot_table);
+    cudaFree(p->pad_x);
+    cudaFree(p->pad_y);
     cudaFree(p->scratch);
     cudaFree(p->stage_x);
     cudaFree(p->stage_y);

@@ -108,7 +108,12 @@ struct drone_plan {
     // tagged plans: the table of hot rows, refilled from X by every call
     float *hot_table = nullptr;
     size_t hot_table_bytes = 0;
-    bool window_chunks = true;     // long rows of unaligned operands through the aligned-window kernel (DRONE_WINDOW_CHUNKS=0: scalar kernel)
+    // Staging for operands whose rows cannot be read as float4 (a width that is not a multiple of 4, odd leading
+    // dimensions or addresses): [pad_rows, pad_width] floats each, made by drone_plan_reserve on request.  When
+    // present and large enough, such a call copies X into pad_x with rows padded to a multiple of 4 floats, runs the
+    // float4 kernels on the padded copies and copies the result out of pad_y.
+    float *pad_x = nullptr, *pad_y = nullptr;
+    int pad_width = 0;
     int chunk_blocks_per_sm = 0;   // cap on resident blocks of the chunk kernel per SM (0: as many as fit)
     cudaStream_t own_stream = nullptr;
     // second stream and fork/join events: the short-row kernel runs beside the chunk kernels of the same call

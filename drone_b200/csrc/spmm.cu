@@ -30,6 +30,27 @@ __global__ void degree_scales_kernel(const int *__restrict__ in_deg, const int *
     out_scale[i] = out_deg[i] > 0 ? (float)(1.0 / sqrt((double)out_deg[i])) : 0.f;
 }
 
+// padded[r, 0:F] = X[r, 0:F], padded[r, F:Fp] = 0          (Fp = F rounded up to a multiple of 4)
+__global__ void pad_rows_kernel(const float *__restrict__ X, long long ldx, int n_rows, int F, int Fp,
+                                float *__restrict__ padded) {
+    const long long total = (long long)n_rows * Fp;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / Fp), j = (int)(i - (long long)r * Fp);
+        padded[i] = j < F ? __ldg(X + (long long)r * ldx + j) : 0.f;
+    }
+}
+
+// Y[row, 0:F] = padded[row, 0:F] for the rows of `rows` (rows == NULL: rows 0..n_rows-1)
+__global__ void unpad_rows_kernel(const float *__restrict__ padded, int Fp, const int *__restrict__ rows, int n_rows, int F,
+                                  float *__restrict__ Y, long long ldy) {
+    const long long total = (long long)n_rows * F;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int k = (int)(i / F), j = (int)(i - (long long)k * F);
+        const int r = rows ? __ldg(rows + k) : k;
+        Y[(long long)r * ldy + j] = __ldcs(padded + (long long)r * Fp + j);
+    }
+}
+
 static int ensure_scratch(drone_plan *p, size_t bytes) {
     if (bytes <= p->scratch_bytes) return DRONE_OK;
     // grow: frees and reallocates, so earlier calls that use the scratch must have finished
@@ -93,7 +114,22 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
                      long long ldy, cudaStream_t st, const CallOptions &opt = CallOptions()) {
     const Side &s = p->side[orientation];
     if (p->n_rows == 0) return DRONE_OK;
-    const bool vec4 = operands_allow_vec4(F, ldx, ldy, X, Y);
+    bool vec4 = operands_allow_vec4(F, ldx, ldy, X, Y);
+    // Rows that cannot be read as float4 where they lie: with padded staging reserved, work on padded copies.
+    const int Fp = (F + 3) & ~3;
+    const bool padded = !vec4 && p->pad_x != nullptr && Fp <= p->pad_width && F >= 5;
+    float *const caller_Y = Y;
+    const long long caller_ldy = ldy;
+    const int caller_F = F;
+    if (padded) {
+        const long long total = (long long)p->n_rows * Fp;
+        pad_rows_kernel<<<(int)std::min<long long>((total + 255) / 256, 148 * 16), 256, 0, st>>>(X, ldx, p->n_rows, F, Fp, p->pad_x);
+        DRONE_LAUNCH_CHECK("pad_rows_kernel");
+        X = p->pad_x;
+        Y = p->pad_y;
+        ldx = ldy = F = Fp;
+        vec4 = true;
+    }
     const int slice = slice_width(p, F, vec4);
     const int width = slice > 0 ? slice : F;
     p->last_slice_width = slice;
@@ -114,13 +150,26 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
     a.join = p->join_event;
     a.row_class = opt.row_class;
     a.resident_per_sm = p->chunk_blocks_per_sm;
-    a.window_chunks = p->window_chunks;
     a.gather.ldv = vec4 ? ldx / 4 : ldx;
     for (int c0 = 0; c0 < F; c0 += width) {
         a.gather.X = X + c0;
         a.Y = Y + c0;
         const int rc = run_variant(p, s, a, vec4, width, opt.unit_values);
         if (rc) return rc;
+    }
+    if (padded) {
+        const int *rows = nullptr;
+        int n_out = p->n_rows;
+        if (opt.row_class >= 0 && p->row_order) {      // only the rows this call computed
+            rows = p->row_order + p->class_start[opt.row_class];
+            n_out = p->class_start[opt.row_class + 1] - p->class_start[opt.row_class];
+        }
+        if (n_out > 0) {
+            const long long total = (long long)n_out * caller_F;
+            unpad_rows_kernel<<<(int)std::min<long long>((total + 255) / 256, 148 * 16), 256, 0, st>>>(
+                p->pad_y, Fp, rows, n_out, caller_F, caller_Y, caller_ldy);
+            DRONE_LAUNCH_CHECK("unpad_rows_kernel");
+        }
     }
     return DRONE_OK;
 }
@@ -227,7 +276,7 @@ static int ensure_staging(drone_plan *p, size_t bytes) {
     return DRONE_OK;
 }
 
-int drone_plan_reserve(drone_plan *p, int max_features, int host_operands) {
+int drone_plan_reserve(drone_plan *p, int max_features, int what) {
     DRONE_REQUIRE(p != nullptr, "drone_plan_reserve: plan is NULL");
     DRONE_REQUIRE(max_features >= 1 && max_features <= 1024, "drone_plan_reserve: max_features=%d outside 1..1024",
                   max_features);
@@ -236,9 +285,25 @@ int drone_plan_reserve(drone_plan *p, int max_features, int host_operands) {
     if (rc) return rc;
     const size_t slots = (size_t)std::max(p->side[0].n_partials, p->side[1].n_partials);
     if (slots > 0 && (rc = ensure_scratch(p, sizeof(float) * slots * (size_t)max_features))) return rc;
-    if (host_operands) {
+    DRONE_REQUIRE((what & ~(DRONE_RESERVE_HOST_OPERANDS | DRONE_RESERVE_PADDED_ROWS)) == 0,
+                  "drone_plan_reserve: what=%d is not a combination of DRONE_RESERVE_* flags", what);
+    if (what & DRONE_RESERVE_HOST_OPERANDS) {
         if ((rc = ensure_staging(p, sizeof(float) * (size_t)p->n_rows * (size_t)max_features))) return rc;
         if (!p->own_stream) DRONE_CUDA(cudaStreamCreateWithFlags(&p->own_stream, cudaStreamNonBlocking));
+    }
+    if ((what & DRONE_RESERVE_PADDED_ROWS) && p->n_rows > 0) {
+        const int width = (max_features + 3) & ~3;
+        if (width > p->pad_width) {
+            DRONE_CUDA(cudaDeviceSynchronize());
+            cudaFree(p->pad_x);
+            cudaFree(p->pad_y);
+            p->pad_x = p->pad_y = nullptr;
+            p->pad_width = 0;
+            const size_t bytes = sizeof(float) * (size_t)p->n_rows * (size_t)width;
+            DRONE_CUDA(cudaMalloc(&p->pad_x, bytes));
+            DRONE_CUDA(cudaMalloc(&p->pad_y, bytes));
+            p->pad_width = width;
+        }
     }
     return DRONE_OK;
 }
@@ -321,7 +386,7 @@ extern "C" int drone_spmm_static_scratch(drone_plan *p, int orientation, int F, 
     if (p->n_rows == 0) return DRONE_OK;
     DRONE_REQUIRE(d_X && d_Y, "drone_spmm_static_scratch: NULL operand");
     DRONE_REQUIRE(d_X != d_Y, "drone_spmm_static_scratch: X and Y must not alias");
-    const size_t need = (size_t)s.n_partials * (size_t)F;
+    const size_t need = (size_t)s.n_partials * (size_t)((F + 3) & ~3);   // the width the kernels may run at (padded rows)
     if (need > drone::kStaticScratchFloats)
         return drone::set_error(DRONE_E_TOO_LARGE,
                                 "drone_spmm_static_scratch: this plan needs %zu bytes of partial sums at F=%d, the built-in "
@@ -333,20 +398,18 @@ extern "C" int drone_spmm_static_scratch(drone_plan *p, int orientation, int F, 
     float *partials = nullptr;
     int rc = drone::static_partials_address(p->device, &partials);
     if (rc == DRONE_OK) {
-        drone::SpmmArgs a;
-        a.side = &s;
-        a.n_rows = p->n_rows;
-        a.gather.X = d_X;
-        a.Y = d_Y;
-        a.ldy = ldy;
-        a.partials = partials;
-        a.counter = p->counter;
-        a.st = (cudaStream_t)stream;
-        a.resident_per_sm = p->chunk_blocks_per_sm;
-        a.window_chunks = p->window_chunks;
-        const bool vec4 = drone::operands_allow_vec4(F, ldx, ldy, d_X, d_Y);
-        a.gather.ldv = vec4 ? ldx / 4 : ldx;
-        rc = drone::run_variant(p, s, a, vec4, F, false);
+        // same route as drone_spmm (padded staging when the plan has it, no column slices), with the partial sums in
+        // the built-in array: the plan's own scratch pointer is swapped for the duration of the call
+        float *const plan_scratch = p->scratch;
+        const size_t plan_scratch_bytes = p->scratch_bytes;
+        const int plan_slices = p->slice_forced;
+        p->scratch = partials;
+        p->scratch_bytes = DRONE_STATIC_SCRATCH_BYTES;
+        p->slice_forced = 0;
+        rc = drone::spmm_impl(p, orientation, F, d_X, ldx, d_Y, ldy, (cudaStream_t)stream);
+        p->scratch = plan_scratch;
+        p->scratch_bytes = plan_scratch_bytes;
+        p->slice_forced = plan_slices;
     }
     if (dev != p->device) cudaSetDevice(dev);
     return rc;

@@ -422,140 +422,6 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
 }
 
 // ---------------------------------------------------------------------------
-// 2b. chunks of long rows when the rows of X cannot be read as float4 from their first element (a feature width
-//     that is not a multiple of 4, such as the class widths 41 and 47, or operands that are not 16-byte aligned).
-//     A row then starts 0..3 floats past a 16-byte boundary.  A lane group reads the ALIGNED 16-byte window that
-//     covers the row (G lanes, one float4 each: up to 3 floats before the row and up to 3 after it come along and
-//     are never used) and keeps one accumulator per starting offset, so that rows with the same offset add up
-//     float4 by float4 without any realignment; the four accumulators are shifted into place and added once per
-//     chunk.  Costs one 16-byte load per lane and row where the scalar kernel needs four 4-byte loads.
-//     The window never leaves the 16-byte-aligned span around the operand, which lies inside its allocation.
-//     Same chunk hand-out and (col, val) prefetch as the kernel above; F <= 4 * G - 3.
-// ---------------------------------------------------------------------------
-template <int G, int U, bool UNIT, bool HOT>
-__global__ void __launch_bounds__(256)
-spmm_chunks_window_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__restrict__ col,
-                          const float *__restrict__ val, Gather g, float *__restrict__ Y, long long ldy,
-                          float *__restrict__ partials, int F, Epilogue epi, unsigned *counter, int group_size) {
-    constexpr int RPW = 32 / G;
-    constexpr int UU = MinOf<U, G>::value;
-    const int lane = threadIdx.x & 31;
-    const int gl = lane & (G - 1);
-    const int gi = lane / G;
-    const unsigned long long pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
-
-    // the row a resolved column stands for (first element), in X or in the table of hot rows
-    auto row_start = [&](unsigned c) -> const float * {
-        if (HOT && (c & kHotTag)) return g.hot + (long long)(c & kHotMask) * F;
-        return g.X + (long long)(c & (HOT ? kHotMask : 0xffffffffu)) * g.ldv;
-    };
-
-    unsigned group = 0;
-    if (lane == 0) group = atomicAdd(counter, (unsigned)group_size);
-    group = __shfl_sync(0xffffffffu, group, 0);
-    while (group < (unsigned)n_chunks) {
-        int4 desc = make_int4(0, 0, 0, 0);
-        if (lane < group_size && group + lane < (unsigned)n_chunks)
-            desc = __ldg(reinterpret_cast<const int4 *>(chunks) + group + lane);
-        const int in_group = min(group_size, n_chunks - (int)group);
-        unsigned next_group = 0;
-        if (lane == 0) next_group = atomicAdd(counter, (unsigned)group_size);
-
-        int c = 0;
-        float v = UNIT ? 1.f : 0.f;
-        {
-            const int k0 = __shfl_sync(0xffffffffu, desc.y, 0), len = __shfl_sync(0xffffffffu, desc.z, 0);
-            if (lane < len) {
-                c = ld_stream(col + k0 + lane, pol_stream);
-                if (!UNIT) v = ld_stream(val + k0 + lane, pol_stream);
-            }
-            c = (int)resolve_column<HOT>(g, (unsigned)c);
-        }
-        for (int j = 0; j < in_group; ++j) {
-            const int row = __shfl_sync(0xffffffffu, desc.x, j), k0 = __shfl_sync(0xffffffffu, desc.y, j);
-            const int len = __shfl_sync(0xffffffffu, desc.z, j), slot = __shfl_sync(0xffffffffu, desc.w, j);
-            int c_ahead = 0;
-            float v_ahead = UNIT ? 1.f : 0.f;
-            if (j + 1 < in_group) {
-                const int nk0 = __shfl_sync(0xffffffffu, desc.y, j + 1), nlen = __shfl_sync(0xffffffffu, desc.z, j + 1);
-                if (lane < nlen) {
-                    c_ahead = ld_stream(col + nk0 + lane, pol_stream);
-                    if (!UNIT) v_ahead = ld_stream(val + nk0 + lane, pol_stream);
-                }
-            }
-            float4 acc[4];     // by starting offset of the row inside its window
-#pragma unroll
-            for (int q = 0; q < 4; ++q) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-
-            for (int base = 0; base < len; base += 32) {
-                int c_next = 0;
-                float v_next = UNIT ? 1.f : 0.f;
-                if (base + 32 + lane < len) {
-                    c_next = ld_stream(col + k0 + base + 32 + lane, pol_stream);
-                    if (!UNIT) v_next = ld_stream(val + k0 + base + 32 + lane, pol_stream);
-                }
-                const int cnt = min(32, len - base);
-                const int steps = (cnt + RPW - 1) / RPW;  // <= G
-                for (int t = 0; t < steps; t += UU) {
-                    int off[UU];
-                    float vv[UU];
-                    float4 x[UU];
-#pragma unroll
-                    for (int u = 0; u < UU; ++u) {
-                        const int e = (t + u) * RPW + gi;
-                        const unsigned cc = (unsigned)__shfl_sync(0xffffffffu, c, e & 31);
-                        vv[u] = UNIT ? 1.f : __shfl_sync(0xffffffffu, v, e & 31);
-                        const bool live = e < cnt;
-                        const uintptr_t first = reinterpret_cast<uintptr_t>(row_start(live ? cc : 0u));
-                        off[u] = live ? (int)((first >> 2) & 3) : -1;
-                        const float4 *window = reinterpret_cast<const float4 *>(first & ~(uintptr_t)15) + gl;
-                        x[u] = (live && 4 * gl < off[u] + F) ? ld_keep(window, pol_keep) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-#pragma unroll
-                    for (int u = 0; u < UU; ++u)
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            if (off[u] == q) Vec<4>::fma(acc[q], vv[u], x[u]);
-                }
-                c = (int)resolve_column<HOT>(g, (unsigned)c_next);
-                v = v_next;
-            }
-            // combine the lane groups, then shift every offset class into place: the lane ends with the row's floats
-            // 4*gl .. 4*gl+3
-#pragma unroll
-            for (int o = G; o < 32; o <<= 1)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) Vec<4>::add(acc[q], Vec<4>::shfl_xor(acc[q], o));
-            float out[4] = {acc[0].x, acc[0].y, acc[0].z, acc[0].w};
-#pragma unroll
-            for (int q = 1; q < 4; ++q) {
-                const float mine[4] = {acc[q].x, acc[q].y, acc[q].z, acc[q].w};
-                float next[4];       // the following lane's vector (garbage past the last lane of the group: unused)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) next[k] = __shfl_down_sync(0xffffffffu, mine[k], 1, G);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) out[k] += (k + q < 4) ? mine[k + q] : next[k + q - 4];
-            }
-            if (gi == 0) {
-                float *dst = slot < 0 ? Y + (long long)row * ldy : partials + (long long)slot * F;
-                const float scale = (slot < 0 && epi.row_scale) ? __ldg(epi.row_scale + row) : 1.f;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int f = 4 * gl + k;
-                    if (f < F) {
-                        if (slot < 0) st_stream(dst + f, finish_row<1>(out[k], epi, scale), pol_stream);
-                        else dst[f] = out[k];
-                    }
-                }
-            }
-            c = (int)resolve_column<HOT>(g, (unsigned)c_ahead);
-            v = v_ahead;
-        }
-        group = __shfl_sync(0xffffffffu, next_group, 0);
-    }
-}
-
-// ---------------------------------------------------------------------------
 // 3. split rows: add the partial slots of a row in slot order.
 //    WIDE = false: one warp per split row (eight rows per block), its lane groups take interleaved slots; rows
 //    with more than max_slots slots are left to the wide launch.
@@ -652,7 +518,6 @@ struct SpmmArgs {
     cudaEvent_t fork = nullptr, join = nullptr;
     int row_class = -1;   // >= 0: only the rows of that class of a plan with row classes
     int resident_per_sm = 0;   // 0: as many blocks of the chunk kernel as fit; > 0: at most this many per SM
-    bool window_chunks = true; // scalar operands: long rows through the aligned-window kernel where the width allows
 };
 
 // The part of a class-major list with class starts `start` that the call computes.
@@ -670,39 +535,6 @@ static int resident_grid(Kernel kernel, int cap_per_sm) {
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess) return 0;
     if (cap_per_sm > 0 && per_sm > cap_per_sm) per_sm = cap_per_sm;
     return per_sm * sms;
-}
-
-// Launch of the window kernel over chunks [chunk_lo, chunk_lo + n_chunks) for a feature width F (floats).
-template <int G, bool UNIT, bool HOT>
-static int launch_window_chunks_g(const SpmmArgs &a, int chunk_lo, int n_chunks) {
-    const Side &s = *a.side;
-    auto kernel = spmm_chunks_window_kernel<G, 4, UNIT, HOT>;
-    static int resident_all = 0;
-    if (resident_all == 0) resident_all = resident_grid(kernel, 0);
-    int resident = resident_all;
-    if (a.resident_per_sm > 0) resident = std::min(resident, a.resident_per_sm * 148);
-    int grid = ceil_div(n_chunks, 8);
-    if (resident > 0 && grid > resident) grid = resident;
-    const long long per_warp = n_chunks / ((long long)grid * 8);
-    const int group_size = per_warp >= 32 ? kChunkGroup : per_warp >= 8 ? 2 : 1;
-    DRONE_CUDA(cudaMemsetAsync(a.counter, 0, sizeof(unsigned), a.st));
-    kernel<<<grid, 256, 0, a.st>>>(s.chunks + chunk_lo, n_chunks, s.col, s.val, a.gather, a.Y, a.ldy, a.partials, a.nvec,
-                                   a.epi, a.counter, group_size);
-    DRONE_LAUNCH_CHECK("spmm_chunks_window_kernel");
-    return DRONE_OK;
-}
-
-// Widths the window kernel takes: 5 .. 125 floats (2 .. 32 lanes of one float4 per row).
-static inline bool window_kernel_fits(int F) { return F >= 5 && F <= 125; }
-
-template <bool UNIT, bool HOT>
-static int launch_window_chunks(const SpmmArgs &a, int chunk_lo, int n_chunks) {
-    const int lanes = (a.nvec + 3 + 3) / 4;     // float4 per window: a row of F floats starting up to 3 floats in
-    if (lanes <= 2) return launch_window_chunks_g<2, UNIT, HOT>(a, chunk_lo, n_chunks);
-    if (lanes <= 4) return launch_window_chunks_g<4, UNIT, HOT>(a, chunk_lo, n_chunks);
-    if (lanes <= 8) return launch_window_chunks_g<8, UNIT, HOT>(a, chunk_lo, n_chunks);
-    if (lanes <= 16) return launch_window_chunks_g<16, UNIT, HOT>(a, chunk_lo, n_chunks);
-    return launch_window_chunks_g<32, UNIT, HOT>(a, chunk_lo, n_chunks);
 }
 
 template <int G, int VPL, int VEC, int U, bool EXACT, bool UNIT, bool HOT>
@@ -735,10 +567,7 @@ static int launch_all(const SpmmArgs &a) {
         DRONE_LAUNCH_CHECK("spmm_short_stream_kernel");
         if (overlap) DRONE_CUDA(cudaEventRecord(a.join, a.side_stream));
     }
-    if (n_chunks > 0 && VEC == 1 && a.window_chunks && window_kernel_fits(a.nvec)) {
-        const int rc = launch_window_chunks<UNIT, HOT>(a, chunk_lo, n_chunks);
-        if (rc) return rc;
-    } else if (n_chunks > 0) {
+    if (n_chunks > 0) {
         auto kernel = spmm_chunks_kernel<G, VPL, VEC, 2 * U, EXACT, UNIT, HOT>;
         static int resident_all = 0;
         if (resident_all == 0) resident_all = resident_grid(kernel, 0);

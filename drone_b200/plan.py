@@ -103,11 +103,13 @@ class AggregationPlan:
                 out.append(_view_device_memory(ptr.value, n, dt, self.device).clone())
         return tuple(out)
 
-    def reserve(self, max_features, host_operands=False):
+    def reserve(self, max_features, host_operands=False, padded_rows=False):
         """Allocate now what calls with F <= max_features would allocate on first use (partial sums of split rows;
-        with host_operands the device staging of spmm_host)."""
+        with host_operands the device staging of spmm_host; with padded_rows the staging that lets widths which are
+        not multiples of 4 run on the float4 kernels)."""
         with torch.cuda.device(self.device):
-            check(_lib.lib().drone_plan_reserve(self._h, int(max_features), 1 if host_operands else 0))
+            check(_lib.lib().drone_plan_reserve(self._h, int(max_features),
+                                                (1 if host_operands else 0) | (2 if padded_rows else 0)))
 
     def set_row_classes(self, row_class, n_classes, stream=None):
         """Give every row a class in 0..n_classes-1 (int32 CUDA tensor [n_rows]); spmm(..., row_class=c) then

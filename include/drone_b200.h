@@ -177,13 +177,23 @@ int drone_spmm_rows(drone_plan *plan, int orientation, int row_class, int F,
 
 /*
  * Allocates, ahead of time, everything later calls of this plan would otherwise allocate on first use: the
- * partial-sum buffer of split rows for feature widths up to max_features and, with host_operands != 0, the device
- * staging of drone_spmm_host for [n_rows, max_features] operands.  After it, drone_spmm / drone_spmm_rows /
- * drone_spmm_host with F <= max_features reach neither cudaMalloc nor a device-wide synchronisation.
+ * partial-sum buffer of split rows for feature widths up to max_features and, as `what` asks,
+ *   DRONE_RESERVE_HOST_OPERANDS  the device staging of drone_spmm_host for [n_rows, max_features] operands;
+ *   DRONE_RESERVE_PADDED_ROWS    two [n_rows, max_features rounded up to 4] buffers for operands whose rows cannot
+ *                                be read 16 bytes at a time where they lie (a width that is not a multiple of 4 such
+ *                                as the class widths 41 and 47, odd leading dimensions, unaligned addresses).  With
+ *                                them, such calls copy X into rows padded to a multiple of 4 floats, run the float4
+ *                                kernels and copy the result out (two extra passes over [n_rows, F], small beside the
+ *                                gathers); without them the scalar kernels run.  The two routes add in different
+ *                                (each fixed) orders, so they agree to rounding, not bit for bit.
+ * After it, drone_spmm / drone_spmm_rows / drone_spmm_host with F <= max_features reach neither cudaMalloc nor a
+ * device-wide synchronisation.
  * Stands where the reference sizes its cuSPARSE workspace on the first training step,
  * cuda_gcn/src/cuda/cuda_module.cu:234-244 (cusparseSpMM_bufferSize, cudaFree + cudaMalloc of sparseBuffer).
  */
-int drone_plan_reserve(drone_plan *plan, int max_features, int host_operands);
+#define DRONE_RESERVE_HOST_OPERANDS 1
+#define DRONE_RESERVE_PADDED_ROWS   2
+int drone_plan_reserve(drone_plan *plan, int max_features, int what);
 
 /*
  * Same operation with HOST operands: copies X to the device, aggregates, and

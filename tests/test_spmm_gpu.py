@@ -240,10 +240,10 @@ def test_table_of_hot_rows(cuda_device, oracle, f):
 
 @pytest.mark.parametrize("f,lead,shift", [(41, 41, 0), (47, 47, 0), (33, 36, 0), (32, 40, 1), (64, 72, 3), (125, 125, 0), (9, 11, 2)])
 def test_rows_that_do_not_start_on_16_bytes(cuda_device, oracle, f, lead, shift):
-    """Operands whose rows start 0..3 floats past a 16-byte boundary (odd widths, odd leading dimensions, a view that
-    starts inside a row): the long rows go through the aligned-window kernel.  Against the double oracle, bit for
-    bit against the scalar kernel's plan being repeatable, and rows that are never gathered must not leak into the
-    result even when they hold NaN (the windows of their neighbours overlap them)."""
+    """Operands whose rows cannot be read 16 bytes at a time (odd widths, odd leading dimensions, a view that starts
+    inside a row), without and with the padded staging of drone_plan_reserve: both against the double oracle, each
+    repeatable bit for bit, nothing written outside the result's rows, and a row that is never gathered may hold NaN
+    without leaking into the result."""
     n, u, v = gg.rmat_graph(11, 16, seed=42, symmetrise=False, self_loops="drop")
     u, v = u.numpy(), v.numpy()
     keep = u != 7                                        # vertex 7 has no out-edge: X[7] is never gathered by A^T x
@@ -258,8 +258,11 @@ def test_rows_that_do_not_start_on_16_bytes(cuda_device, oracle, f, lead, shift)
     xz = xh.copy()
     xz[7] = 0.0
     want, mag = oracle.spmm_csr_f64(*t, xz, with_abs=True)
-    for env in ({}, {"DRONE_SHORT_ROW_LIMIT": 4, "DRONE_CHUNK_NNZ": 16}, {"DRONE_WINDOW_CHUNKS": 0}):
-        plan = make_plan(cuda_device, index, dst, in_deg, out_deg, **env)
+    results = []
+    for padded in (False, True):
+        plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+        if padded:
+            plan.reserve(f, padded_rows=True)
         ybig = torch.full((n + 1, lead + shift), 3.0, device=cuda_device)
         y = ybig[:n, shift:shift + f]
         plan.spmm(db.OP_AT, x, out=y)
@@ -272,6 +275,27 @@ def test_rows_that_do_not_start_on_16_bytes(cuda_device, oracle, f, lead, shift)
         y2 = torch.empty_like(ybig)[:n, shift:shift + f]
         plan.spmm(db.OP_AT, x, out=y2)
         assert torch.equal(y2, y)
+        assert torch.equal(plan.spmm(db.OP_AT, x, relu=True), torch.clamp_min(y, 0.0))
+        results.append(got)
+    assert np.abs(results[0] - results[1]).max() <= REL_TOL * np.abs(want).max()
+
+
+def test_padded_rows_with_row_classes(cuda_device, oracle):
+    """The padded route computes one row class at a time like the plain one: other rows of Y stay as they are."""
+    n, u, v = gg.rmat_graph(11, 16, seed=43, symmetrise=False, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    plan.reserve(41, padded_rows=True)
+    x = torch.as_tensor(gg.seeded_normal(44, (n, 41)), device=cuda_device)
+    whole = plan.spmm(db.OP_AT, x)
+    cls = torch.as_tensor((np.arange(n) % 3).astype(np.int32), device=cuda_device)
+    plan.set_row_classes(cls, 3)
+    y = torch.full((n, 41), 9.0, device=cuda_device)
+    plan.spmm(db.OP_AT, x, out=y, row_class=1)
+    assert torch.equal(y[cls == 1], whole[cls == 1]) and (y[cls != 1] == 9.0).all()
+    for c in (0, 2):
+        plan.spmm(db.OP_AT, x, out=y, row_class=c)
+    assert torch.equal(y, whole)
 
 
 def test_golden_vectors(cuda_device, oracle):
