@@ -582,35 +582,7 @@ def large_graph_timing(device, workload, steps=10):
     return out
 
 
-def glorot_weights(dims, device, seed=7):
-    """(U - 0.5) * 2 * sqrt(6 / (in + out)) per layer (cuda_gcn/src/cuda/cuda_kernel.cu:469-474), same on every rank."""
-    gen = torch.Generator(device="cpu")
-    gen.manual_seed(seed)
-    return [((torch.rand((a, b), generator=gen) - 0.5) * 2 * (6.0 / (a + b)) ** 0.5).to(device)
-            for a, b in zip(dims[:-1], dims[1:])]
-
-
-def hashed_normal(global_ids, f, seed, device):
-    """N(0,1) features that depend only on (seed, global vertex id, column): every rank that holds a vertex makes the
-    same row.  Counter hash (splitmix64 on int64, wrapping) + Box-Muller, on the device."""
-    ids = torch.as_tensor(np.asarray(global_ids).astype(np.int64), device=device)
-    ctr = (ids[:, None] * f + torch.arange(f, device=device, dtype=torch.int64)[None, :]) * 2 + seed * 0x5851F42D
-
-    def mix(x):
-        x = x + (-7046029254386353131)              # 0x9E3779B97F4A7C15 as a signed 64-bit value
-        x = (x ^ ((x >> 30) & 0x3FFFFFFFF)) * (-4658895280553007687)
-        x = (x ^ ((x >> 27) & 0x1FFFFFFFFF)) * (-7723592293110705685)
-        return x ^ ((x >> 31) & 0x1FFFFFFFF)
-    u1 = ((mix(ctr) >> 11) & 0x1FFFFFFFFFFFFF).double() / 9007199254740992.0
-    u2 = ((mix(ctr + 1) >> 11) & 0x1FFFFFFFFFFFFF).double() / 9007199254740992.0
-    z = torch.sqrt(-2.0 * torch.log(u1.clamp_(min=1e-300))) * torch.cos(2.0 * np.pi * u2)
-    return z.float()
-
-
-def hashed_labels(global_ids, classes, seed, device):
-    ids = torch.as_tensor(np.asarray(global_ids).astype(np.int64), device=device)
-    h = (ids * 2654435761 + seed * 40503) & 0x7FFFFFFF
-    return (h % classes).to(torch.int32)
+from drone_b200.graphgen import glorot_weights, hashed_labels, hashed_normal  # noqa: E402
 
 
 def time_epochs(step, epochs, sync):
@@ -710,7 +682,29 @@ def gcn_epoch_timing(device, cfg_name, with_cusparse, epochs=5):
             out["ms_cusparse_aggregation"] = None
             out["cusparse_error"] = repr(e)
     g.plan.close()
+    del step, x, truth, weights, g
+    torch.cuda.empty_cache()
+    if with_cusparse and len(dims) == 3:
+        out["reference_epoch"] = reference_gcn_epoch(cfg, epochs)
+        ref = out["reference_epoch"]
+        if "first_epoch_loss" in ref:
+            ref["loss_rel_diff_vs_drone_b200"] = abs(ref["first_epoch_loss"] - loss_ours) / max(abs(loss_ours), 1e-30)
     return out
+
+
+def reference_gcn_epoch(cfg, epochs, timeout_s=600):
+    """The reference's own training epoch on the same graph, features, labels and starting weights, in a child process
+    (baseline/ref_gcn_epoch.py; needs oracle/_ref/libref_graphsum.so)."""
+    import subprocess
+    try:
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "ref_gcn_epoch.py"), "--vertices",
+                            str(cfg["vertices"]), "--pairs", str(cfg["pairs"]), "--seed", str(cfg["seed"]), "--dims",
+                            ",".join(str(d) for d in cfg["dims"]), "--epochs", str(epochs)],
+                           capture_output=True, text=True, timeout=timeout_s)
+        lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+        return json.loads(lines[-1]) if lines else {"error": "exit %d: %s" % (r.returncode, r.stderr[-300:])}
+    except Exception as e:
+        return {"error": repr(e)}
 
 
 def distribute_graph(n, make_edges, world, rank, device, keep_self_loops=True):

@@ -126,3 +126,34 @@ def seeded_normal(seed, shape):
     u2 = (h2 >> np.uint64(11)).astype(np.float64) / 9007199254740992.0           # [0, 1)
     z = np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)
     return z.astype(np.float32).reshape(shape)
+
+
+def glorot_weights(dims, device, seed=7):
+    """(U - 0.5) * 2 * sqrt(6 / (in + out)) per layer (cuda_gcn/src/cuda/cuda_kernel.cu:469-474), same on every rank."""
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(seed)
+    return [((torch.rand((a, b), generator=gen) - 0.5) * 2 * (6.0 / (a + b)) ** 0.5).to(device)
+            for a, b in zip(dims[:-1], dims[1:])]
+
+
+def hashed_normal(global_ids, f, seed, device):
+    """N(0,1) features that depend only on (seed, global vertex id, column): every rank that holds a vertex makes the
+    same row.  Counter hash (splitmix64 on int64, wrapping) + Box-Muller, on the device."""
+    ids = torch.as_tensor(np.asarray(global_ids).astype(np.int64), device=device)
+    ctr = (ids[:, None] * f + torch.arange(f, device=device, dtype=torch.int64)[None, :]) * 2 + seed * 0x5851F42D
+
+    def mix(x):
+        x = x + (-7046029254386353131)              # 0x9E3779B97F4A7C15 as a signed 64-bit value
+        x = (x ^ ((x >> 30) & 0x3FFFFFFFF)) * (-4658895280553007687)
+        x = (x ^ ((x >> 27) & 0x1FFFFFFFFF)) * (-7723592293110705685)
+        return x ^ ((x >> 31) & 0x1FFFFFFFF)
+    u1 = ((mix(ctr) >> 11) & 0x1FFFFFFFFFFFFF).double() / 9007199254740992.0
+    u2 = ((mix(ctr + 1) >> 11) & 0x1FFFFFFFFFFFFF).double() / 9007199254740992.0
+    z = torch.sqrt(-2.0 * torch.log(u1.clamp_(min=1e-300))) * torch.cos(2.0 * np.pi * u2)
+    return z.float()
+
+
+def hashed_labels(global_ids, classes, seed, device):
+    ids = torch.as_tensor(np.asarray(global_ids).astype(np.int64), device=device)
+    h = (ids * 2654435761 + seed * 40503) & 0x7FFFFFFF
+    return (h % classes).to(torch.int32)

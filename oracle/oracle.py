@@ -42,6 +42,25 @@ def build_ref(force=False):
     return _REF_SO
 
 
+def reference_gcn_epochs(global_v, u, v, global_in_degree, global_out_degree, dims, features, labels, w1, w2,
+                         warmup=2, epochs=5):
+    """Run the REFERENCE's own training epoch (CUDAGCN::train_epoch, cuda_gcn/src/cuda/cuda_gcn.cu:287-306) on one
+    worker on cuda:0, over the given graph / features / labels (by global id) and starting weights.  Returns
+    (ms per epoch, ms per epoch of its bookkeeping steps timed on their own, cross-entropy loss of the first epoch)."""
+    ref = C.CDLL(_REF_SO)
+    u, v = _i32(u), _i32(v)
+    ind, outd = _i32(global_in_degree), _i32(global_out_degree)
+    features, w1, w2, labels = _f32(features), _f32(w1), _f32(w2), _i32(labels)
+    ms, book, loss = C.c_double(0), C.c_double(0), C.c_float(0)
+    rc = ref.ref_gcn_epochs(int(global_v), len(u), _p(u, C.c_int), _p(v, C.c_int), _p(ind, C.c_int), _p(outd, C.c_int),
+                            int(dims[0]), int(dims[1]), int(dims[2]), _p(features, C.c_float), _p(labels, C.c_int),
+                            _p(w1, C.c_float), _p(w2, C.c_float), int(warmup), int(epochs), C.byref(ms), C.byref(book),
+                            C.byref(loss))
+    if rc != 0:
+        raise RuntimeError("reference GCN epoch run failed (%d)" % rc)
+    return ms.value, book.value, loss.value
+
+
 def reference_available():
     return os.path.exists(_REF_SO)
 

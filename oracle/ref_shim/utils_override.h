@@ -10,7 +10,17 @@
 #include <cstdlib>
 #include <stdlib.h>
 struct DroneRefExit { int code; };
-inline void drone_ref_exit(int code) { throw DroneRefExit{code}; }
+/* The driver of a whole training epoch sets drone_ref_tolerate_exit: the launch error of a zero-row kernel is then
+ * cleared where the reference checks it and the epoch carries on (the driver checks the device at the end). */
+extern int drone_ref_tolerate_exit;
+extern "C" int cudaGetLastError_for_ref_shim(void);
+inline void drone_ref_exit(int code) {
+    if (drone_ref_tolerate_exit) {
+        cudaGetLastError_for_ref_shim();
+        return;
+    }
+    throw DroneRefExit{code};
+}
 #define exit(code) drone_ref_exit(code)
 typedef enum { FULL_BATCH, SEMI_BATCH } BatchType;
 const BatchType batch_type = FULL_BATCH;
