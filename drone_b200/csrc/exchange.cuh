@@ -49,6 +49,11 @@ struct drone_p2p {
     unsigned *d_done = nullptr;         // [2] blocks of push_up / add_push_down that have finished (last one publishes the flags)
 };
 
+namespace drone {
+// One direction of the peer-memory exchange for 8- or 16-byte elements per boundary vertex (exchange_p2p.cu).
+int p2p_move_elements(drone_xplan *x, const void *d_send, size_t bytes, bool up, cudaStream_t st, const void **recv_out);
+}  // namespace drone
+
 #define DRONE_NCCL(call)                                                                 \
     do {                                                                                 \
         ncclResult_t r__ = (call);                                                       \

@@ -99,7 +99,7 @@ template <> struct PVec<1> { using type = float; };
 __device__ __forceinline__ void vadd(float4 &a, const float4 &b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
 __device__ __forceinline__ void vadd(float &a, const float &b) { a += b; }
 
-// One mirror row of the walk: {local row, owner, row in the owner's up-receive area}.
+// One mirror row of the walk: {local row, owner, row in the owner's up-receive area, position in this rank's up list}.
 // rows[rec.x, :] -> peer_up_recv[rec.y][rec.z, :]      (nvec = F / VEC vectors per row)
 // The records lie in walk order: the mirror rows are grouped by owner, and walking them as they lie would make every
 // rank store to the same owner at the same time, whose NVLink ingress then limits all of them.
@@ -163,6 +163,23 @@ __global__ void p2p_scatter_kernel(float *__restrict__ rows, long long ld, const
         const int r = (int)(i / nvec), j = (int)(i - (long long)r * nvec);
         *(reinterpret_cast<V *>(rows + (long long)up_rows[r] * ld) + j) = __ldcv(recv + i);
     }
+}
+
+// The same transport for one small element per boundary vertex instead of a row of features (the PageRank job's
+// {value, flag} pairs): send[i] of this rank's up (or down) list goes to its fixed place in the peer's receive area.
+// table[k] = {.., peer, place at the peer, position i in this rank's list}; T is 8 or 16 bytes.
+template <typename T, bool UP>
+__global__ void p2p_move_elements_kernel(const T *__restrict__ send, const int4 *__restrict__ table, int n,
+                                         float *const *__restrict__ peer_recv, const int *error, unsigned *done,
+                                         unsigned *const *__restrict__ peer_flag, const int *__restrict__ send_to,
+                                         int nranks, unsigned epoch) {
+    if (*(volatile const int *)error != 0) return;
+    for (long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x; k < n; k += (long long)gridDim.x * blockDim.x) {
+        const int4 rec = __ldg(table + k);
+        const int src = UP ? rec.w : rec.x;
+        reinterpret_cast<T *>(peer_recv[rec.y])[rec.z] = send[src];
+    }
+    publish_when_all_blocks_done(done, peer_flag, send_to, nranks, epoch);
 }
 
 static inline int p2p_grid(long long n) {
@@ -271,7 +288,7 @@ static int p2p_connect(drone_xplan *x, drone_p2p *p, const std::vector<char> &al
             for (int d = 1; d <= P; ++d) {
                 const int q = (me + d) % P;
                 const int end = std::min(next[q] + kRun, x->up_off[q + 1]);
-                for (int i = next[q]; i < end; ++i) walk.push_back(make_int4(x->up_rows[i], up_peer[i], up_dest[i], 0));
+                for (int i = next[q]; i < end; ++i) walk.push_back(make_int4(x->up_rows[i], up_peer[i], up_dest[i], i));
                 next[q] = end;
             }
     }
@@ -475,6 +492,57 @@ int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t 
     }
     timer.mark();
     timer.report(x->rank, n_up, n_m, F);
+    return DRONE_OK;
+}
+
+// One direction of the exchange for elements of `bytes` (8 or 16) per boundary vertex: stores this rank's send list
+// into the peers' receive areas, publishes the epoch, waits for the peers' epochs.  *recv_out is where the elements
+// sent to this rank lie afterwards (indexed like the receive buffer of the send/recv transport).  up = true starts a
+// new epoch; the down move that follows belongs to the same one.
+int p2p_move_elements(drone_xplan *x, const void *d_send, size_t bytes, bool up, cudaStream_t st, const void **recv_out) {
+    drone_p2p *p = x->p2p;
+    if (!p) return set_error(DRONE_E_STATE, "peer-memory transport is not enabled on this exchange plan");
+    if (bytes != 8 && bytes != 16)
+        return set_error(DRONE_E_INVALID, "peer-memory element move: %zu bytes per element (8 or 16)", bytes);
+    if ((size_t)x->max_features * 4 < bytes)
+        return set_error(DRONE_E_TOO_LARGE, "peer-memory element move: the plan's receive areas hold %d floats per vertex, "
+                         "%zu bytes are needed", x->max_features, bytes);
+    if (*(volatile int *)p->h_error != 0)
+        return set_error(DRONE_E_STATE,
+                         "peer-memory exchange: an earlier call gave up waiting for rank %d (%s flag); the ranks are out of step",
+                         *p->h_error % 100, *p->h_error >= 200 ? "down" : "up");
+    const int P = x->nranks;
+    const int n_up = (int)x->up_rows.size(), n_down = (int)x->down_rows.size();
+    if (up) ++p->epoch;
+    const unsigned epoch = p->epoch;
+    unsigned *my_flags = reinterpret_cast<unsigned *>(p->segment);
+    char *my_up_recv = p->segment + kFlagBytes;
+    char *my_down_recv = p->segment + kFlagBytes + align_up(x->down_rows.size() * (size_t)x->max_features * 4, 256);
+    if (up) {
+        if (n_up) {
+            const int grid = p2p_grid(n_up);
+            if (bytes == 8) p2p_move_elements_kernel<float2, true><<<grid, 256, 0, st>>>((const float2 *)d_send, p->d_walk, n_up, p->d_peer_up_recv, p->d_error, p->d_done, p->d_peer_flag_up, p->d_need_down, P, epoch);
+            else p2p_move_elements_kernel<double2, true><<<grid, 256, 0, st>>>((const double2 *)d_send, p->d_walk, n_up, p->d_peer_up_recv, p->d_error, p->d_done, p->d_peer_flag_up, p->d_need_down, P, epoch);
+            DRONE_LAUNCH_CHECK("p2p_move_elements_kernel");
+        }
+        if (n_down) {
+            p2p_wait_kernel<<<1, 64, 0, st>>>(my_flags, p->d_need_up, P, epoch, p->d_error, p->d_host_error, 100);
+            DRONE_LAUNCH_CHECK("p2p_wait_kernel");
+        }
+        *recv_out = my_up_recv;
+    } else {
+        if (n_down) {
+            const int grid = p2p_grid(n_down);
+            if (bytes == 8) p2p_move_elements_kernel<float2, false><<<grid, 256, 0, st>>>((const float2 *)d_send, p->d_pairs, n_down, p->d_peer_down_recv, p->d_error, p->d_done + 1, p->d_peer_flag_down, p->d_need_up, P, epoch);
+            else p2p_move_elements_kernel<double2, false><<<grid, 256, 0, st>>>((const double2 *)d_send, p->d_pairs, n_down, p->d_peer_down_recv, p->d_error, p->d_done + 1, p->d_peer_flag_down, p->d_need_up, P, epoch);
+            DRONE_LAUNCH_CHECK("p2p_move_elements_kernel");
+        }
+        if (n_up) {
+            p2p_wait_kernel<<<1, 64, 0, st>>>(my_flags + P, p->d_need_down, P, epoch, p->d_error, p->d_host_error, 200);
+            DRONE_LAUNCH_CHECK("p2p_wait_kernel");
+        }
+        *recv_out = my_down_recv;
+    }
     return DRONE_OK;
 }
 

@@ -435,6 +435,8 @@ static inline int grid1d(long long n, int cap = 148 * 16) {
 // Moves the packed boundary entries: up == true sends my `up` slices and receives `down` slices.
 struct Transport {
     virtual int move(std::vector<drone_pr *> &parts, bool up, size_t pair_bytes, bool dbl, cudaStream_t st) = 0;
+    // where the entries sent to part p lie after move(): its receive buffer unless the transport delivers elsewhere
+    virtual const void *received(drone_pr *p) { return p->recv; }
     virtual int allreduce(std::vector<drone_pr *> &parts, int slot, bool dbl, cudaStream_t st) = 0;
     virtual ~Transport() {}
 };
@@ -465,6 +467,24 @@ struct NcclTransport : Transport {
         return DRONE_OK;
     }
 };
+
+// One process per GPU on one NVLink domain: entries are stored straight into the receiver's memory
+// (the exchange plan's peer-memory transport, exchange_p2p.cu); the scalar sums stay on NCCL.
+struct PeerTransport : NcclTransport {
+    const void *landed = nullptr;
+    int move(std::vector<drone_pr *> &parts, bool up, size_t pair_bytes, bool, cudaStream_t st) override {
+        drone_pr *p = parts[0];
+        if (p->xplan->nranks == 1) return DRONE_OK;
+        return p2p_move_elements(p->xplan, p->send, pair_bytes, up, st, &landed);
+    }
+    const void *received(drone_pr *p) override { return p->xplan->nranks == 1 ? p->recv : landed; }
+};
+
+// The transport of a job that runs as one process per GPU: peer memory when the exchange plan has it enabled and its
+// receive areas are wide enough for a {value, flag} pair, grouped send/recv otherwise.
+static bool use_peer_transport(const drone_pr *p) {
+    return p->xplan->p2p != nullptr && (size_t)p->xplan->max_features * 4 >= (p->dbl ? 16u : 8u);
+}
 
 template <typename R>
 __global__ void pr_sum_scalars_kernel(R **scalars, int n_parts, int slot) {
@@ -556,7 +576,7 @@ static int exchange(std::vector<drone_pr *> &parts, Transport &tr, cudaStream_t 
         const int n_m = (int)x->m_rows.size(), n_down = (int)x->down_rows.size();
         if (n_m) {
             pr_apply_up_kernel<R><<<grid1d(n_m), 256, 0, st>>>(x->d_m_rows, x->d_m_off, x->d_m_pos, n_m,
-                                                              (const Pair<R> *)p->recv, (R *)p->diff, p->ubm, p->counters);
+                                                              (const Pair<R> *)tr.received(p), (R *)p->diff, p->ubm, p->counters);
             DRONE_LAUNCH_CHECK("pr_apply_up_kernel");
         }
         if (n_down) {
@@ -570,7 +590,7 @@ static int exchange(std::vector<drone_pr *> &parts, Transport &tr, cudaStream_t 
         const drone_xplan *x = p->xplan;
         const int n_up = (int)x->up_rows.size();
         if (n_up) {
-            pr_apply_down_kernel<R><<<grid1d(n_up), 256, 0, st>>>(x->d_up_rows, n_up, (const Pair<R> *)p->recv, (R *)p->diff,
+            pr_apply_down_kernel<R><<<grid1d(n_up), 256, 0, st>>>(x->d_up_rows, n_up, (const Pair<R> *)tr.received(p), (R *)p->diff,
                                                                  p->ubm, p->counters);
             DRONE_LAUNCH_CHECK("pr_apply_down_kernel");
         }
@@ -797,6 +817,10 @@ int drone_pr_peval(drone_pr *p, drone_pr_response *res, void *stream) {
     DRONE_REQUIRE(p && res, "drone_pr_peval: NULL argument");
     DRONE_REQUIRE(p->xplan->nranks == 1 || p->comm, "drone_pr_peval: %d ranks but no communicator", p->xplan->nranks);
     std::vector<drone_pr *> parts{p};
+    if (use_peer_transport(p)) {
+        PeerTransport tr;
+        return run_delta(parts, true, tr, res, stream);
+    }
     NcclTransport tr;
     return run_delta(parts, true, tr, res, stream);
 }
@@ -804,6 +828,10 @@ int drone_pr_peval(drone_pr *p, drone_pr_response *res, void *stream) {
 int drone_pr_inceval(drone_pr *p, drone_pr_response *res, void *stream) {
     DRONE_REQUIRE(p && res, "drone_pr_inceval: NULL argument");
     std::vector<drone_pr *> parts{p};
+    if (use_peer_transport(p)) {
+        PeerTransport tr;
+        return run_delta(parts, false, tr, res, stream);
+    }
     NcclTransport tr;
     return run_delta(parts, false, tr, res, stream);
 }
@@ -838,6 +866,10 @@ int drone_pr_power_iterate(drone_pr *p, int iterations, double damping, void *st
     DRONE_REQUIRE(p->xplan->nranks == 1 || p->comm, "drone_pr_power_iterate: %d ranks but no communicator",
                   p->xplan->nranks);
     std::vector<drone_pr *> parts{p};
+    if (use_peer_transport(p)) {
+        PeerTransport tr;
+        return run_power(parts, iterations, damping, tr, stream);
+    }
     NcclTransport tr;
     return run_power(parts, iterations, damping, tr, stream);
 }

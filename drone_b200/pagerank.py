@@ -32,6 +32,14 @@ class PageRank:
     def handle(self):
         return self._h
 
+    def transport_name(self):
+        """How boundary entries travel between ranks: stored into the peer's memory when the graph's exchange plan has
+        that transport enabled and holds at least a {value, flag} pair per vertex, grouped send/recv otherwise."""
+        need = 4 if self.use_double else 2
+        if getattr(self.graph.xplan, "p2p_enabled", False) and self.graph.xplan.max_features >= need:
+            return "peer memory (stores into the receiver's buffer + epoch flags) + scalar all-reduce"
+        return "grouped ncclSend/ncclRecv of all boundary vertices + scalar all-reduce"
+
     def peval(self, stream=None):
         res = PRResponse()
         check(_lib.lib().drone_pr_peval(self._h, C.byref(res), _stream_ptr(stream)))

@@ -340,6 +340,8 @@ class ExchangePlan:
             workers = _i32(workers[np.repeat(row_mask, per_row)])
             mwi = _i32(np.concatenate([[0], np.cumsum(np.where(row_mask, per_row, 0))]))
         self._keep = (g, m2w, mwi, workers)
+        self.max_features = int(max_features)
+        self.p2p_enabled = False
         self._h = C.c_void_p(0)
         check(_lib.lib().drone_xplan_create(C.byref(self._h), g.rank, g.n_parts, g.n_local, _vp(g.l2g),
                                             _vp(m2w), _vp(mwi), _vp(workers), int(max_features)))
@@ -365,6 +367,7 @@ class ExchangePlan:
     def enable_p2p(self, comm, stream_ptr=None):
         """Switch later exchanges on this plan to the peer-memory transport (collective over `comm`)."""
         check(_lib.lib().drone_xplan_enable_p2p(self._h, comm.handle, C.c_void_p(stream_ptr or 0)))
+        self.p2p_enabled = comm.nranks > 1
 
     def close(self):
         if self._h.value:

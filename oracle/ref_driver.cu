@@ -159,8 +159,8 @@ extern "C" int ref_gcn_epochs(int global_v, int n_edges, int *u, int *v, const i
                 *ms_per_epoch = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() / epochs;
                 break;
             }
-            const std::pair<float, float> r = gcn->train_epoch();
-            if (e == 0) *first_loss = r.first - gcn->get_l2_penalty();     // train_epoch adds the penalty to the loss
+            gcn->train_epoch();
+            if (e == 0) *first_loss = gcn->loss;     // the cross-entropy loss alone (train_epoch returns it plus the L2 penalty)
         }
         cudaDeviceSynchronize();
         const auto t0 = std::chrono::steady_clock::now();

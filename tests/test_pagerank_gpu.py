@@ -144,8 +144,28 @@ def _nccl_rank(rank, world, port, ok):
         wantp = oracle.pagerank_power_f64(index.numpy(), dst.numpy(), 20, 0.85)
         vals = pr_.values()
         assert np.max(np.abs(vals[keep] - wantp[gid]) / wantp[gid]) < PR_TOL
+        # the same job with the boundary entries stored straight into the peer's memory: same supersteps, same values
+        g2 = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, dev, max_features=4)
+        g2.xplan.enable_p2p(comm)
+        pr2 = prk.PageRank(g2, n, comm=comm, use_double=True, eps=1e-6, n_isolated=int((part.replicas == 0).sum()))
+        assert pr2.transport_name().startswith("peer memory")
+        res = pr2.peval()
+        steps2 = 1
+        while True:
+            flag = torch.tensor([0 if res.is_empty() else 1])
+            dist.all_reduce(flag)
+            if int(flag) == 0:
+                break
+            res = pr2.inceval()
+            steps2 += 1
+        assert steps2 == want_steps
+        vals2 = pr2.values()
+        assert np.max(np.abs(vals2[keep] - want[gid]) / want[gid]) < PR_TOL
+        pr2.power_iterate(20, 0.85)
+        assert np.array_equal(pr2.values(), vals)
         ok[rank] = 1
         dist.barrier()
+        pr2.close()
         pr_.close()
         comm.close()
     finally:

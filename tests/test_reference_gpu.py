@@ -14,6 +14,35 @@ from helpers import REL_TOL
 pytestmark = pytest.mark.gpu
 
 
+def test_reference_training_epoch_loss_vs_oracle_and_library(cuda_device, oracle):
+    """The reference's own CUDAGCN::train_epoch (cuSPARSE aggregation, cuBLAS layers, its cross-entropy) on one
+    worker: the loss of the first epoch equals the double oracle's and this library's GCN step on the same graph,
+    features, labels and starting weights to 1e-5.  Pins oracle/gcn_oracle.py against the reference itself."""
+    if not oracle.reference_available():
+        pytest.skip("oracle/_ref/libref_graphsum.so was not built (reference tree absent at build time)")
+    from drone_b200 import gcn, graphsum as gs, partition as pt
+    from helpers import graph_case
+    from oracle import gcn_oracle
+    dims = (40, 32, 7)
+    n, u, v = gg.rmat_graph(10, 12, seed=91, symmetrise=True, self_loops="add")
+    u, v = u.numpy(), v.numpy()
+    x = gg.seeded_normal(3, (n, dims[0]))
+    truth = np.random.default_rng(4).integers(0, dims[2], n).astype(np.int32)      # the reference trains on every row
+    w1, w2 = [w.numpy() for w in gg.glorot_weights(dims, "cpu", seed=5)]
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u, v)
+    want = gcn_oracle.gcn_step(index, dst, val, x, w1, w2, truth)
+    ms, book, ref_loss = oracle.reference_gcn_epochs(n, u, v, in_deg, out_deg, dims, x, truth, w1, w2, warmup=1, epochs=1)
+    assert ms > 0 and book > 0
+    assert abs(ref_loss - want["loss"]) <= 1e-5 * max(1.0, abs(want["loss"]))
+    part = pt.ebv_partition(n, u, v, 1)
+    lg = part.local_graph(0)
+    g = gs.DeviceGraph(lg, in_deg, out_deg, cuda_device, max_features=32)
+    t = lambda a: torch.as_tensor(a, device=cuda_device)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    step = gcn.GCNStep(g, t(x[lg.l2g]), t(truth[lg.l2g]), t(w1), t(w2))
+    assert abs(float(step.forward()) - ref_loss) <= 1e-5 * max(1.0, abs(ref_loss))
+
+
 @pytest.mark.parametrize("scale,sym,dim", [(10, True, 64), (11, False, 41), (9, False, 128)])
 def test_reference_graphsum_vs_oracle_and_library(cuda_device, oracle, scale, sym, dim):
     if not oracle.reference_available():
