@@ -41,6 +41,8 @@ WORKLOADS = {
     "rmat26": dict(scale=26, edge_factor=16, features=32, symmetrise=False, seed=20261130),
     "rmat24": dict(scale=24, edge_factor=16, features=32, symmetrise=False, seed=20261132),
     "rmat22": dict(scale=22, edge_factor=16, features=32, symmetrise=False, seed=20261131),
+    # the aggregation alone on the graph of the GCN configuration c3 (Reddit-shaped), at its hidden width
+    "c3": dict(kind="powerlaw", vertices=232965, pairs=57_200_000, features=128, seed=20261203),
 }
 
 # the GCN configurations: vertices, undirected pairs drawn, layer widths (input, hidden..., classes)
@@ -168,7 +170,7 @@ def workload_config(args):
             cfg["features"] = args.features
     # weak scaling: the graph doubles with the GPU count, so every EBV part keeps the single-GPU edge count
     n = max(args.gpus, 1)
-    if args.scaling == "weak":
+    if args.scaling == "weak" and "scale" in cfg:
         cfg["scale"] += max(n.bit_length() - 1, 0)
     return cfg
 
@@ -176,6 +178,11 @@ def workload_config(args):
 def build_graph(cfg, device):
     """CSR by source, global degrees (int32 tensors on `device`)."""
     from drone_b200 import graphgen as gg
+    if cfg.get("kind") == "powerlaw":
+        n, u, v = gg.powerlaw_graph(cfg["vertices"], cfg["pairs"], seed=cfg["seed"], device=device)
+        index, dst = gg.csr_by_source(u, v, n)
+        in_deg, out_deg = gg.degrees(u, v, n)
+        return n, index, dst, in_deg, out_deg
     n, u, v = gg.rmat_graph(cfg["scale"], cfg["edge_factor"], seed=cfg["seed"], device=device,
                             symmetrise=cfg["symmetrise"], self_loops="add")
     index, dst = gg.csr_by_source(u, v, n)
@@ -320,9 +327,13 @@ def run_reference(args, cfg):
 
 
 def workload_descr(args, cfg, n, nnz):
-    return {"workload": "%s: R-MAT scale %d ef %d%s +I, Y = A_hat * H, F=%d" % (
-        args.workload, cfg["scale"], cfg["edge_factor"], " symmetrised" if cfg["symmetrise"] else " directed",
-        cfg["features"]), "vertices": n, "nnz": nnz, "features": cfg["features"],
+    if cfg.get("kind") == "powerlaw":
+        what = "%s: power-law graph, %d vertices, symmetrised +I, Y = A_hat * H, F=%d" % (args.workload, n, cfg["features"])
+    else:
+        what = "%s: R-MAT scale %d ef %d%s +I, Y = A_hat * H, F=%d" % (
+            args.workload, cfg["scale"], cfg["edge_factor"], " symmetrised" if cfg["symmetrise"] else " directed",
+            cfg["features"])
+    return {"workload": what, "vertices": n, "nnz": nnz, "features": cfg["features"],
         "l2_policy": "operands rotate over 3 buffer sets; CSR + H + Y exceed the 126 MB L2"}
 
 
