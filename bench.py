@@ -472,7 +472,11 @@ def run_ours(args, cfg):
         line["e2e"] = {"value": nnz * f / e2e_s, "unit": "nnz*F/s", "h2d_bytes_per_step": 4 * n * f,
                        "d2h_bytes_per_step": 4 * n * f, "ms_per_step": 1e3 * e2e_s, "steps": args.e2e_steps,
                        "checksum": float(yh[:1024].double().sum()),
-                       "equals_device_call": bool(torch.equal(yh[:4096], plan.spmm(db.OP_AT, xs[0])[:4096].cpu()))}
+                       "max_rel_diff_vs_device_call": float((yh[:65536] - plan.spmm(db.OP_AT, xs[0])[:65536].cpu()).abs().max()
+                                                            / yh[:65536].abs().max()),
+                       "how": "drone_spmm_host on pinned operands: two column halves, the second half's copy in and the "
+                              "first half's result rows (stored by the kernels straight into the pinned output) cross PCIe "
+                              "in opposite directions"}
         del xh, yh
 
     parity = {}

@@ -27,6 +27,25 @@ inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 // bad row pointer or column, DRONE_OK for a well-formed input.  Synchronises `st`.
 int validate_csr(const char *who, const int *d_index, const int *d_col, int n_rows, int n_cols, int nnz, cudaStream_t st);
 
+#ifdef __CUDACC__
+// (row, column) of a flat element index over rows of `width` elements that advances by a fixed stride: two divisions
+// when a thread starts, none per element (a 64-bit division costs more instructions than the copy it indexes).
+struct RowColumn {
+    int row, col, d_row, d_col, width;
+    __device__ RowColumn(long long first, long long stride, int w) : width(w) {
+        row = (int)(first / w);
+        col = (int)(first - (long long)row * w);
+        d_row = (int)(stride / w);
+        d_col = (int)(stride - (long long)d_row * w);
+    }
+    __device__ void advance() {
+        row += d_row;
+        col += d_col;
+        if (col >= width) { col -= width; ++row; }
+    }
+};
+#endif
+
 }  // namespace drone
 
 // Evaluate a CUDA runtime call; on failure record the message and return DRONE_E_CUDA

@@ -111,9 +111,10 @@ __global__ void p2p_push_up_kernel(const float *__restrict__ rows, long long ld,
     using V = typename PVec<VEC>::type;
     if (*(volatile const int *)error != 0) return;      // an earlier wait of this rank gave up: stay silent
     const long long total = (long long)n_up * nvec;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int k = (int)(i / nvec), j = (int)(i - (long long)k * nvec);
+    const long long first = blockIdx.x * (long long)blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+    RowColumn at(first, stride, nvec);
+    for (long long i = first; i < total; i += stride, at.advance()) {
+        const int k = at.row, j = at.col;
         const int4 rec = __ldg(walk + k);
         V *dst = reinterpret_cast<V *>(peer_up_recv[rec.y]) + (long long)rec.z * nvec + j;
         *dst = *(reinterpret_cast<const V *>(rows + (long long)rec.x * ld) + j);
@@ -134,9 +135,10 @@ __global__ void p2p_add_push_down_kernel(float *__restrict__ rows, long long ld,
     if (*(volatile const int *)error != 0) return;      // the wait in front of this launch gave up
     const V *recv = reinterpret_cast<const V *>(up_recv);
     const long long total = (long long)n_masters * nvec;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int m = (int)(i / nvec), j = (int)(i - (long long)m * nvec);
+    const long long first = blockIdx.x * (long long)blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+    RowColumn at(first, stride, nvec);
+    for (long long i = first; i < total; i += stride, at.advance()) {
+        const int m = at.row, j = at.col;
         V *mine = reinterpret_cast<V *>(rows + (long long)m_rows[m] * ld) + j;
         V acc = *mine;
         const int k0 = m_off[m], k1 = m_off[m + 1];
@@ -158,9 +160,10 @@ __global__ void p2p_scatter_kernel(float *__restrict__ rows, long long ld, const
     if (*(volatile const int *)error != 0) return;
     const V *recv = reinterpret_cast<const V *>(down_recv);
     const long long total = (long long)n_up * nvec;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int r = (int)(i / nvec), j = (int)(i - (long long)r * nvec);
+    const long long first = blockIdx.x * (long long)blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+    RowColumn at(first, stride, nvec);
+    for (long long i = first; i < total; i += stride, at.advance()) {
+        const int r = at.row, j = at.col;
         *(reinterpret_cast<V *>(rows + (long long)up_rows[r] * ld) + j) = __ldcv(recv + i);
     }
 }

@@ -135,6 +135,21 @@ __global__ void fill_chunks_kernel(const int *__restrict__ rowptr, int n_rows, i
     }
 }
 
+// key[i] = first column of chunk i (tags removed), idx[i] = i
+__global__ void chunk_first_column_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__restrict__ col,
+                                          int *__restrict__ key, int *__restrict__ idx) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_chunks; i += (long long)gridDim.x * blockDim.x) {
+        key[i] = (int)((unsigned)col[chunks[i].k0] & kHotMask);
+        idx[i] = (int)i;
+    }
+}
+
+__global__ void permute_chunks_kernel(const Chunk *__restrict__ in, const int *__restrict__ order, int n_chunks,
+                                      Chunk *__restrict__ out) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_chunks; i += (long long)gridDim.x * blockDim.x)
+        out[i] = in[order[i]];
+}
+
 // Per row: 1 if short, and its number of stream entries (a row without nonzeros gets one placeholder).
 __global__ void count_short_kernel(const int *__restrict__ rowptr, int n_rows, int short_limit,
                                    int *__restrict__ is_short, int *__restrict__ n_entries) {
@@ -493,6 +508,35 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
             }
         }
         DRONE_CUDA(cudaStreamSynchronize(st));
+        // DRONE_CHUNK_ORDER=col: the chunk list ordered by each chunk's first column instead of by row (an experiment:
+        // chunks that start in the same column range are then worked on at about the same time).  Every chunk writes
+        // its own row or its own partial slot, so the order changes no result.  Plans without row classes only.
+        const char *order = getenv("DRONE_CHUNK_ORDER");
+        if (order && order[0] == 'c' && K == 1 && s.n_chunks > 1) {
+            struct Sort {
+                int *key = nullptr, *idx = nullptr, *key2 = nullptr, *idx2 = nullptr;
+                Chunk *sorted = nullptr;
+                void *tmp = nullptr;
+                ~Sort() { cudaFree(key); cudaFree(idx); cudaFree(key2); cudaFree(idx2); cudaFree(tmp); cudaFree(sorted); }
+            } o;
+            const size_t nb = sizeof(int) * (size_t)s.n_chunks;
+            DRONE_CUDA(cudaMalloc(&o.key, nb));
+            DRONE_CUDA(cudaMalloc(&o.idx, nb));
+            DRONE_CUDA(cudaMalloc(&o.key2, nb));
+            DRONE_CUDA(cudaMalloc(&o.idx2, nb));
+            DRONE_CUDA(cudaMalloc(&o.sorted, sizeof(Chunk) * (size_t)s.n_chunks));
+            chunk_first_column_kernel<<<grid_for(s.n_chunks), 256, 0, st>>>(s.chunks, s.n_chunks, s.col, o.key, o.idx);
+            DRONE_LAUNCH_CHECK("chunk_first_column_kernel");
+            size_t sort_bytes = 0;
+            DRONE_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, o.key, o.key2, o.idx, o.idx2, s.n_chunks, 0, 30, st));
+            DRONE_CUDA(cudaMalloc(&o.tmp, sort_bytes > 0 ? sort_bytes : 1));
+            DRONE_CUDA(cub::DeviceRadixSort::SortPairs(o.tmp, sort_bytes, o.key, o.key2, o.idx, o.idx2, s.n_chunks, 0, 30, st));
+            count_launch();
+            permute_chunks_kernel<<<grid_for(s.n_chunks), 256, 0, st>>>(s.chunks, o.idx2, s.n_chunks, o.sorted);
+            DRONE_LAUNCH_CHECK("permute_chunks_kernel");
+            DRONE_CUDA(cudaMemcpyAsync(s.chunks, o.sorted, sizeof(Chunk) * (size_t)s.n_chunks, cudaMemcpyDeviceToDevice, st));
+            DRONE_CUDA(cudaStreamSynchronize(st));
+        }
     }
     // stream of the short rows
     count_short_kernel<<<grid_for(n + 1), 256, 0, st>>>(s.rowptr, n, p->short_row_limit, cnt[0], cnt[1]);
@@ -770,6 +814,9 @@ int drone_plan_destroy(drone_plan *p) {
     cudaFree(p->stage_x);
     cudaFree(p->stage_y);
     if (p->own_stream) cudaStreamDestroy(p->own_stream);
+    if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
+    for (cudaEvent_t e : p->half_loaded)
+        if (e) cudaEventDestroy(e);
     if (p->side_stream) cudaStreamDestroy(p->side_stream);
     if (p->fork_event) cudaEventDestroy(p->fork_event);
     if (p->join_event) cudaEventDestroy(p->join_event);

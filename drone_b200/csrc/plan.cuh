@@ -116,6 +116,9 @@ struct drone_plan {
     int pad_width = 0;
     int chunk_blocks_per_sm = 0;   // cap on resident blocks of the chunk kernel per SM (0: as many as fit)
     cudaStream_t own_stream = nullptr;
+    // drone_spmm_host with pinned operands: second stream and one event per column half for the copy that runs ahead
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t half_loaded[2] = {nullptr, nullptr};
     // second stream and fork/join events: the short-row kernel runs beside the chunk kernels of the same call
     cudaStream_t side_stream = nullptr;
     cudaEvent_t fork_event = nullptr, join_event = nullptr;

@@ -276,6 +276,52 @@ static int ensure_staging(drone_plan *p, size_t bytes) {
     return DRONE_OK;
 }
 
+// Pinned host operands of at least 64 columns (a multiple of 8): the call can run as two column halves, the
+// second half's host-to-device copy and the first half's result going over PCIe at the same time, in opposite
+// directions.  DRONE_HOST_PIPELINE=0 keeps the copy - compute - copy sequence.
+static bool host_call_can_be_pipelined(const drone_plan *p, int F, const float *h_X, const float *h_Y) {
+    static const bool enabled = [] {
+        const char *v = getenv("DRONE_HOST_PIPELINE");
+        return !(v && v[0] == '0');
+    }();
+    if (!enabled || F < 64 || F % 8 != 0 || p->pad_x != nullptr) return false;
+    for (const void *ptr : {(const void *)h_X, (const void *)h_Y}) {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        if (attr.type != cudaMemoryTypeHost) return false;
+    }
+    return (reinterpret_cast<uintptr_t>(h_X) & 15) == 0 && (reinterpret_cast<uintptr_t>(h_Y) & 15) == 0;
+}
+
+// The two halves: half h of X is copied (strided, the DMA engine reads 4·F/2 bytes of every host row) into the
+// plan's staging on the copy stream; the aggregation of that half starts when it has landed and stores its result
+// rows straight into the caller's pinned Y (the kernels' stores go out over PCIe as they are issued), while the copy
+// engine is already bringing the other half of X in.
+static int spmm_host_pipelined(drone_plan *p, int orientation, int F, const float *h_X, float *h_Y) {
+    if (!p->copy_stream) DRONE_CUDA(cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
+    for (cudaEvent_t &e : p->half_loaded)
+        if (!e) DRONE_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    float *d_Y = nullptr;
+    DRONE_CUDA(cudaHostGetDevicePointer((void **)&d_Y, h_Y, 0));
+    const int w = F / 2;
+    const size_t pitch = sizeof(float) * (size_t)F;
+    for (int h = 0; h < 2; ++h) {
+        DRONE_CUDA(cudaMemcpy2DAsync(p->stage_x + h * w, pitch, h_X + h * w, pitch, sizeof(float) * (size_t)w, (size_t)p->n_rows,
+                                     cudaMemcpyHostToDevice, p->copy_stream));
+        DRONE_CUDA(cudaEventRecord(p->half_loaded[h], p->copy_stream));
+    }
+    for (int h = 0; h < 2; ++h) {
+        DRONE_CUDA(cudaStreamWaitEvent(p->own_stream, p->half_loaded[h], 0));
+        const int rc = spmm_impl(p, orientation, w, p->stage_x + h * w, F, d_Y + h * w, F, p->own_stream);
+        if (rc) return rc;
+    }
+    DRONE_CUDA(cudaStreamSynchronize(p->own_stream));
+    return DRONE_OK;
+}
+
 int drone_plan_reserve(drone_plan *p, int max_features, int what) {
     DRONE_REQUIRE(p != nullptr, "drone_plan_reserve: plan is NULL");
     DRONE_REQUIRE(max_features >= 1 && max_features <= 1024, "drone_plan_reserve: max_features=%d outside 1..1024",
@@ -322,6 +368,7 @@ int drone_spmm_host(drone_plan *p, int orientation, int F, const float *h_X, flo
     const size_t bytes = sizeof(float) * (size_t)p->n_rows * (size_t)F;
     if ((rc = ensure_staging(p, bytes))) return rc;      // no-op after drone_plan_reserve(.., host_operands = 1)
     if (!p->own_stream) DRONE_CUDA(cudaStreamCreateWithFlags(&p->own_stream, cudaStreamNonBlocking));
+    if (host_call_can_be_pipelined(p, F, h_X, h_Y)) return spmm_host_pipelined(p, orientation, F, h_X, h_Y);
     DRONE_CUDA(cudaMemcpyAsync(p->stage_x, h_X, bytes, cudaMemcpyHostToDevice, p->own_stream));
     if ((rc = spmm_impl(p, orientation, F, p->stage_x, F, p->stage_y, F, p->own_stream))) return rc;
     DRONE_CUDA(cudaMemcpyAsync(h_Y, p->stage_y, bytes, cudaMemcpyDeviceToHost, p->own_stream));

@@ -113,6 +113,18 @@ def test_rmat12(cuda_device, oracle, f):
     check_both_orientations(plan, oracle, index, dst, val, x, cuda_device)
 
 
+def test_chunk_list_order_changes_no_bit(cuda_device, oracle):
+    """DRONE_CHUNK_ORDER=col sorts the chunk list by first column: every chunk still writes its own row or slot."""
+    n, u, v = gg.rmat_graph(12, 16, seed=31, symmetrise=True, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    by_row = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    by_col = make_plan(cuda_device, index, dst, in_deg, out_deg, DRONE_CHUNK_ORDER="col")
+    for f in (32, 41):
+        x = torch.as_tensor(gg.seeded_normal(55 + f, (n, f)), device=cuda_device)
+        for op in (db.OP_AT, db.OP_A):
+            assert torch.equal(by_row.spmm(op, x), by_col.spmm(op, x))
+
+
 def test_many_partials_per_row(cuda_device, oracle):
     """One row with thousands of nonzeros and tiny chunks: the wide (eight-warp) reduction runs."""
     n = 3000
@@ -356,8 +368,20 @@ def test_host_operand_entry_point(cuda_device, oracle):
     xh = torch.as_tensor(gg.seeded_normal(3, (n, f))).pin_memory()
     yh = torch.empty((n, f)).pin_memory()
     plan.spmm_host(db.OP_AT, xh, yh)
-    y_dev = plan.spmm(db.OP_AT, xh.to(cuda_device))
-    assert torch.equal(yh, y_dev.cpu())
+    xd = xh.to(cuda_device)
+    y_dev = plan.spmm(db.OP_AT, xd)
+    # pinned operands of 64 columns run as two column halves (copy of the second overlapping the first's result):
+    # each half is the 32-column call on those columns bit for bit, the whole agrees with the 64-column call to rounding
+    for h in range(2):
+        half = plan.spmm(db.OP_AT, xd[:, 32 * h:32 * h + 32].contiguous())
+        assert torch.equal(yh[:, 32 * h:32 * h + 32], half.cpu())
+    assert (yh - y_dev.cpu()).abs().max() <= REL_TOL * y_dev.abs().max().item()
+    w, a = oracle.spmm_csr_f64(*oracle.transpose_csr(n, n, index, dst, val), xh.numpy(), with_abs=True)
+    assert_close_to_oracle(yh.numpy(), w, a)
+    x24 = xh[:, :24].contiguous().pin_memory()           # below 64 columns: copy, aggregate, copy
+    y24 = torch.empty((n, 24)).pin_memory()
+    plan.spmm_host(db.OP_AT, x24, y24)
+    assert torch.equal(y24, plan.spmm(db.OP_AT, x24.to(cuda_device)).cpu())
     xn = xh.numpy().copy()                               # pageable numpy operands work too
     yn = np.empty_like(xn)
     plan.spmm_host(db.OP_A, xn, yn)
