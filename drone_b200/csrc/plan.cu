@@ -508,11 +508,15 @@ static int build_work_lists(drone_plan *p, Side &s, cudaStream_t st) {
             }
         }
         DRONE_CUDA(cudaStreamSynchronize(st));
-        // DRONE_CHUNK_ORDER=col: the chunk list ordered by each chunk's first column instead of by row (an experiment:
-        // chunks that start in the same column range are then worked on at about the same time).  Every chunk writes
-        // its own row or its own partial slot, so the order changes no result.  Plans without row classes only.
+        // The chunk list ordered by each chunk's first column instead of by row: chunks that start in the same column
+        // range are then worked on at about the same time, which keeps more of their gathers in L2 (measured: R-MAT-22
+        // F = 32 1.053 -> 0.986 ms, R-MAT-20 symmetrised F = 64 0.645 -> 0.623 ms).  Every chunk writes its own row or
+        // its own partial slot, so the order changes no result.  Plans without row classes and without a table of hot
+        // rows only: on R-MAT-26 (operand 70 x L2) the row order, which mixes gathers that hit L2 with gathers that go to
+        // HBM at all times, is the faster one (21.1 ms against 25.7 ms).  DRONE_CHUNK_ORDER=row / col forces either.
         const char *order = getenv("DRONE_CHUNK_ORDER");
-        if (order && order[0] == 'c' && K == 1 && s.n_chunks > 1) {
+        const bool by_column = order && order[0] == 'c' ? true : order && order[0] == 'r' ? false : s.hot_ids == nullptr;
+        if (by_column && K == 1 && s.n_chunks > 1) {
             struct Sort {
                 int *key = nullptr, *idx = nullptr, *key2 = nullptr, *idx2 = nullptr;
                 Chunk *sorted = nullptr;

@@ -114,11 +114,11 @@ def test_rmat12(cuda_device, oracle, f):
 
 
 def test_chunk_list_order_changes_no_bit(cuda_device, oracle):
-    """DRONE_CHUNK_ORDER=col sorts the chunk list by first column: every chunk still writes its own row or slot."""
+    """The chunk list is sorted by first column unless DRONE_CHUNK_ORDER=row: every chunk writes its own row or slot."""
     n, u, v = gg.rmat_graph(12, 16, seed=31, symmetrise=True, self_loops="add")
     index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
-    by_row = make_plan(cuda_device, index, dst, in_deg, out_deg)
-    by_col = make_plan(cuda_device, index, dst, in_deg, out_deg, DRONE_CHUNK_ORDER="col")
+    by_row = make_plan(cuda_device, index, dst, in_deg, out_deg, DRONE_CHUNK_ORDER="row")
+    by_col = make_plan(cuda_device, index, dst, in_deg, out_deg)
     for f in (32, 41):
         x = torch.as_tensor(gg.seeded_normal(55 + f, (n, f)), device=cuda_device)
         for op in (db.OP_AT, db.OP_A):
