@@ -268,8 +268,9 @@ spmm_short_stream_kernel(const int *__restrict__ s_range_row, int n_ranges, cons
 // ---------------------------------------------------------------------------
 // 2. chunks of long rows: one warp per chunk.  The warp loads 32 (col, val)
 //    pairs at a time; its 32/G lane groups take interleaved entries.  Warps take
-//    chunks from `counter` group_size (at most kChunkGroup) at a time (the counter starts at 0; short lists are
-//    handed out one chunk at a time so that the last warps to finish hold little work); the
+//    chunks from `counter` kChunkGroup at a time (the counter starts at 0; the group size is a compile-time
+//    constant on purpose: with a run-time size the compiler produced a tighter loop over the group that ran a
+//    quarter slower on the largest graphs); the
 //    next group's index is requested while the current group is being worked on,
 //    and the first (col, val) batch of the next chunk while the current chunk is.
 // ---------------------------------------------------------------------------
@@ -279,7 +280,7 @@ template <int G, int VPL, int VEC, int U, bool EXACT, bool UNIT, bool HOT>
 __global__ void __launch_bounds__(256)
 spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__restrict__ col,
                    const float *__restrict__ val, Gather g, float *__restrict__ Y, long long ldy,
-                   float *__restrict__ partials, int nvec, Epilogue epi, unsigned *counter, int group_size) {
+                   float *__restrict__ partials, int nvec, Epilogue epi, unsigned *counter) {
     using V = typename Vec<VEC>::type;
     constexpr int RPW = 32 / G;
     constexpr int UU = MinOf<U, G>::value;
@@ -289,15 +290,15 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
     const unsigned long long pol_keep = l2_policy_keep(), pol_stream = l2_policy_stream();
 
     unsigned group = 0;
-    if (lane == 0) group = atomicAdd(counter, (unsigned)group_size);
+    if (lane == 0) group = atomicAdd(counter, (unsigned)kChunkGroup);
     group = __shfl_sync(0xffffffffu, group, 0);
     while (group < (unsigned)n_chunks) {
         int4 desc = make_int4(0, 0, 0, 0);
-        if (lane < group_size && group + lane < (unsigned)n_chunks)
+        if (lane < kChunkGroup && group + lane < (unsigned)n_chunks)
             desc = __ldg(reinterpret_cast<const int4 *>(chunks) + group + lane);
-        const int in_group = min(group_size, n_chunks - (int)group);
+        const int in_group = min(kChunkGroup, n_chunks - (int)group);
         unsigned next_group = 0;
-        if (lane == 0) next_group = atomicAdd(counter, (unsigned)group_size);   // needed only after this group
+        if (lane == 0) next_group = atomicAdd(counter, (unsigned)kChunkGroup);   // needed only after this group
 
         // first batch of the group's first chunk
         int c = 0;
@@ -573,14 +574,11 @@ static int launch_all(const SpmmArgs &a) {
         if (resident_all == 0) resident_all = resident_grid(kernel, 0);
         int resident = resident_all;
         if (a.resident_per_sm > 0) resident = std::min(resident, a.resident_per_sm * 148);
-        int grid = ceil_div(n_chunks, 8);
+        int grid = ceil_div(ceil_div(n_chunks, kChunkGroup), 8);
         if (resident > 0 && grid > resident) grid = resident;
-        // chunks per request of a warp: four when every warp will come back many times, fewer for short lists
-        const long long per_warp = n_chunks / ((long long)grid * 8);
-        const int group_size = per_warp >= 32 ? kChunkGroup : per_warp >= 8 ? 2 : 1;
         DRONE_CUDA(cudaMemsetAsync(a.counter, 0, sizeof(unsigned), a.st));
         kernel<<<grid, 256, 0, a.st>>>(s.chunks + chunk_lo, n_chunks, s.col, s.val, a.gather, a.Y, a.ldy, a.partials,
-                                       a.nvec, a.epi, a.counter, group_size);
+                                       a.nvec, a.epi, a.counter);
         DRONE_LAUNCH_CHECK("spmm_chunks_kernel");
     }
     if (n_split > 0) {
