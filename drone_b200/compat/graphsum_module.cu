@@ -35,6 +35,9 @@ CUDAGraphSum::CUDAGraphSum(CUDAVariable *in, CUDAVariable *out, Graph *graph, Co
     drone_check(drone_plan_create(&plan, n, *graph->edgeSize, graph->index, graph->dst, nullptr, degree->inDegree,
                                   degree->outDegree, DRONE_PLAN_BOTH, comm ? comm->s : nullptr),
                 "drone_plan_create");
+    // was: cusparseSpMM_bufferSize + cudaMalloc of the workspace on the first training step (cuda_module.cu:234-244);
+    // padded staging lets class-width layers (41, 47 columns) run on the 16-byte kernels
+    drone_check(drone_plan_reserve(plan, dim, dim % 4 ? DRONE_RESERVE_PADDED_ROWS : 0), "drone_plan_reserve");
     if (workerNum > 1) {
         const std::vector<int> l2g = to_host(graph->Local2Global, (size_t)n);
         const std::vector<int> mir = to_host(graph->Mirror2Worker, (size_t)n);
