@@ -23,6 +23,7 @@
 #include "exchange.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <new>
 
 namespace drone {
@@ -185,10 +186,16 @@ __global__ void p2p_move_elements_kernel(const T *__restrict__ send, const int4 
     publish_when_all_blocks_done(done, peer_flag, send_to, nranks, epoch);
 }
 
+// Blocks of a row kernel: at most DRONE_P2P_BLOCKS_PER_SM (default 8) per SM of a 148-SM part.
 static inline int p2p_grid(long long n) {
+    static const int per_sm = [] {
+        const char *v = getenv("DRONE_P2P_BLOCKS_PER_SM");
+        const int k = (v && *v) ? atoi(v) : 8;
+        return k >= 1 && k <= 8 ? k : 8;
+    }();
     long long g = (n + 255) / 256;
     if (g < 1) g = 1;
-    if (g > 148 * 8) g = 148 * 8;
+    if (g > 148 * per_sm) g = 148 * per_sm;
     return (int)g;
 }
 
