@@ -284,7 +284,8 @@ static bool host_call_can_be_pipelined(const drone_plan *p, int F, const float *
         const char *v = getenv("DRONE_HOST_PIPELINE");
         return !(v && v[0] == '0');
     }();
-    if (!enabled || F < 64 || F % 8 != 0 || p->pad_x != nullptr) return false;
+    (void)p;
+    if (!enabled || F < 64 || F % 8 != 0) return false;
     for (const void *ptr : {(const void *)h_X, (const void *)h_Y}) {
         cudaPointerAttributes attr;
         if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
@@ -293,7 +294,12 @@ static bool host_call_can_be_pipelined(const drone_plan *p, int F, const float *
         }
         if (attr.type != cudaMemoryTypeHost) return false;
     }
-    return (reinterpret_cast<uintptr_t>(h_X) & 15) == 0 && (reinterpret_cast<uintptr_t>(h_Y) & 15) == 0;
+    void *mapped = nullptr;      // the kernels store into Y through its device alias: it must be mapped memory
+    if (cudaHostGetDevicePointer(&mapped, const_cast<float *>(h_Y), 0) != cudaSuccess || mapped == nullptr) {
+        cudaGetLastError();
+        return false;
+    }
+    return (reinterpret_cast<uintptr_t>(h_X) & 15) == 0 && (reinterpret_cast<uintptr_t>(mapped) & 15) == 0;
 }
 
 // The two halves: half h of X is copied (strided, the DMA engine reads 4·F/2 bytes of every host row) into the

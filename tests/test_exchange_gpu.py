@@ -78,6 +78,24 @@ def test_rows_in_groups_give_the_same_bits(cuda_device, oracle, parts, groups, f
             assert torch.equal(again[p], whole[p])
 
 
+@pytest.mark.parametrize("f,ld", [(64, 64), (41, 41), (32, 40), (1, 1)])
+def test_clear_mirror_rows(cuda_device, f, ld):
+    """drone_clear_mirror_rows zeroes exactly the rows whose Mirror2Worker entry is not -1 (clear_mirror_grad)."""
+    n = 1000
+    rng = np.random.default_rng(f)
+    m2w = np.where(rng.random(n) < 0.3, rng.integers(0, 4, n), -1).astype(np.int32)
+    big = torch.as_tensor(rng.standard_normal((n, ld)).astype(np.float32), device=cuda_device)
+    before = big.clone()
+    gs.clear_mirror_rows(big[:, :f], torch.as_tensor(m2w, device=cuda_device))
+    mirrors = torch.as_tensor(m2w != -1, device=cuda_device)
+    assert (big[mirrors][:, :f] == 0).all()
+    assert torch.equal(big[~mirrors], before[~mirrors])
+    assert torch.equal(big[:, f:], before[:, f:])          # padding columns untouched
+    lib = db.lib()
+    assert lib.drone_clear_mirror_rows(None, 5, 4, 4, None, None) == -1 and b"NULL" in lib.drone_last_error()
+    assert lib.drone_clear_mirror_rows(None, 5, 8, 4, None, None) == -1
+
+
 def test_row_classes_check_arguments(cuda_device):
     n, u, v = gg.rmat_graph(9, 8, seed=5, device=cuda_device, self_loops="add")
     index, dst = gg.csr_by_source(u, v, n)
