@@ -20,6 +20,7 @@
 #include "plan.cuh"
 
 #include <chrono>
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -36,6 +37,10 @@ struct drone_pr {
     drone_comm *comm = nullptr;       // borrowed (may be NULL for a single part)
     int *out_degree = nullptr, *mirror2worker = nullptr;
     void *pr = nullptr, *acc = nullptr, *diff = nullptr, *push = nullptr;   // real[n], real[n], real[n], real2[n]
+    // Large parts: where vertex i publishes its {delta, pushed} pair.  The pairs lie in the order of how often they are
+    // gathered (most gathered first) and the pull lists' columns are renumbered to match, so that the hot pairs are
+    // contiguous and stay in L2 (a pair is 8 bytes of a 32-byte sector).  NULL: pair i lies at i.
+    int *place = nullptr;
     int *active = nullptr, *ubm = nullptr;
     void *scalars = nullptr;          // real[4]: globalDiff, globalAcc, dangling (power mode), spare
     void *block_sums = nullptr;       // real[kReduceBlocks]
@@ -79,7 +84,7 @@ __device__ R block_sum(R v) {
 template <typename R>
 __global__ void pr_init_kernel(R *pr, R *acc, R *diff, Pair<R> *push, int *active, int *ubm,
                                const int *__restrict__ out_degree, const int *__restrict__ mirror2worker, int n,
-                               int global_v, R start, R *block_sums) {
+                               int global_v, R start, R *block_sums, const int *__restrict__ place) {
     R dangling = 0;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         pr[i] = start;
@@ -97,7 +102,7 @@ __global__ void pr_init_kernel(R *pr, R *acc, R *diff, Pair<R> *push, int *activ
             p.val = start / od;
             p.flag = 1;
         }
-        push[i] = p;
+        push[place ? place[i] : i] = p;
     }
     const R tot = block_sum<R>(dangling);
     if (threadIdx.x == 0) block_sums[blockIdx.x] = tot;
@@ -126,7 +131,8 @@ __global__ void pr_roll_scalars_kernel(R *scalars) {
 template <typename R>
 __global__ void pr_increment_kernel(R *pr, R *acc, R *diff, Pair<R> *push, int *active, int *ubm,
                                     const int *__restrict__ out_degree, const int *__restrict__ mirror2worker, int n,
-                                    int global_v, R eps, const R *scalars, R *block_sums) {
+                                    int global_v, R eps, const R *scalars, R *block_sums,
+                                    const int *__restrict__ place) {
     const R alpha = (R)0.85f;                // pr.cu:12 declares a float constant
     const R one_minus_alpha = (R)1 - alpha;
     const R gacc = scalars[1];
@@ -154,7 +160,7 @@ __global__ void pr_increment_kernel(R *pr, R *acc, R *diff, Pair<R> *push, int *
             }
             pr[i] = now;
         }
-        push[i] = p;
+        push[place ? place[i] : i] = p;
     }
     const R tot = block_sum<R>(dangling);
     if (threadIdx.x == 0) block_sums[blockIdx.x] = tot;
@@ -365,7 +371,8 @@ __global__ void pr_count_active_kernel(const int *active, int n, int *counters) 
 // publish pr/outDegree, collect dangling mass (non-mirror copies only) into block sums
 template <typename R>
 __global__ void pr_power_prepare_kernel(const R *pr, Pair<R> *push, const int *__restrict__ out_degree,
-                                        const int *__restrict__ mirror2worker, int n, R *block_sums) {
+                                        const int *__restrict__ mirror2worker, int n, R *block_sums,
+                                        const int *__restrict__ place) {
     R dangling = 0;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         Pair<R> p;
@@ -378,7 +385,7 @@ __global__ void pr_power_prepare_kernel(const R *pr, Pair<R> *push, const int *_
             p.val = pr[i] / od;
             p.flag = 1;
         }
-        push[i] = p;
+        push[place ? place[i] : i] = p;
     }
     const R tot = block_sum<R>(dangling);
     if (threadIdx.x == 0) block_sums[blockIdx.x] = tot;
@@ -396,7 +403,7 @@ __global__ void pr_power_isolated_kernel(R *scalars, long long n_isolated) {
 template <typename R>
 __global__ void pr_power_apply_kernel(R *pr, const R *diff, Pair<R> *push, const int *__restrict__ out_degree,
                                       const int *__restrict__ mirror2worker, int n, int global_v, R damping, R *scalars,
-                                      R *block_sums) {
+                                      R *block_sums, const int *__restrict__ place) {
     const R dang = scalars[2];
     const R base = ((R)1 - damping) / global_v;
     R dangling = 0;
@@ -413,7 +420,7 @@ __global__ void pr_power_apply_kernel(R *pr, const R *diff, Pair<R> *push, const
             p.val = now / od;
             p.flag = 1;
         }
-        push[i] = p;
+        push[place ? place[i] : i] = p;
     }
     const R tot = block_sum<R>(dangling);
     if (threadIdx.x == 0) block_sums[blockIdx.x] = tot;
@@ -613,7 +620,7 @@ static int delta_step(std::vector<drone_pr *> &parts, bool peval, Transport &tr,
             DRONE_CUDA(cudaMemsetAsync(p->scalars, 0, sizeof(R) * 4, st));
             pr_init_kernel<R><<<grid, 256, 0, st>>>((R *)p->pr, (R *)p->acc, (R *)p->diff, (Pair<R> *)p->push, p->active,
                                                     p->ubm, p->out_degree, p->mirror2worker, n, p->global_v, (R)1,
-                                                    (R *)p->block_sums);
+                                                    (R *)p->block_sums, p->place);
             DRONE_LAUNCH_CHECK("pr_init_kernel");
         } else {
             pr_roll_scalars_kernel<R><<<1, 32, 0, st>>>((R *)p->scalars);
@@ -621,7 +628,7 @@ static int delta_step(std::vector<drone_pr *> &parts, bool peval, Transport &tr,
             pr_increment_kernel<R><<<grid, 256, 0, st>>>((R *)p->pr, (R *)p->acc, (R *)p->diff, (Pair<R> *)p->push,
                                                          p->active, p->ubm, p->out_degree, p->mirror2worker, n,
                                                          p->global_v, (R)p->eps, (const R *)p->scalars,
-                                                         (R *)p->block_sums);
+                                                         (R *)p->block_sums, p->place);
             DRONE_LAUNCH_CHECK("pr_increment_kernel");
         }
         pr_fold_block_sums_kernel<R><<<1, 32, 0, st>>>((const R *)p->block_sums, grid, (R *)p->scalars, 0);
@@ -668,7 +675,7 @@ static int power_iterations(std::vector<drone_pr *> &parts, int iterations, doub
         DRONE_CUDA(cudaMemsetAsync(p->scalars, 0, sizeof(R) * 4, st));
         pr_init_kernel<R><<<grid1d(n, kReduceBlocks), 256, 0, st>>>(
             (R *)p->pr, (R *)p->acc, (R *)p->diff, (Pair<R> *)p->push, p->active, p->ubm, p->out_degree,
-            p->mirror2worker, n, p->global_v, (R)1 / (R)p->global_v, (R *)p->block_sums);
+            p->mirror2worker, n, p->global_v, (R)1 / (R)p->global_v, (R *)p->block_sums, p->place);
         DRONE_LAUNCH_CHECK("pr_init_kernel");
         pr_set_scalar_kernel<R><<<1, 32, 0, st>>>((R *)p->scalars, 3, (R)1 / (R)p->global_v);
         DRONE_LAUNCH_CHECK("pr_set_scalar_kernel");
@@ -676,7 +683,8 @@ static int power_iterations(std::vector<drone_pr *> &parts, int iterations, doub
     }
     for (drone_pr *p : parts) {
         pr_power_prepare_kernel<R><<<grid1d(p->n_local, kReduceBlocks), 256, 0, st>>>(
-            (const R *)p->pr, (Pair<R> *)p->push, p->out_degree, p->mirror2worker, p->n_local, (R *)p->block_sums);
+            (const R *)p->pr, (Pair<R> *)p->push, p->out_degree, p->mirror2worker, p->n_local, (R *)p->block_sums,
+            p->place);
         DRONE_LAUNCH_CHECK("pr_power_prepare_kernel");
     }
     for (int it = 0; it < iterations; ++it) {
@@ -697,7 +705,7 @@ static int power_iterations(std::vector<drone_pr *> &parts, int iterations, doub
             // new values, and what they publish for the next iteration, in one pass
             pr_power_apply_kernel<R><<<grid1d(p->n_local, kReduceBlocks), 256, 0, st>>>(
                 (R *)p->pr, (const R *)p->diff, (Pair<R> *)p->push, p->out_degree, p->mirror2worker, p->n_local,
-                p->global_v, (R)damping, (R *)p->scalars, (R *)p->block_sums);
+                p->global_v, (R)damping, (R *)p->scalars, (R *)p->block_sums, p->place);
             DRONE_LAUNCH_CHECK("pr_power_apply_kernel");
         }
     }
@@ -755,6 +763,14 @@ int drone_pr_create(drone_pr **out, int n_local, int global_v, int nnz, const in
         rc = plan_create_untagged(&p->plan, n_local, nnz, d_index, d_dst, ones, nullptr, nullptr, DRONE_PLAN_AT, nullptr);
         cudaFree(ones);
         if (rc) break;
+        {
+            const char *v = getenv("DRONE_PR_ORDER_MIN_ROWS");
+            const long long min_rows = (v && *v) ? atoll(v) : (1LL << 22);
+            if (min_rows > 0 && n_local >= min_rows && nnz > 0) {
+                rc = plan_order_columns_by_frequency(p->plan, DRONE_OP_AT, d_index, &p->place, nullptr);
+                if (rc) break;
+            }
+        }
         cudaError_t e = cudaSuccess;
         auto alloc = [&](void **ptr, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(ptr, bytes > 0 ? bytes : 16); };
         alloc((void **)&p->out_degree, sizeof(int) * n1);
@@ -793,6 +809,7 @@ int drone_pr_destroy(drone_pr *p) {
     cudaGetDevice(&prev);
     cudaSetDevice(p->device);
     drone_plan_destroy(p->plan);
+    cudaFree(p->place);
     cudaFree(p->out_degree); cudaFree(p->mirror2worker); cudaFree(p->pr); cudaFree(p->acc); cudaFree(p->diff);
     cudaFree(p->push); cudaFree(p->active); cudaFree(p->ubm); cudaFree(p->scalars); cudaFree(p->block_sums);
     cudaFree(p->partials); cudaFree(p->send); cudaFree(p->recv); cudaFree(p->counters);

@@ -290,6 +290,15 @@ __global__ void tag_columns_kernel(int *__restrict__ col, long long nnz, const i
     }
 }
 
+// col[k] = place[col[k]]; stream entries keep their flags, placeholders stay as they are
+__global__ void renumber_columns_kernel(int *__restrict__ col, long long n, const int *__restrict__ place, int with_flags) {
+    for (long long k = blockIdx.x * (long long)blockDim.x + threadIdx.x; k < n; k += (long long)gridDim.x * blockDim.x) {
+        const unsigned c = (unsigned)col[k];
+        if (!with_flags) col[k] = __ldg(place + c);
+        else if (!(c & kPlaceholder)) col[k] = (int)((c & ~kColMask) | (unsigned)__ldg(place + (c & kColMask)));
+    }
+}
+
 // plain[k] = the column a possibly tagged entry stands for
 __global__ void untag_columns_kernel(const int *__restrict__ col, long long nnz, const int *__restrict__ hot_ids,
                                      int *__restrict__ plain) {
@@ -736,6 +745,49 @@ static int plan_create_impl(drone_plan *p, int n_rows, int nnz, const int *d_ind
     return DRONE_OK;
 }
 
+}  // namespace drone
+
+namespace drone {
+int plan_order_columns_by_frequency(drone_plan *p, int orientation, const int *d_other_rowptr, int **d_place_out, void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    Side &s = p->side[orientation];
+    if (!s.ready || s.hot_ids) return set_error(DRONE_E_STATE, "plan_order_columns_by_frequency: orientation not prepared, or tagged");
+    const int n = p->n_rows;
+    struct Temp {
+        int *freq = nullptr, *ids = nullptr, *freq_sorted = nullptr, *ids_sorted = nullptr, *place = nullptr;
+        void *sort = nullptr;
+        ~Temp() { cudaFree(freq); cudaFree(ids); cudaFree(freq_sorted); cudaFree(ids_sorted); cudaFree(place); cudaFree(sort); }
+    } t;
+    const size_t bytes = sizeof(int) * (size_t)(n + 1);
+    DRONE_CUDA(cudaMalloc(&t.freq, bytes));
+    DRONE_CUDA(cudaMalloc(&t.ids, bytes));
+    DRONE_CUDA(cudaMalloc(&t.freq_sorted, bytes));
+    DRONE_CUDA(cudaMalloc(&t.ids_sorted, bytes));
+    DRONE_CUDA(cudaMalloc(&t.place, bytes));
+    row_lengths_kernel<<<grid_for(n), 256, 0, st>>>(d_other_rowptr, n, t.freq);
+    DRONE_LAUNCH_CHECK("row_lengths_kernel");
+    iota_kernel<<<grid_for(n), 256, 0, st>>>(t.ids, n);
+    DRONE_LAUNCH_CHECK("iota_kernel");
+    size_t tmp_bytes = 0;
+    DRONE_CUDA(cub::DeviceRadixSort::SortPairsDescending(nullptr, tmp_bytes, t.freq, t.freq_sorted, t.ids, t.ids_sorted, n, 0, 32, st));
+    DRONE_CUDA(cudaMalloc(&t.sort, tmp_bytes > 0 ? tmp_bytes : 1));
+    DRONE_CUDA(cub::DeviceRadixSort::SortPairsDescending(t.sort, tmp_bytes, t.freq, t.freq_sorted, t.ids, t.ids_sorted, n, 0, 32, st));
+    count_launch();
+    scatter_positions_kernel<<<grid_for(n), 256, 0, st>>>(t.ids_sorted, n, t.place);
+    DRONE_LAUNCH_CHECK("scatter_positions_kernel");
+    if (p->nnz > 0) {
+        renumber_columns_kernel<<<grid_for(p->nnz), 256, 0, st>>>(s.col, p->nnz, t.place, 0);
+        DRONE_LAUNCH_CHECK("renumber_columns_kernel");
+    }
+    if (s.n_short_entries > 0) {
+        renumber_columns_kernel<<<grid_for(s.n_short_entries), 256, 0, st>>>(s.s_col, s.n_short_entries, t.place, 1);
+        DRONE_LAUNCH_CHECK("renumber_columns_kernel");
+    }
+    DRONE_CUDA(cudaStreamSynchronize(st));
+    *d_place_out = t.place;
+    t.place = nullptr;
+    return DRONE_OK;
+}
 }  // namespace drone
 
 using namespace drone;

@@ -82,6 +82,11 @@ namespace drone {
 // PageRank pull): never tags columns.
 int plan_create_untagged(drone_plan **out, int n_rows, int nnz, const int *d_index, const int *d_dst, const float *d_values,
                          const int *d_in_degree, const int *d_out_degree, int orientations, void *stream);
+// Renumbers the columns of one orientation of an untagged plan by how often they occur, most frequent first (the
+// frequencies are the row lengths of d_other_rowptr, the row pointer of the opposite orientation): afterwards column c of
+// the plan's lists means position (*d_place_out)[c], a device array of n_rows ints the caller owns.  For users inside
+// the library whose gathered operand is their own array and can be laid out in that order (the PageRank pull).
+int plan_order_columns_by_frequency(drone_plan *p, int orientation, const int *d_other_rowptr, int **d_place_out, void *stream);
 }  // namespace drone
 
 struct drone_plan {

@@ -85,6 +85,30 @@ def test_power_iteration_rmat16_config(cuda_device, oracle, parts):
     assert np.max(np.abs(got32[touched] - want[touched]) / want[touched]) < 1e-4
 
 
+@pytest.mark.parametrize("parts", [1, 3])
+def test_pairs_laid_out_by_gather_frequency(cuda_device, oracle, parts, monkeypatch):
+    """Large parts publish their {delta, pushed} pairs in the order of how often they are gathered and renumber the pull
+    lists' columns to match (forced here on a small graph): only the addresses of the gathers change, so the values
+    and the superstep count are bit for bit those of the plain layout, in both schedules."""
+    n, u, v = gg.rmat_graph(13, 16, seed=36, symmetrise=False, self_loops="drop")
+    u, v = u.numpy(), v.numpy()
+    part = pt.ebv_partition(n, u, v, parts, keep_self_loops=False)
+    results = []
+    for min_rows in ("0", "1"):
+        monkeypatch.setenv("DRONE_PR_ORDER_MIN_ROWS", min_rows)
+        graphs, prs = build_parts(part, n, u, v, cuda_device, False, 1e-6)
+        steps, _ = prk.run_job_local(prs)
+        delta = prk.gather_global(prs, graphs, n)
+        prk.power_iterate_local(prs, 20, 0.85)
+        results.append((steps, delta, prk.gather_global(prs, graphs, n)))
+    assert results[0][0] == results[1][0]
+    assert np.array_equal(results[0][1], results[1][1]) and np.array_equal(results[0][2], results[1][2])
+    index, dst = gg.csr_by_source(torch.as_tensor(u), torch.as_tensor(v), n)
+    want = oracle.pagerank_power_f64(index.numpy(), dst.numpy(), 20, 0.85)
+    touched = part.replicas > 0
+    assert np.max(np.abs(results[1][2][touched] - want[touched]) / want[touched]) < 1e-4
+
+
 def test_against_cpu_job_restatement(cuda_device, oracle):
     """DRONE's CPU job (float, eps 0.01, at most 200 supersteps) and the GPU schedule agree to the
     accuracy the CPU job's threshold allows."""
