@@ -16,9 +16,11 @@
 //     and counters (:334-370);
 //   * a vertex held by several parts gets as master the replica number
 //     (id mod #replicas) in ascending part order (:567-581); the others are mirrors.
-// The only liberty taken: the per-rank sort is stable (the reference uses
-// std::sort, whose order among equal keys is unspecified), so the result is
-// deterministic.
+// The per-rank sort is stable by default (the reference uses std::sort, whose order
+// among equal keys is unspecified), which makes the result independent of the C++
+// library.  With DRONE_EBV_STD_SORT_TIES the shares are sorted by std::sort itself,
+// the call the reference makes (:265): built with the same standard library, the
+// parts then equal the reference's edge for edge.
 #include "common.cuh"
 
 #include <algorithm>
@@ -99,12 +101,21 @@ static void sort_by_key(std::vector<EbvEdge> &edges, int max_key) {
     if (src != edges.data()) edges.swap(other);
 }
 
+// The reference's own call (EBV_mpi.cpp:46-48,265): std::sort over the array with a comparator on the key alone.
+// Equal keys end up in whatever order the library's algorithm leaves them.
+static bool key_less(EbvEdge a, EbvEdge b) { return a.key < b.key; }
+static void sort_by_key_as_reference(std::vector<EbvEdge> &edges) {
+    std::sort(edges.data(), edges.data() + edges.size(), key_less);
+}
+
 // The partitioner proper.  Mask is an unsigned type of at least n_parts bits: held[v] has bit p set when part p holds
 // vertex v, so that scoring an edge costs two random reads whatever the number of parts.
 template <typename Mask>
-static int ebv_run(int n_vertices, long long n_edges, const int *h_u, const int *h_v, int P, int keep_self_loops,
+static int ebv_run(int n_vertices, long long n_edges, const int *h_u, const int *h_v, int P, int flags,
                    int *h_out_u, int *h_out_v, long long *h_part_offset, int *h_owner, int *h_replicas) {
     const int max_batch = 1000;
+    const bool keep_self_loops = (flags & DRONE_EBV_KEEP_SELF_LOOPS) != 0;
+    const bool std_sort_ties = (flags & DRONE_EBV_STD_SORT_TIES) != 0;
     int hw = (int)std::thread::hardware_concurrency();
     if (hw < 1) hw = 1;
     PhasePool pool(std::min(P, hw));
@@ -139,7 +150,8 @@ static int ebv_run(int n_vertices, long long n_edges, const int *h_u, const int 
             e.key = deg[e.u] + deg[e.v];
             max_key = std::max(max_key, e.key);
         }
-        sort_by_key(share[r], max_key);
+        if (std_sort_ties) sort_by_key_as_reference(share[r]);
+        else sort_by_key(share[r], max_key);
     });
     for (int r = 0; r < P; ++r) kept += (long long)share[r].size();
 
@@ -248,22 +260,22 @@ static int ebv_run(int n_vertices, long long n_edges, const int *h_u, const int 
 using namespace drone;
 
 extern "C" int drone_ebv_partition(int n_vertices, long long n_edges, const int *h_u, const int *h_v, int n_parts,
-                                   int keep_self_loops, int *h_out_u, int *h_out_v, long long *h_part_offset,
+                                   int flags, int *h_out_u, int *h_out_v, long long *h_part_offset,
                                    int *h_owner, int *h_replicas) {
     DRONE_REQUIRE(n_vertices > 0 && n_edges >= 0, "drone_ebv_partition: bad sizes (V=%d, E=%lld)", n_vertices, n_edges);
     DRONE_REQUIRE(n_parts >= 1 && n_parts <= 64, "drone_ebv_partition: n_parts=%d outside 1..64", n_parts);
     DRONE_REQUIRE(n_edges == 0 || (h_u && h_v), "drone_ebv_partition: NULL edge list");
     DRONE_REQUIRE(h_out_u && h_out_v && h_part_offset && h_owner && h_replicas, "drone_ebv_partition: NULL output");
     if (n_parts <= 8)
-        return ebv_run<uint8_t>(n_vertices, n_edges, h_u, h_v, n_parts, keep_self_loops, h_out_u, h_out_v, h_part_offset,
+        return ebv_run<uint8_t>(n_vertices, n_edges, h_u, h_v, n_parts, flags, h_out_u, h_out_v, h_part_offset,
                                 h_owner, h_replicas);
     if (n_parts <= 16)
-        return ebv_run<uint16_t>(n_vertices, n_edges, h_u, h_v, n_parts, keep_self_loops, h_out_u, h_out_v, h_part_offset,
+        return ebv_run<uint16_t>(n_vertices, n_edges, h_u, h_v, n_parts, flags, h_out_u, h_out_v, h_part_offset,
                                  h_owner, h_replicas);
     if (n_parts <= 32)
-        return ebv_run<uint32_t>(n_vertices, n_edges, h_u, h_v, n_parts, keep_self_loops, h_out_u, h_out_v, h_part_offset,
+        return ebv_run<uint32_t>(n_vertices, n_edges, h_u, h_v, n_parts, flags, h_out_u, h_out_v, h_part_offset,
                                  h_owner, h_replicas);
-    return ebv_run<uint64_t>(n_vertices, n_edges, h_u, h_v, n_parts, keep_self_loops, h_out_u, h_out_v, h_part_offset,
+    return ebv_run<uint64_t>(n_vertices, n_edges, h_u, h_v, n_parts, flags, h_out_u, h_out_v, h_part_offset,
                              h_owner, h_replicas);
 }
 

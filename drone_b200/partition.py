@@ -83,21 +83,28 @@ class Partition:
         mine = np.nonzero(self.present(p) & (self.replicas > 1) & (self.owner != p))[0].astype(np.int32)
         return mine, self.owner[mine].astype(np.int32)
 
+    def _file_order(self, vertices):
+        """Line order of Master.<p> / Mirror.<p>: the reference walks the vertices in blocks of 1000 * n_parts ids and,
+        inside a block, takes those with id mod n_parts = 0 first, then 1, ... (EBV_mpi.cpp:551-559,598-604)."""
+        v = vertices.astype(np.int64)
+        return np.lexsort((v, v % self.n_parts, v // (1000 * self.n_parts)))
+
     def write_files(self, directory):
-        """G.<p>, Master.<p>, Mirror.<p> in the reference's text formats (EBV_mpi.cpp:342,602-603,631-632)."""
+        """G.<p>, Master.<p>, Mirror.<p> in the reference's text formats and line order (EBV_mpi.cpp:342,551-634)."""
         os.makedirs(directory, exist_ok=True)
         for p in range(self.n_parts):
             np.savetxt(os.path.join(directory, "G.%d" % p), np.stack([self.part_u[p], self.part_v[p]], 1), fmt="%d")
             mv, num, wk = self.master_rows(p)
+            start = np.concatenate([[0], np.cumsum(num)]).tolist()
+            mv, num = mv.tolist(), num.tolist()
             with open(os.path.join(directory, "Master.%d" % p), "w") as f:
-                pos = 0
-                for v, k in zip(mv.tolist(), num.tolist()):
-                    f.write("%d %s \n" % (v, " ".join(str(w) for w in wk[pos:pos + k].tolist())))
-                    pos += k
+                for i in self._file_order(np.asarray(mv, np.int64)).tolist():
+                    f.write("%d %s \n" % (mv[i], " ".join(str(w) for w in wk[start[i]:start[i] + num[i]].tolist())))
             mr, ow = self.mirror_rows(p)
+            mr, ow = mr.tolist(), ow.tolist()
             with open(os.path.join(directory, "Mirror.%d" % p), "w") as f:
-                for v, o in zip(mr.tolist(), ow.tolist()):
-                    f.write("%d %d \n" % (v, o))
+                for i in self._file_order(np.asarray(mr, np.int64)).tolist():
+                    f.write("%d %d \n" % (mr[i], ow[i]))
 
     def local_graph(self, p):
         return LocalGraph(self, p)
@@ -195,8 +202,14 @@ def load_partition(path, part=None):
     return Partition(n, P, pu, pv, owner, replicas, present_bits=bits)
 
 
-def ebv_partition(n_vertices, u, v, n_parts, keep_self_loops=True):
-    """EBV vertex cut (restating EBV_mpi.cpp; see drone_ebv_partition in include/drone_b200.h)."""
+EBV_KEEP_SELF_LOOPS, EBV_STD_SORT_TIES = 1, 2
+
+
+def ebv_partition(n_vertices, u, v, n_parts, keep_self_loops=True, std_sort_ties=False):
+    """EBV vertex cut (restating EBV_mpi.cpp; see drone_ebv_partition in include/drone_b200.h).
+    std_sort_ties: order edges of equal degree sum as std::sort leaves them, which is what the reference's binary
+    does (EBV_mpi.cpp:265); the default stable order does not depend on the C++ library."""
+    flags = (EBV_KEEP_SELF_LOOPS if keep_self_loops else 0) | (EBV_STD_SORT_TIES if std_sort_ties else 0)
     u, v = _i32(u), _i32(v)
     e = len(u)
     out_u = np.empty(max(e, 1), np.int32)
@@ -204,7 +217,7 @@ def ebv_partition(n_vertices, u, v, n_parts, keep_self_loops=True):
     off = np.zeros(n_parts + 1, np.int64)
     owner = np.empty(n_vertices, np.int32)
     replicas = np.empty(n_vertices, np.int32)
-    check(_lib.lib().drone_ebv_partition(n_vertices, e, _vp(u), _vp(v), n_parts, int(bool(keep_self_loops)),
+    check(_lib.lib().drone_ebv_partition(n_vertices, e, _vp(u), _vp(v), n_parts, flags,
                                          _vp(out_u), _vp(out_v), _vp(off), _vp(owner), _vp(replicas)))
     part_u = [out_u[off[p]:off[p + 1]] for p in range(n_parts)]     # views: no second copy of the edge list
     part_v = [out_v[off[p]:off[p + 1]] for p in range(n_parts)]

@@ -481,13 +481,20 @@ int drone_mp_values(drone_mp *job, void *h_out, void *stream);
  * reference writes them to G.<p> (h_out_u/h_out_v hold all kept edges,
  * h_part_offset[n_parts+1] delimits the parts), h_replicas[v] = number of parts
  * holding v, h_owner[v] = part of v's master copy (-1 if v has no edge).
- * keep_self_loops = 1 keeps edges u==u (the variant used for GCN inputs).
+ * flags: DRONE_EBV_KEEP_SELF_LOOPS keeps edges u==u (cuda_gcn/src/tools/EBV_mpi.cpp:217, the variant used for GCN
+ * inputs; EBV_mpi.cpp:219 drops them).  DRONE_EBV_STD_SORT_TIES sorts every rank's share with std::sort, the call
+ * the reference makes (EBV_mpi.cpp:265), instead of the default stable sort: edges with equal degree sums then come
+ * in the order the C++ library's algorithm leaves them, and a build against the same library returns the
+ * reference's parts edge for edge (checked against files the reference's partitioner wrote).  The default order
+ * does not depend on the library.
  * Restates EBV_mpi.cpp:212-374 (deal, local-degree sort, batched scoring) and
  * :549-581 (master = replica number id mod #replicas), as a simulation of its
  * n_parts MPI ranks.
  */
+#define DRONE_EBV_KEEP_SELF_LOOPS 1
+#define DRONE_EBV_STD_SORT_TIES 2
 int drone_ebv_partition(int n_vertices, long long n_edges, const int *h_u, const int *h_v,
-                        int n_parts, int keep_self_loops,
+                        int n_parts, int flags,
                         int *h_out_u, int *h_out_v, long long *h_part_offset,
                         int *h_owner, int *h_replicas);
 

@@ -6,8 +6,14 @@ lock-step batches of 10, 13, ... 1000 edges per rank scored against the state at
 of the batch (:273-331, first-maximum rule :50-61), hand-over in sender order (:334-370),
 master = replica number (id mod #replicas) in ascending part order (:567-581).
 The reference sorts with std::sort (order of equal keys unspecified); this restatement and
-the C++ partitioner both use a stable sort.  "parity unpinned": the reference ships no
-partition fixtures and its binary needs MPI, which is not available here.
+the C++ partitioner's default both use a stable sort.
+
+Pinned against the reference's own partitioner, compiled from EBV_mpi.cpp over stand-ins for
+its MPI and gflags calls (oracle/ref_shim/ebv, `make -C oracle ref_ebv`) and run as P ranks:
+tests/golden/ebv_golden.npz holds the files it wrote.  Where no rank has more than 16 edges
+(std::sort keeps input order there) this restatement reproduces them exactly; on larger
+inputs the C++ partitioner, which this restatement equals in stable order, reproduces them
+byte for byte once it sorts with std::sort too (tests/test_partition.py).
 """
 
 

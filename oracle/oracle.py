@@ -35,7 +35,8 @@ def build_ref(force=False):
     if not os.path.isdir(os.path.join(REFERENCE_ROOT, "cuda_gcn", "src")):
         return _REF_SO if os.path.exists(_REF_SO) else None
     deps = [os.path.join(_HERE, f) for f in ("ref_driver.cu", "Makefile", "ref_shim/mpi.h", "ref_shim/utils_override.h")]
-    if force or not os.path.exists(_REF_SO) or not os.path.exists(os.path.join(_HERE, "_ref", "libref_drone_jobs.so")) \
+    built = [_REF_SO] + [os.path.join(_HERE, "_ref", f) for f in ("libref_drone_jobs.so", "ebv_mpi", "ebv_mpi_keep_loops")]
+    if force or not all(os.path.exists(b) for b in built) \
             or any(os.path.getmtime(d) > os.path.getmtime(_REF_SO) for d in deps):
         subprocess.run(["make", "-C", _HERE, "ref", "REFERENCE=" + REFERENCE_ROOT] + (["-B"] if force else []),
                        check=True, stdout=subprocess.DEVNULL)
@@ -59,6 +60,34 @@ def reference_gcn_epochs(global_v, u, v, global_in_degree, global_out_degree, di
     if rc != 0:
         raise RuntimeError("reference GCN epoch run failed (%d)" % rc)
     return ms.value, book.value, loss.value
+
+
+def reference_ebv_binary(keep_self_loops):
+    """The reference's partitioner compiled by `make ref_ebv` (EBV_mpi.cpp, or the copy under cuda_gcn/src/tools that
+    keeps self-loops), or None when it was not built."""
+    path = os.path.join(_HERE, "_ref", "ebv_mpi_keep_loops" if keep_self_loops else "ebv_mpi")
+    return path if os.path.exists(path) else None
+
+
+def reference_ebv_partition(n_vertices, u, v, n_parts, keep_self_loops, workdir):
+    """Run the REFERENCE's partitioner as n_parts ranks on the edge list (written as its text input into workdir)
+    and return {file name: bytes} of the G.<p> / Master.<p> / Mirror.<p> files it dumps (EBV_mpi.cpp:342,598-634)."""
+    exe = reference_ebv_binary(keep_self_loops)
+    if exe is None:
+        raise RuntimeError("the reference's partitioner was not built (make -C oracle ref_ebv)")
+    os.makedirs(workdir, exist_ok=True)
+    edges = os.path.join(workdir, "edges.txt")
+    np.savetxt(edges, np.stack([_i32(u), _i32(v)], 1), fmt="%d")
+    out = os.path.join(workdir, "parts")
+    env = dict(os.environ, EBV_STANDIN_RANKS=str(n_parts))
+    subprocess.run([exe, "-filename", edges, "-vertices", str(n_vertices), "-edges", str(len(u)), "--is_dump",
+                    "-output", out], check=True, env=env, stdout=subprocess.DEVNULL, timeout=300)
+    files = {}
+    for p in range(n_parts):
+        for kind in ("G", "Master", "Mirror"):
+            with open(os.path.join(out, "%s.%d" % (kind, p)), "rb") as f:
+                files["%s.%d" % (kind, p)] = f.read()
+    return files
 
 
 def reference_available():

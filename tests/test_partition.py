@@ -1,4 +1,6 @@
 """EBV partitioner and routing tables (host code, no GPU)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -138,3 +140,101 @@ def test_rank_with_only_its_own_edges_builds_the_same_tables():
         a, b = alone.local_graph(p), plain.local_graph(p)
         for name in ("l2g", "index", "dst", "master_worker_index", "master2workers", "mirror2worker"):
             assert np.array_equal(getattr(a, name), getattr(b, name)), name
+
+
+# ----- against files written by the reference's own partitioner (tests/golden/make_ebv_golden.py) -----
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ebv_golden.npz")
+GOLDEN_CASES = ["tiny", "uniform_p3", "skewed_p2", "skewed_p4_blocks", "skewed_p8"]
+
+
+def golden_case(name):
+    g = np.load(GOLDEN)
+    n, parts, keep = g[name + "/meta"].tolist()
+    files = {"%s.%d" % (kind, p): g["%s/%s.%d" % (name, kind, p)].tobytes()
+             for p in range(parts) for kind in ("G", "Master", "Mirror")}
+    return n, g[name + "/u"], g[name + "/v"], parts, bool(keep), files
+
+
+def written_files(part, directory):
+    part.write_files(directory)
+    out = {}
+    for p in range(part.n_parts):
+        for kind in ("G", "Master", "Mirror"):
+            with open(os.path.join(directory, "%s.%d" % (kind, p)), "rb") as f:
+                out["%s.%d" % (kind, p)] = f.read()
+    return out
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_files_equal_reference_partitioner(name, tmp_path):
+    """With the reference's tie order (std::sort) the three files of every part equal, byte for byte, what the
+    reference's partitioner wrote for the same edge list."""
+    n, u, v, parts, keep, ref_files = golden_case(name)
+    p = pt.ebv_partition(n, u, v, parts, keep_self_loops=keep, std_sort_ties=True)
+    mine = written_files(p, str(tmp_path))
+    assert sorted(mine) == sorted(ref_files)
+    for fname in sorted(ref_files):
+        assert mine[fname] == ref_files[fname], fname
+
+
+def test_restatement_equals_reference_partitioner_without_ties_in_play(tmp_path):
+    """At most 16 edges per rank: std::sort is an insertion sort there and keeps equal keys in input order, so the
+    stable restatements (Python and the library's default) must reproduce the reference's files as well."""
+    n, u, v, parts, keep, ref_files = golden_case("tiny")
+    ref_parts, ref_owner, ref_rep = ebv_oracle.ebv_partition(n, list(zip(u.tolist(), v.tolist())), parts, keep)
+    for q in range(parts):
+        lines = ref_files["G.%d" % q].decode().split("\n")[:-1]
+        assert ["%d %d" % e for e in ref_parts[q]] == lines
+    p = pt.ebv_partition(n, u, v, parts, keep_self_loops=keep)
+    assert p.owner.tolist() == ref_owner and p.replicas.tolist() == ref_rep
+    assert written_files(p, str(tmp_path)) == ref_files
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES[1:])
+def test_stable_order_cuts_as_well_as_reference(name):
+    """The default (stable) order changes which of several equally ranked edges goes first, not the quality of the cut:
+    replication factor within 3 % of the reference's, edge balance as tight."""
+    n, u, v, parts, keep, ref_files = golden_case(name)
+    ref_replicas = np.zeros(n, np.int64)
+    ref_sizes = []
+    for q in range(parts):
+        e = np.array(ref_files["G.%d" % q].split(), dtype=np.int64).reshape(-1, 2)
+        ref_sizes.append(len(e))
+        ref_replicas[np.unique(e)] += 1
+    p = pt.ebv_partition(n, u, v, parts, keep_self_loops=keep)
+    assert sum(len(x) for x in p.part_u) == sum(ref_sizes)
+    assert abs(p.replication_factor() / (ref_replicas.sum() / n) - 1) < 0.03
+    assert p.edge_imbalance() < max(ref_sizes) * parts / sum(ref_sizes) + 0.05
+
+
+def test_reference_partitioner_live(tmp_path):
+    """The reference's partitioner itself, run here as 3 ranks on a fresh edge list (skipped where it was not built)."""
+    from oracle import oracle
+    if oracle.reference_ebv_binary(True) is None:
+        pytest.skip("reference partitioner not built (make -C oracle ref_ebv)")
+    rng = np.random.default_rng(77)
+    n, m = 4000, 30000
+    u = (n * rng.random(m) ** 2).astype(np.int32)
+    v = (n * rng.random(m) ** 2).astype(np.int32)
+    for keep in (True, False):
+        ref_files = oracle.reference_ebv_partition(n, u, v, 3, keep, str(tmp_path / ("ref%d" % keep)))
+        p = pt.ebv_partition(n, u, v, 3, keep_self_loops=keep, std_sort_ties=True)
+        assert written_files(p, str(tmp_path / ("mine%d" % keep))) == ref_files
+
+
+@pytest.mark.parametrize("name", ["uniform_p3", "skewed_p4_blocks"])
+def test_loader_reads_files_of_reference_partitioner(name, tmp_path):
+    """The text loader on the files the reference's partitioner wrote: same edges, owners and replica counts as the
+    partition computed here, and the same routing tables for every part."""
+    n, u, v, parts, keep, ref_files = golden_case(name)
+    for fname, data in ref_files.items():
+        (tmp_path / fname).write_bytes(data)
+    loaded = pt.read_partition_files(str(tmp_path), n, parts)
+    p = pt.ebv_partition(n, u, v, parts, keep_self_loops=keep, std_sort_ties=True)
+    assert loaded.owner.tolist() == p.owner.tolist() and loaded.replicas.tolist() == p.replicas.tolist()
+    for q in range(parts):
+        assert np.array_equal(loaded.part_u[q], p.part_u[q]) and np.array_equal(loaded.part_v[q], p.part_v[q])
+        for a, b in zip(loaded.master_rows(q), p.master_rows(q)):
+            assert np.array_equal(a, b)
+        for a, b in zip(loaded.mirror_rows(q), p.mirror_rows(q)):
+            assert np.array_equal(a, b)
