@@ -1241,8 +1241,19 @@ def run_partitioned_workload(args, cfg, device, rank, world, comm, sync, headlin
     return line
 
 
+def keep_stdout_for_the_result_line():
+    """Libraries write to file descriptor 1 on their own (NCCL prints its version line there when NCCL_DEBUG asks for
+    it): from here on descriptor 1 is the error stream, and Python's sys.stdout writes to a copy of the original
+    descriptor, so that the JSON line is the only thing on standard output."""
+    sys.stdout.flush()
+    original = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(original, "w", buffering=1)
+
+
 def main():
     args = parse_args()
+    keep_stdout_for_the_result_line()
     if args.record_traffic:
         record_traffic(args.record_traffic, args.workload)
         return
