@@ -124,6 +124,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cusparse", action="store_true")
     ap.add_argument("--no-gcn", action="store_true", help="leave out gcn_epoch, gcn_c4, pagerank, minprop, jobs, rmat26")
+    ap.add_argument("--no-fused-push", action="store_true",
+                    help="peer-memory transport: send mirror rows with the exchange's copy kernel after the aggregation "
+                         "instead of from the aggregation's store")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl", "dense"],
                     help="transport of the mirror/master exchange on several GPUs")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
@@ -932,9 +935,11 @@ def pagerank_timing(device):
 class MultiStep:
     """Local aggregation + mirror/master exchange of one rank, plain or in row groups (PipelinedAggregation)."""
 
-    def __init__(self, graph, comm, f, exchange, dense=None):
+    def __init__(self, graph, comm, f, exchange, dense=None, fused_push=True):
         self.graph, self.comm, self.f, self.exchange_kind, self.dense = graph, comm, f, exchange, dense
         self.piped = {}
+        # peer-memory transport: the aggregation kernels store mirror rows straight into their owners' memory
+        self.fused_push = bool(fused_push) and exchange == "p2p"
 
     def exchange(self, rows):
         from drone_b200 import graphsum as gs
@@ -952,19 +957,23 @@ class MultiStep:
         self.piped = {}
         if groups > 1:
             self.piped[groups] = gs.PipelinedAggregation(self.graph, self.comm, self.f, n_groups=groups,
-                                                         p2p=self.exchange_kind == "p2p")
+                                                         p2p=self.exchange_kind == "p2p", fused_push=self.fused_push)
         else:
             self.graph.plan.set_row_classes(None, 1)
 
     def __call__(self, op, x, y):
         if self.groups > 1:
             self.piped[self.groups](op, x, y)
+        elif self.fused_push:
+            from drone_b200 import graphsum as gs
+            self.graph.plan.spmm(op, x, out=y, push_up_to=self.graph.xplan.handle)
+            gs.exchange_finish(self.graph.xplan, y)
         else:
             self.graph.plan.spmm(op, x, out=y)
             self.exchange(y)
 
 
-def multi_parity(device, rank, world, comm, exchange, groups):
+def multi_parity(device, rank, world, comm, exchange, groups, fused_push=True):
     """Aggregation + exchange over WORLD_SIZE EBV parts of a seeded R-MAT-13 graph (F = 32, both orientations)
     against the double-precision oracle of the whole graph, compared by global vertex id on every rank: the largest
     error relative to the largest element, maximum over ranks."""
@@ -991,7 +1000,7 @@ def multi_parity(device, rank, world, comm, exchange, groups):
     graph = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, device, max_features=f)
     if exchange == "p2p":
         graph.xplan.enable_p2p(comm)
-    step = MultiStep(graph, comm, f, exchange)
+    step = MultiStep(graph, comm, f, exchange, fused_push=fused_push)
     l2g = torch.as_tensor(graph.host.l2g.astype(np.int64), device=device)
     xl = torch.as_tensor(x, device=device)[l2g]
     worst = torch.zeros(1, dtype=torch.float64, device=device)
@@ -1037,11 +1046,13 @@ def run_ours_multi(args, cfg):
 
     line_extra = {}
     if "parity" in chosen:
-        err = multi_parity(device, rank, world, comm, args.exchange, 2)
+        err = multi_parity(device, rank, world, comm, args.exchange, 2, fused_push=not args.no_fused_push)
         line_extra["parity"] = {"max_rel_err": err, "ranks": world, "tolerance": 1e-5, "ok": err <= 1e-5,
-                                "case": "R-MAT-13 +I over %d EBV parts, F=32, aggregation + exchange (%s transport; one "
+                                "case": "R-MAT-13 +I over %d EBV parts, F=32, aggregation + exchange (%s transport%s; one "
                                         "piece and in 2 row groups), both orientations, against the double oracle by "
-                                        "global id" % (world, args.exchange)}
+                                        "global id" % (world, args.exchange,
+                                                       ", mirror rows sent from the aggregation's store"
+                                                       if args.exchange == "p2p" and not args.no_fused_push else "")}
         if not err <= 1e-5:
             if rank == 0:
                 print(json.dumps({"metric": "spmm_nnzF_per_s", "n_gpus": world, "parity": line_extra["parity"],
@@ -1114,7 +1125,7 @@ def run_partitioned_workload(args, cfg, device, rank, world, comm, sync, headlin
     gen.manual_seed(cfg["seed"] + rank)
     xs = [torch.randn((graph.n_local, f), device=device, generator=gen) for _ in range(nbuf)]
     ys = [torch.empty((graph.n_local, f), device=device) for _ in range(nbuf)]
-    mstep = MultiStep(graph, comm, f, args.exchange, dense)
+    mstep = MultiStep(graph, comm, f, args.exchange, dense, fused_push=not args.no_fused_push)
 
     def step(i):
         mstep(db.OP_AT, xs[i % nbuf], ys[i % nbuf])
@@ -1225,6 +1236,9 @@ def run_partitioned_workload(args, cfg, device, rank, world, comm, sync, headlin
                      "collective": {"p2p": "peer-memory stores + epoch flags (push_up, add_push_down, scatter; waits in one-block kernels)",
                                     "nccl": "grouped ncclSend/ncclRecv x2",
                                     "dense": "ncclReduceScatter + ncclAllGather over the boundary"}[args.exchange],
+                     "mirror_rows_sent_from_aggregation_store": bool(mstep.fused_push),
+                     "note": "ms = the whole exchange run alone (copy kernel for the upward half); in the timed step the "
+                             "upward half is part of the aggregation when mirror_rows_sent_from_aggregation_store",
                      "dense_boundary_rows": dense.boundary_rows() if dense is not None else None},
         "gpu_launches": int(g[:, 3].sum()), "clocks": clocks, "setup_s": setup_s, "partition_seconds": part_s,
     }

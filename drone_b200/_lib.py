@@ -37,7 +37,7 @@ class PRResponse(C.Structure):
 class SpmmOpts(C.Structure):
     """drone_spmm_opts of include/drone_b200.h."""
     _fields_ = [("epilogue", C.c_int), ("row_class", C.c_int), ("unit_values", C.c_int), ("reserved_", C.c_int),
-                ("d_row_scale", C.c_void_p)]
+                ("d_row_scale", C.c_void_p), ("push_up_to", C.c_void_p)]
 
 
 EPILOGUE_NONE = 0
@@ -98,6 +98,7 @@ def _declare(lib):
         "drone_xplan_counts": (i, [vp, vp, vp, C.POINTER(i)]),
         "drone_xplan_lists": (i, [vp, vp, vp]),
         "drone_exchange_sum": (i, [vp, vp, vp, i, i, vp]),
+        "drone_exchange_finish": (i, [vp, vp, i, i, vp]),
         "drone_dense_xplan_create": (i, [C.POINTER(vp), i, i, i, vp, i, vp, vp, i]),
         "drone_dense_xplan_destroy": (i, [vp]),
         "drone_dense_xplan_boundary_rows": (ll, [vp]),

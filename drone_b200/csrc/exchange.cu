@@ -314,6 +314,19 @@ int drone_xplan_lists(const drone_xplan *x, int *up_rows, int *down_rows) {
     return DRONE_OK;
 }
 
+int drone_exchange_finish(drone_xplan *x, float *d_rows, int F, int ld, void *stream) {
+    DRONE_REQUIRE(x != nullptr, "drone_exchange_finish: NULL plan");
+    DRONE_REQUIRE(F >= 1 && F <= x->max_features, "drone_exchange_finish: F=%d outside 1..%d (max_features of the plan)", F,
+                  x->max_features);
+    DRONE_REQUIRE(ld >= F, "drone_exchange_finish: ld=%d below F=%d", ld, F);
+    if (x->nranks == 1) return DRONE_OK;
+    DRONE_REQUIRE(d_rows != nullptr || x->n_local == 0, "drone_exchange_finish: rows is NULL");
+    if (!x->p2p || !x->p2p->push_pending)
+        return set_error(DRONE_E_STATE, "drone_exchange_finish: no aggregation call has sent this plan's mirror rows up "
+                         "(drone_spmm_ex with push_up_to on a plan with the peer-memory transport comes first)");
+    return exchange_finish_p2p(x, d_rows, F, ld, (cudaStream_t)stream);
+}
+
 int drone_exchange_sum(drone_xplan *x, drone_comm *c, float *d_rows, int F, int ld, void *stream) {
     DRONE_REQUIRE(x && c, "drone_exchange_sum: NULL plan or communicator");
     DRONE_REQUIRE(c->nranks == x->nranks && c->rank == x->rank, "drone_exchange_sum: plan is for rank %d/%d, comm is %d/%d",

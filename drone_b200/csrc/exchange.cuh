@@ -47,11 +47,23 @@ struct drone_p2p {
     int *d_host_error = nullptr;        // device alias of h_error (written only when a wait runs out)
     int *d_error = nullptr;             // the same word in device memory: what the kernels poll
     unsigned *d_done = nullptr;         // [2] blocks of push_up / add_push_down that have finished (last one publishes the flags)
+    int2 *d_route = nullptr;            // [n_local] {owner, row in the owner's up-receive} for my mirror rows, {-1, 0} for the others
+    bool push_pending = false;          // the upward half of an exchange was done by an aggregation call; the rest is due
 };
 
 namespace drone {
 // One direction of the peer-memory exchange for 8- or 16-byte elements per boundary vertex (exchange_p2p.cu).
 int p2p_move_elements(drone_xplan *x, const void *d_send, size_t bytes, bool up, cudaStream_t st, const void **recv_out);
+
+// The exchange in two halves, for an aggregation that stores its mirror rows straight into their owners' receive
+// areas (exchange_p2p.cu).  p2p_route_begin opens a new epoch and returns the tables the aggregation kernels need;
+// when those kernels are in the stream, p2p_route_publish tells the owners that this rank's rows are there (or
+// p2p_push_up sends them with the copy kernel, for a call whose kernels could not route); exchange_finish_p2p is the
+// rest of the exchange (masters add and send the totals down, mirror rows take them).
+int p2p_route_begin(drone_xplan *x, int n_rows, int F, const int2 **route, float *const **peer_rows);
+int p2p_route_publish(drone_xplan *x, cudaStream_t st);
+int p2p_push_up(drone_xplan *x, const float *d_rows, int F, int ld, cudaStream_t st);
+int exchange_finish_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t st);
 }  // namespace drone
 
 #define DRONE_NCCL(call)                                                                 \

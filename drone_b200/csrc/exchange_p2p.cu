@@ -73,6 +73,15 @@ __global__ void p2p_wait_kernel(const unsigned *flags, const int *need, int nran
     wait_for_peers(flags, need, nranks, epoch, error, host_error, code);
 }
 
+// The flags of a direction as a launch of its own, for rows that earlier kernels of the stream stored into the
+// peers' memory (those kernels have completed, so their stores are performed; the fence orders the flag behind them).
+__global__ void p2p_publish_kernel(unsigned *const *peer_flag, const int *send_to, int nranks, unsigned epoch,
+                                   const int *error) {
+    if (*(volatile const int *)error != 0) return;      // an earlier wait of this rank gave up: stay silent
+    __threadfence_system();
+    if ((int)threadIdx.x < nranks && send_to[threadIdx.x]) st_release_sys(peer_flag[threadIdx.x], epoch);
+}
+
 // End of a kernel that stored rows into peers' memory: every block fences its stores and counts itself; the last
 // one to arrive publishes `epoch` in every peer that expects a flag from this rank (and resets the counter for the
 // next launch).  Saves the one-block signal launch that would otherwise sit between the store kernel and the
@@ -222,7 +231,7 @@ void p2p_free(drone_p2p *p) {
         if (s) cudaIpcCloseMemHandle(s);
     cudaFree(p->segment);
     cudaFree(p->d_peer_up_recv); cudaFree(p->d_peer_down_recv); cudaFree(p->d_peer_flag_up); cudaFree(p->d_peer_flag_down);
-    cudaFree(p->d_walk); cudaFree(p->d_pairs);
+    cudaFree(p->d_walk); cudaFree(p->d_pairs); cudaFree(p->d_route);
     cudaFree(p->d_need_up); cudaFree(p->d_need_down);
     if (p->h_error) cudaFreeHost(p->h_error);
     cudaFree(p->d_error);
@@ -307,7 +316,10 @@ static int p2p_connect(drone_xplan *x, drone_p2p *p, const std::vector<char> &al
         const int pos = x->m_pos[k];
         pairs[k] = make_int4(pos, down_peer[pos], down_dest[pos], 0);
     }
+    std::vector<int2> route((size_t)x->n_local, make_int2(-1, 0));
+    for (size_t i = 0; i < n_up; ++i) route[(size_t)x->up_rows[i]] = make_int2(up_peer[i], up_dest[i]);
     int rc;
+    if ((rc = upload_vec(&p->d_route, route))) return rc;
     if ((rc = upload_vec(&p->d_walk, walk))) return rc;
     if ((rc = upload_vec(&p->d_pairs, pairs))) return rc;
     if ((rc = upload_vec(&p->d_peer_up_recv, up_base))) return rc;
@@ -423,7 +435,7 @@ int drone_xplan_enable_p2p(drone_xplan *x, drone_comm *c, void *stream) {
 
 namespace drone {
 
-// DRONE_P2P_TIMING=1 in the environment makes every exchange measure its five launches with CUDA events, wait for
+// DRONE_P2P_TIMING=1 in the environment makes every exchange measure its two halves with CUDA events, wait for
 // them and print one line per call on standard error (a diagnosis aid: it serialises the host with the device).
 static bool p2p_timing_enabled() {
     static const bool on = [] {
@@ -450,38 +462,81 @@ struct PhaseTimer {
         cudaStreamSynchronize(st);
         float ms[5] = {0, 0, 0, 0, 0};
         for (int i = 0; i + 1 < n; ++i) cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]);
-        fprintf(stderr, "p2p rank %d: push_up %.3f signal %.3f wait+add_push_down %.3f signal %.3f wait+scatter %.3f ms (n_up %d n_m %d F %d)\n",
-                rank, ms[0], ms[1], ms[2], ms[3], ms[4], n_up, n_m, F);
+        fprintf(stderr, "p2p rank %d: push_up %.3f, wait + add_push_down + wait + scatter %.3f ms (n_up %d n_m %d F %d)\n",
+                rank, ms[0], ms[1], n_up, n_m, F);
         for (auto &e : ev) cudaEventDestroy(e);
     }
 };
 
-// One exchange over peer memory; called by drone_exchange_sum when the plan has the transport enabled.
-int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t st) {
-    drone_p2p *p = x->p2p;
+static int p2p_check_in_step(drone_p2p *p) {
     if (*(volatile int *)p->h_error != 0)
         return set_error(DRONE_E_STATE,
                          "peer-memory exchange: an earlier call gave up waiting for rank %d (%s flag); the ranks are out of step",
                          *p->h_error % 100, *p->h_error >= 200 ? "down" : "up");
+    return DRONE_OK;
+}
+
+static bool p2p_rows_as_float4(const float *d_rows, int F, int ld) {
+    return (F % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_rows) & 15) == 0);
+}
+
+// Upward half, as a copy kernel of its own: my mirror rows go to their owners, whose flags the kernel's last block sets.
+int p2p_push_up(drone_xplan *x, const float *d_rows, int F, int ld, cudaStream_t st) {
+    drone_p2p *p = x->p2p;
+    const int P = x->nranks, n_up = (int)x->up_rows.size();
+    const bool vec4 = p2p_rows_as_float4(d_rows, F, ld);
+    const int nvec = vec4 ? F / 4 : F;
+    if (n_up) {
+        const int grid = p2p_grid((long long)n_up * nvec);
+        if (vec4) p2p_push_up_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error, p->d_done, p->d_peer_flag_up, p->d_need_down, P, p->epoch);
+        else p2p_push_up_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error, p->d_done, p->d_peer_flag_up, p->d_need_down, P, p->epoch);
+        DRONE_LAUNCH_CHECK("p2p_push_up_kernel");
+    }
+    return DRONE_OK;
+}
+
+// Upward half done by the caller's kernels: opens the epoch and hands out the routing tables.
+int p2p_route_begin(drone_xplan *x, int n_rows, int F, const int2 **route, float *const **peer_rows) {
+    drone_p2p *p = x->p2p;
+    if (!p) return set_error(DRONE_E_STATE, "peer-memory transport is not enabled on this exchange plan");
+    if (n_rows != x->n_local)
+        return set_error(DRONE_E_INVALID, "the exchange plan covers %d local rows, the aggregation plan has %d", x->n_local, n_rows);
+    if (F > x->max_features)
+        return set_error(DRONE_E_TOO_LARGE, "exchange of %d features on a plan made for at most %d", F, x->max_features);
+    if (p->push_pending)
+        return set_error(DRONE_E_STATE, "an aggregation already sent this plan's mirror rows up: drone_exchange_finish is due");
+    const int rc = p2p_check_in_step(p);
+    if (rc) return rc;
+    ++p->epoch;
+    p->push_pending = true;
+    *route = p->d_route;
+    *peer_rows = p->d_peer_up_recv;
+    return DRONE_OK;
+}
+
+int p2p_route_publish(drone_xplan *x, cudaStream_t st) {
+    drone_p2p *p = x->p2p;
+    if (!x->up_rows.empty()) {
+        p2p_publish_kernel<<<1, 64, 0, st>>>(p->d_peer_flag_up, p->d_need_down, x->nranks, p->epoch, p->d_error);
+        DRONE_LAUNCH_CHECK("p2p_publish_kernel");
+    }
+    return DRONE_OK;
+}
+
+// Downward half: masters wait for their mirrors' rows, add them and store the totals into the mirrors' memory; mirror
+// rows wait for the totals and take them.
+int exchange_finish_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t st) {
+    drone_p2p *p = x->p2p;
     const int P = x->nranks;
     const int n_up = (int)x->up_rows.size(), n_m = (int)x->m_rows.size();
-    const unsigned epoch = ++p->epoch;
+    const unsigned epoch = p->epoch;
+    p->push_pending = false;
     unsigned *my_flags = reinterpret_cast<unsigned *>(p->segment);
     float *my_up_recv = reinterpret_cast<float *>(p->segment + kFlagBytes);
     float *my_down_recv = reinterpret_cast<float *>(
         p->segment + kFlagBytes + align_up(x->down_rows.size() * (size_t)x->max_features * 4, 256));
-    const bool vec4 = (F % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_rows) & 15) == 0);
+    const bool vec4 = p2p_rows_as_float4(d_rows, F, ld);
     const int nvec = vec4 ? F / 4 : F;
-    PhaseTimer timer(p2p_timing_enabled(), st);
-    timer.mark();
-    if (n_up) {
-        const int grid = p2p_grid((long long)n_up * nvec);
-        if (vec4) p2p_push_up_kernel<4><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error, p->d_done, p->d_peer_flag_up, p->d_need_down, P, epoch);
-        else p2p_push_up_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, p->d_walk, n_up, nvec, p->d_peer_up_recv, p->d_error, p->d_done, p->d_peer_flag_up, p->d_need_down, P, epoch);
-        DRONE_LAUNCH_CHECK("p2p_push_up_kernel");
-    }
-    timer.mark();   // (the up flags go to the owners of my mirrors from the last block of push_up)
-    timer.mark();
     if (n_m) {
         p2p_wait_kernel<<<1, 64, 0, st>>>(my_flags, p->d_need_up, P, epoch, p->d_error, p->d_host_error, 100);
         DRONE_LAUNCH_CHECK("p2p_wait_kernel");
@@ -490,8 +545,6 @@ int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t 
         else p2p_add_push_down_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_m_rows, x->d_m_off, p->d_pairs, n_m, nvec, my_up_recv, p->d_peer_down_recv, p->d_error, p->d_done + 1, p->d_peer_flag_down, p->d_need_up, P, epoch);
         DRONE_LAUNCH_CHECK("p2p_add_push_down_kernel");
     }
-    timer.mark();   // (the down flags go to the holders of my mirrors from the last block of add_push_down)
-    timer.mark();
     if (n_up) {
         p2p_wait_kernel<<<1, 64, 0, st>>>(my_flags + P, p->d_need_down, P, epoch, p->d_error, p->d_host_error, 200);
         DRONE_LAUNCH_CHECK("p2p_wait_kernel");
@@ -500,8 +553,24 @@ int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t 
         else p2p_scatter_kernel<1><<<grid, 256, 0, st>>>(d_rows, ld, x->d_up_rows, n_up, nvec, my_down_recv, p->d_error);
         DRONE_LAUNCH_CHECK("p2p_scatter_kernel");
     }
+    return DRONE_OK;
+}
+
+// One exchange over peer memory; called by drone_exchange_sum when the plan has the transport enabled.
+int exchange_sum_p2p(drone_xplan *x, float *d_rows, int F, int ld, cudaStream_t st) {
+    drone_p2p *p = x->p2p;
+    if (p->push_pending)
+        return set_error(DRONE_E_STATE, "an aggregation already sent this plan's mirror rows up: drone_exchange_finish is due");
+    int rc = p2p_check_in_step(p);
+    if (rc) return rc;
+    ++p->epoch;
+    PhaseTimer timer(p2p_timing_enabled(), st);
     timer.mark();
-    timer.report(x->rank, n_up, n_m, F);
+    if ((rc = p2p_push_up(x, d_rows, F, ld, st))) return rc;
+    timer.mark();
+    if ((rc = exchange_finish_p2p(x, d_rows, F, ld, st))) return rc;
+    timer.mark();
+    timer.report(x->rank, (int)x->up_rows.size(), (int)x->m_rows.size(), F);
     return DRONE_OK;
 }
 

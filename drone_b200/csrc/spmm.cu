@@ -1,6 +1,7 @@
 // Host side of the aggregation: argument checks, column slicing, the choice of kernel variant and the entry points
 // of the C ABI.  The kernels are in spmm_kernels.cuh, compiled once per variant in spmm_variants_*.cu.
 #include "spmm_kernels.cuh"
+#include "exchange.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -84,6 +85,7 @@ struct CallOptions {
     int row_class = -1;
     bool unit_values = false;
     Epilogue epi;
+    drone_xplan *push_up_to = nullptr;   // the call also sends the mirror rows of Y to their owners
 };
 
 static bool operands_allow_vec4(int F, long long ldx, long long ldy, const float *X, const float *Y) {
@@ -130,6 +132,16 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
         ldx = ldy = F = Fp;
         vec4 = true;
     }
+    // The upward half of the exchange inside this call: the kernels store mirror rows into their owners' memory
+    // (rows read as float4 where they lie), or the copy kernel sends them afterwards (any other layout).
+    bool routed = false;
+    const int2 *route = nullptr;
+    float *const *peer_rows = nullptr;
+    if (opt.push_up_to) {
+        const int rc = p2p_route_begin(opt.push_up_to, p->n_rows, F, &route, &peer_rows);
+        if (rc) return rc;
+        routed = vec4 && !padded;
+    }
     const int slice = slice_width(p, F, vec4);
     const int width = slice > 0 ? slice : F;
     p->last_slice_width = slice;
@@ -151,10 +163,20 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
     a.row_class = opt.row_class;
     a.resident_per_sm = p->chunk_blocks_per_sm;
     a.gather.ldv = vec4 ? ldx / 4 : ldx;
+    if (routed) {
+        a.epi.route = route;
+        a.epi.peer_rows = peer_rows;
+        a.epi.route_nvec = F / 4;
+    }
     for (int c0 = 0; c0 < F; c0 += width) {
         a.gather.X = X + c0;
         a.Y = Y + c0;
+        a.epi.route_col0 = c0 / 4;
         const int rc = run_variant(p, s, a, vec4, width, opt.unit_values);
+        if (rc) return rc;
+    }
+    if (routed) {
+        const int rc = p2p_route_publish(opt.push_up_to, st);
         if (rc) return rc;
     }
     if (padded) {
@@ -171,6 +193,7 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
             DRONE_LAUNCH_CHECK("unpad_rows_kernel");
         }
     }
+    if (opt.push_up_to && !routed) return p2p_push_up(opt.push_up_to, caller_Y, caller_F, (int)caller_ldy, st);
     return DRONE_OK;
 }
 
@@ -219,8 +242,18 @@ int drone_spmm_ex(drone_plan *p, int orientation, int F, const float *d_X, int l
         opt.unit_values = opts->unit_values == 1;
         opt.epi.relu = opts->epilogue == DRONE_EPILOGUE_RELU;
         opt.epi.row_scale = opts->d_row_scale;
+        opt.push_up_to = opts->push_up_to;
+        DRONE_REQUIRE(!(opt.push_up_to && opt.epi.relu),
+                      "drone_spmm_ex: DRONE_EPILOGUE_RELU cannot be combined with push_up_to (the sum over the replicas comes first)");
     }
-    if (p->n_rows == 0) return DRONE_OK;
+    if (p->n_rows == 0) {
+        if (opt.push_up_to) {      // a rank without rows still takes part in the exchange that follows
+            const int2 *route = nullptr;
+            float *const *peer_rows = nullptr;
+            return p2p_route_begin(opt.push_up_to, 0, F, &route, &peer_rows);
+        }
+        return DRONE_OK;
+    }
     DRONE_REQUIRE(d_X && d_Y, "drone_spmm_ex: NULL operand");
     DRONE_REQUIRE(d_X != d_Y, "drone_spmm_ex: X and Y must not alias");
     DeviceGuard guard;

@@ -119,6 +119,13 @@ template <int A, int B> struct MinOf { static constexpr int value = A < B ? A : 
 struct Epilogue {
     const float *row_scale = nullptr;   // [n_rows] or NULL
     int relu = 0;                       // 1: negative results are stored as 0
+    // Routed rows (the aggregation that also performs the upward half of the mirror/master exchange): route[r] =
+    // {peer, row in that peer's receive area} for a row whose total another GPU forms, {-1, ..} otherwise.  A routed
+    // row is stored into the peer's memory (rows of route_nvec vectors there; this call writes vectors route_col0 ..)
+    // and not into Y.
+    const int2 *route = nullptr;        // [n_rows] or NULL
+    float *const *peer_rows = nullptr;  // [peers] base of every peer's receive area
+    int route_nvec = 0, route_col0 = 0;
 };
 
 template <int VEC>
@@ -126,6 +133,25 @@ __device__ __forceinline__ typename Vec<VEC>::type finish_row(const typename Vec
                                                               float scale) {
     if (e.row_scale == nullptr && !e.relu) return acc;
     return Vec<VEC>::finish(acc, scale, e.relu);
+}
+
+// Where a finished row goes: its row of Y, or its place in the owner's receive area (remote: the caller uses a plain
+// store, no cache policy of this GPU's L2 on a peer's address).
+template <int VEC>
+struct RowDestination {
+    typename Vec<VEC>::type *ptr;
+    bool remote;
+};
+
+template <int VEC>
+__device__ __forceinline__ RowDestination<VEC> row_destination(const Epilogue &e, float *Y, long long ldy, int row) {
+    using V = typename Vec<VEC>::type;
+    if (e.route != nullptr) {
+        const int2 r = __ldg(e.route + row);
+        if (r.x >= 0)
+            return {reinterpret_cast<V *>(e.peer_rows[r.x]) + (long long)r.y * e.route_nvec + e.route_col0, true};
+    }
+    return {reinterpret_cast<V *>(Y + (long long)row * ldy), false};
 }
 
 // Where the gathered rows come from.  Without HOT only X is used.
@@ -252,10 +278,16 @@ spmm_short_stream_kernel(const int *__restrict__ s_range_row, int n_ranges, cons
                 if ((cc[u] & kLastInRow) && (k + base + j + u < kend)) {
                     const int row = s_rows[ri];
                     const float scale = epi.row_scale ? __ldg(epi.row_scale + row) : 1.f;
-                    V *yr = reinterpret_cast<V *>(Y + (long long)row * ldy) + gl;
+                    const RowDestination<VEC> dest = row_destination<VEC>(epi, Y, ldy, row);
+                    const bool remote = dest.remote;
+                    V *yr = dest.ptr + gl;
 #pragma unroll
                     for (int p = 0; p < VPL; ++p) {
-                        if (EXACT || gl + p * G < nvec) st_stream(yr + p * G, finish_row<VEC>(acc[p], epi, scale), pol_stream);
+                        if (EXACT || gl + p * G < nvec) {
+                            const V out = finish_row<VEC>(acc[p], epi, scale);
+                            if (remote) yr[p * G] = out;
+                            else st_stream(yr + p * G, out, pol_stream);
+                        }
                         acc[p] = Vec<VEC>::zero();
                     }
                     ++ri;
@@ -404,10 +436,16 @@ spmm_chunks_kernel(const Chunk *__restrict__ chunks, int n_chunks, const int *__
             if (gi == 0) {
                 if (slot < 0) {
                     const float scale = epi.row_scale ? __ldg(epi.row_scale + row) : 1.f;
-                    V *out = reinterpret_cast<V *>(Y + (long long)row * ldy) + gl;
+                    const RowDestination<VEC> dest = row_destination<VEC>(epi, Y, ldy, row);
+                    const bool remote = dest.remote;
+                    V *out = dest.ptr + gl;
 #pragma unroll
                     for (int p = 0; p < VPL; ++p)
-                        if (EXACT || gl + p * G < nvec) st_stream(out + p * G, finish_row<VEC>(acc[p], epi, scale), pol_stream);
+                        if (EXACT || gl + p * G < nvec) {
+                            const V tot = finish_row<VEC>(acc[p], epi, scale);
+                            if (remote) out[p * G] = tot;
+                            else st_stream(out + p * G, tot, pol_stream);
+                        }
                 } else {
                     V *out = reinterpret_cast<V *>(partials + (long long)slot * nvec * VEC) + gl;
 #pragma unroll
@@ -466,13 +504,18 @@ spmm_reduce_partials_kernel(const SplitRow *__restrict__ split, int n_split,
         for (int p = 0; p < VPL; ++p) Vec<VEC>::add(acc[p], Vec<VEC>::shfl_xor(acc[p], o));
 
     const float scale = epi.row_scale ? __ldg(epi.row_scale + row) : 1.f;
-    V *yr = reinterpret_cast<V *>(Y + (long long)row * ldy);
+    const RowDestination<VEC> dest = row_destination<VEC>(epi, Y, ldy, row);
+    const bool remote = dest.remote;
+    V *yr = dest.ptr;
     if (!WIDE) {
         if (gi == 0) {
 #pragma unroll
             for (int p = 0; p < VPL; ++p) {
                 const int vi = gl + p * G;
-                if (vi < nvec) __stcs(yr + vi, finish_row<VEC>(acc[p], epi, scale));
+                if (vi < nvec) {
+                    if (remote) yr[vi] = finish_row<VEC>(acc[p], epi, scale);
+                    else __stcs(yr + vi, finish_row<VEC>(acc[p], epi, scale));
+                }
             }
         }
         return;
@@ -493,7 +536,8 @@ spmm_reduce_partials_kernel(const SplitRow *__restrict__ split, int n_split,
             if (vi < nvec) {
                 V tot = sm[vi];
                 for (int ww = 1; ww < 8; ++ww) Vec<VEC>::add(tot, sm[ww * nvec + vi]);
-                __stcs(yr + vi, finish_row<VEC>(tot, epi, scale));
+                if (remote) yr[vi] = finish_row<VEC>(tot, epi, scale);
+                else __stcs(yr + vi, finish_row<VEC>(tot, epi, scale));
             }
         }
     }

@@ -11,7 +11,7 @@ The reference's module list is this with L = 2 (cuda_gcn.cu:44-83); its layer in
 import torch
 
 from ._lib import OP_A, OP_AT
-from .graphsum import clear_mirror_rows, exchange_sum
+from .graphsum import aggregate_and_exchange, clear_mirror_rows, exchange_sum
 
 
 class GCN:
@@ -50,6 +50,17 @@ class GCN:
         elif self.worker_num > 1:
             exchange_sum(self.g.xplan, self.comm, rows)
 
+    def _aggregate_and_sync(self, op, src, out):
+        """GraphSum of one layer and direction: aggregation + mirror/master sync.  With the library's own aggregation
+        and its peer-memory transport the two are one fused sequence (mirror rows leave from the aggregation's
+        store); with a custom aggregation or sync they run one after the other."""
+        if not self._custom_aggregate and self._sync is None and self.worker_num > 1:
+            aggregate_and_exchange(self.g.plan, self.g.xplan, self.comm, op, src, out)
+            return out
+        self._aggregate(op, src, out)
+        self.sync(out)
+        return out
+
     def _aggregate(self, op, src, out, relu=False):
         if self._custom_aggregate:
             self.aggregate(op, src, out)
@@ -81,8 +92,10 @@ class GCN:
             # The mirror/master sync adds partial sums, so the ReLU can sit in the aggregation's store only when there
             # is nothing to add afterwards (one worker); with several workers it follows the sync.
             fused = relu and self.fuse_relu and self.worker_num == 1 and self._sync is None
-            self._aggregate(OP_AT, self.h[l], self.z[l], relu=fused)       # CUDAGraphSum::forward
-            self.sync(self.z[l])
+            if fused:
+                self._aggregate(OP_AT, self.h[l], self.z[l], relu=True)    # CUDAGraphSum::forward + CUDAReLU::forward
+            else:
+                self._aggregate_and_sync(OP_AT, self.h[l], self.z[l])      # CUDAGraphSum::forward with its sync
             if relu and not fused:
                 self.z[l].clamp_(min=0)                                    # CUDAReLU::forward, in place
             a = self.z[l]
@@ -103,8 +116,7 @@ class GCN:
     def backward(self):
         g = self.d_logits
         for l in range(self.n_layers - 1, -1, -1):
-            self._aggregate(OP_A, g, self.d_h[l])                          # CUDAGraphSum::backward
-            self.sync(self.d_h[l])
+            self._aggregate_and_sync(OP_A, g, self.d_h[l])                 # CUDAGraphSum::backward with its sync
             a_prev = self.z[l - 1] if l > 0 else self.x
             if l > 0:
                 d_a = torch.matmul(self.d_h[l], self.weights[l].t(), out=self.d_a[l - 1])   # CUDAMatmul::backward: dA first ...

@@ -109,6 +109,29 @@ def exchange_sum(xplan, comm, rows, stream=None):
                                         _stream_ptr(stream)))
 
 
+def exchange_finish(xplan, rows, stream=None):
+    """The rest of the exchange after an aggregation that sent the mirror rows up itself (plan.spmm(...,
+    push_up_to=xplan.handle)): masters add and send the totals down, mirror rows take them (in place)."""
+    f = rows.shape[1]
+    ld = rows.stride(0) if rows.shape[0] > 1 else max(f, rows.stride(0))
+    check(_lib.lib().drone_exchange_finish(xplan.handle, C.c_void_p(rows.data_ptr()), f, int(ld), _stream_ptr(stream)))
+
+
+def aggregate_and_exchange(plan, xplan, comm, orientation, x, out, stream=None):
+    """out = aggregation of x summed over the replicas of every vertex.  With the peer-memory transport the
+    aggregation kernels store mirror rows straight into their owners' memory (one pass less over those rows, and the
+    transfer runs beside the arithmetic); otherwise aggregation, then the exchange.  Same bits either way."""
+    if comm is None or comm.nranks == 1:
+        return plan.spmm(orientation, x, out=out, stream=stream)
+    if getattr(xplan, "p2p_enabled", False):
+        plan.spmm(orientation, x, out=out, stream=stream, push_up_to=xplan.handle)
+        exchange_finish(xplan, out, stream=stream)
+    else:
+        plan.spmm(orientation, x, out=out, stream=stream)
+        exchange_sum(xplan, comm, out, stream=stream)
+    return out
+
+
 def exchange_sum_dense(dense_plan, comm, rows, stream=None):
     """The exchange as ncclReduceScatter + ncclAllGather over the boundary buffer (in place)."""
     f = rows.shape[1]
@@ -140,8 +163,11 @@ class PipelinedAggregation:
     CUDAGraphSum::forward / backward (cuda_gcn/src/cuda/cuda_module.cu:210-307, 310-389) with the two steps
     overlapped; the reference runs them one after the other."""
 
-    def __init__(self, graph, comm, max_features, n_groups=4, p2p=True):
+    def __init__(self, graph, comm, max_features, n_groups=4, p2p=True, fused_push=True):
         self.graph, self.comm, self.n_groups = graph, comm, int(n_groups)
+        # with the peer-memory transport the aggregation of a group stores its mirror rows into their owners' memory
+        # itself, and only the downward half of the group's exchange runs on the second stream
+        self.fused_push = bool(fused_push) and p2p and comm is not None and comm.nranks > 1
         groups = row_groups(graph.host.l2g, self.n_groups)
         self.row_class = torch.as_tensor(groups, device=graph.device)
         graph.plan.set_row_classes(self.row_class, self.n_groups)
@@ -159,10 +185,16 @@ class PipelinedAggregation:
     def __call__(self, orientation, x, out):
         main = torch.cuda.current_stream(self.graph.device)
         for g in range(self.n_groups):
-            self.graph.plan.spmm(orientation, x, out=out, row_class=g)
+            if self.fused_push:
+                self.graph.plan.spmm(orientation, x, out=out, row_class=g, push_up_to=self.xplans[g].handle)
+            else:
+                self.graph.plan.spmm(orientation, x, out=out, row_class=g)
             self.ready[g].record(main)
             self.side.wait_event(self.ready[g])
-            exchange_sum(self.xplans[g], self.comm, out, stream=self.side)
+            if self.fused_push:
+                exchange_finish(self.xplans[g], out, stream=self.side)
+            else:
+                exchange_sum(self.xplans[g], self.comm, out, stream=self.side)
         self.done.record(self.side)
         main.wait_event(self.done)
         return out
@@ -182,11 +214,9 @@ class GraphSum:
         self.ModuleName, self.layer = name, layer
 
     def forward(self, training=True):
-        self.graph.plan.spmm(OP_AT, self.inp.data, out=self.out.data)
-        if self.worker_num > 1:
-            exchange_sum(self.graph.xplan, self.comm, self.out.data)
+        aggregate_and_exchange(self.graph.plan, self.graph.xplan, self.comm if self.worker_num > 1 else None, OP_AT,
+                               self.inp.data, self.out.data)
 
     def backward(self):
-        self.graph.plan.spmm(OP_A, self.out.grad, out=self.inp.grad)
-        if self.worker_num > 1:
-            exchange_sum(self.graph.xplan, self.comm, self.inp.grad)
+        aggregate_and_exchange(self.graph.plan, self.graph.xplan, self.comm if self.worker_num > 1 else None, OP_A,
+                               self.out.grad, self.inp.grad)

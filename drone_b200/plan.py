@@ -122,10 +122,13 @@ class AggregationPlan:
                                                         int(n_classes), _stream_ptr(stream)))
         self.n_classes = int(n_classes)
 
-    def spmm(self, orientation, x, out=None, stream=None, row_class=None, relu=False, row_scale=None, unit_values=False):
+    def spmm(self, orientation, x, out=None, stream=None, row_class=None, relu=False, row_scale=None, unit_values=False,
+             push_up_to=None):
         """out[r,:] = sum_k val[k]*x[col[k],:] (rows of the chosen orientation).  x: [n_rows, F] float32.
         With row_class only the rows of that class are written.  relu / row_scale / unit_values are the options of
-        drone_spmm_ex: out = max(row_scale[r] * sum, 0), and every coefficient taken as 1."""
+        drone_spmm_ex: out = max(row_scale[r] * sum, 0), and every coefficient taken as 1.  push_up_to: handle of an
+        exchange plan with the peer-memory transport; the call then also sends the mirror rows of out to their
+        owners, and drone_exchange_finish (graphsum.exchange_finish) must follow."""
         if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1):
             raise ValueError("x must be a 2-D float32 CUDA tensor with unit inner stride")
         if x.shape[0] != self.n_rows:
@@ -138,12 +141,13 @@ class AggregationPlan:
         ldx = x.stride(0) if self.n_rows > 1 else max(f, x.stride(0))
         ldy = out.stride(0) if self.n_rows > 1 else max(f, out.stride(0))
         with torch.cuda.device(self.device):
-            if relu or row_scale is not None or unit_values:
+            if relu or row_scale is not None or unit_values or push_up_to is not None:
                 if row_scale is not None and not (row_scale.is_cuda and row_scale.dtype == torch.float32 and
                                                   row_scale.is_contiguous() and row_scale.numel() == self.n_rows):
                     raise ValueError("row_scale must be a contiguous float32 CUDA tensor with one entry per row")
                 opts = SpmmOpts(EPILOGUE_RELU if relu else EPILOGUE_NONE, -1 if row_class is None else int(row_class),
-                                1 if unit_values else 0, 0, row_scale.data_ptr() if row_scale is not None else None)
+                                1 if unit_values else 0, 0, row_scale.data_ptr() if row_scale is not None else None,
+                                getattr(push_up_to, "value", push_up_to))
                 check(_lib.lib().drone_spmm_ex(self._h, int(orientation), f, _ptr(x), int(ldx), _ptr(out), int(ldy),
                                                C.byref(opts), _stream_ptr(stream)))
             elif row_class is None:

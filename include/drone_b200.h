@@ -139,16 +139,31 @@ int drone_spmm(drone_plan *plan, int orientation, int F,
  *                                    the row factor as d_row_scale; drone_degree_scales computes both factors.
  *                                    Results differ from the stored-coefficient path by rounding only.
  *   row_class                        -1: all rows; >= 0: as drone_spmm_rows.
+ *   push_up_to                       an exchange plan with the peer-memory transport enabled (drone_xplan_enable_p2p),
+ *                                    made for this plan's local rows: the call also performs the upward half of the
+ *                                    mirror/master exchange of Y.  The kernels store every finished mirror row
+ *                                    straight into its owner's memory over NVLink instead of into Y (pack kernel,
+ *                                    send and receive of GraphSum_sync_value_nccl, cuda_communicate.cu:374-409, fused
+ *                                    into the aggregation), so the transfer runs while the aggregation computes and
+ *                                    the rows are neither written locally nor read again.  drone_exchange_finish on
+ *                                    the same Y must follow on every rank; until then the mirror rows of Y are
+ *                                    unspecified.  After both calls Y holds bit for bit what drone_spmm followed by
+ *                                    drone_exchange_sum gives.  Not with DRONE_EPILOGUE_RELU (the sum over the
+ *                                    replicas comes first).  Widths that are not a multiple of 4 are aggregated
+ *                                    as usual and sent with the exchange's own copy kernel; the call sequence is
+ *                                    the same.
  * opts == NULL is drone_spmm.  Zero-initialise the struct, set row_class = -1, then set what is needed.
  */
 #define DRONE_EPILOGUE_NONE 0
 #define DRONE_EPILOGUE_RELU 1
+struct drone_xplan;
 typedef struct drone_spmm_opts {
     int          epilogue;
     int          row_class;
     int          unit_values;
     int          reserved_;
     const float *d_row_scale;
+    struct drone_xplan *push_up_to;
 } drone_spmm_opts;
 int drone_spmm_ex(drone_plan *plan, int orientation, int F,
                   const float *d_X, int ldx, float *d_Y, int ldy,
@@ -324,6 +339,15 @@ int drone_xplan_lists(const drone_xplan *plan, int *up_rows, int *down_rows);
  * :126-207, sendID_Value :296-372, apply_sum :239-249, apply_assign :264-274).
  */
 int drone_exchange_sum(drone_xplan *plan, drone_comm *comm, float *d_rows, int F, int ld, void *stream);
+
+/*
+ * The rest of an exchange whose upward half an aggregation call performed (drone_spmm_ex with push_up_to = plan):
+ * masters wait for their mirrors' rows, add them in ascending rank order and store the totals into the mirrors'
+ * memory; mirror rows take the totals (apply_sum / apply_assign and the second send of GraphSum_sync_value_nccl,
+ * cuda_communicate.cu:410-448).  Same F and rows as the aggregation call wrote.  DRONE_E_STATE when no such call
+ * precedes.  Asynchronous on `stream`, which must be the aggregation call's stream or ordered behind it.
+ */
+int drone_exchange_finish(drone_xplan *plan, float *d_rows, int F, int ld, void *stream);
 
 /*
  * Switch a plan to the peer-memory transport (one process per GPU, all GPUs in one NVLink domain): later

@@ -274,6 +274,96 @@ def _mismatched_rank(rank, world, port, ok):
         dist.destroy_process_group()
 
 
+def _fused_push_rank(rank, world, port, ok):
+    """The aggregation that sends its mirror rows up itself (push_up_to) + drone_exchange_finish against aggregation
+    followed by the whole exchange: the same bits at every width, in one piece, in column slices and in row groups."""
+    import torch.distributed as dist
+    from oracle import oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        fmax = 128
+        n, part, in_deg, out_deg, x, want_fwd, want_bwd = setup_case(oracle, world, scale=11, seed=12, f=fmax, sym=False)
+        comm = gs.Comm(rank, world)
+        for slice_width in (None, "32"):
+            if slice_width:
+                os.environ["DRONE_SLICE_WIDTH"] = slice_width
+            g = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, dev, max_features=fmax)
+            os.environ.pop("DRONE_SLICE_WIDTH", None)
+            g.plan.reserve(47, padded_rows=True)
+            g.xplan.enable_p2p(comm)
+            xl = torch.as_tensor(x[g.host.l2g], device=dev)
+            for f in (128, 64, 41, 8, 3):
+                src = xl[:, :f].contiguous()
+                for op, want in ((db.OP_AT, want_fwd), (db.OP_A, want_bwd)):
+                    plain = g.plan.spmm(op, src)
+                    gs.exchange_sum(g.xplan, comm, plain)
+                    for _ in range(3):      # call after call, no host synchronisation in between
+                        fused = torch.full((g.n_local, f), float("nan"), device=dev)
+                        g.plan.spmm(op, src, out=fused, push_up_to=g.xplan.handle)
+                        gs.exchange_finish(g.xplan, fused)
+                    torch.cuda.synchronize()
+                    assert torch.equal(fused, plain), (slice_width, f, op)
+                    assert_close_to_oracle(fused.cpu().numpy(), want[g.host.l2g][:, :f])
+            if slice_width:      # the calls above did run in slices
+                g.plan.spmm(db.OP_AT, xl[:, :64].contiguous())
+                assert g.plan.stats().last_slice_width == 32
+            # a padded leading dimension on both operands
+            wide_x = torch.zeros((g.n_local, 72), device=dev)
+            wide_x[:, :64] = xl[:, :64]
+            wide_y = torch.full((g.n_local, 72), 7.0, device=dev)
+            g.plan.spmm(db.OP_AT, wide_x[:, :64], out=wide_y[:, :64], push_up_to=g.xplan.handle)
+            gs.exchange_finish(g.xplan, wide_y[:, :64])
+            ref = g.plan.spmm(db.OP_AT, xl[:, :64].contiguous())
+            gs.exchange_sum(g.xplan, comm, ref)
+            torch.cuda.synchronize()
+            assert torch.equal(wide_y[:, :64], ref) and bool((wide_y[:, 64:] == 7.0).all())
+            # call order is checked: the rest of the exchange needs a call that sent the rows, and only one
+            with pytest.raises(db.DroneError, match="no aggregation call has sent"):
+                gs.exchange_finish(g.xplan, ref)
+            g.plan.spmm(db.OP_AT, xl[:, :64].contiguous(), out=ref, push_up_to=g.xplan.handle)
+            with pytest.raises(db.DroneError, match="drone_exchange_finish is due"):
+                gs.exchange_sum(g.xplan, comm, ref)
+            with pytest.raises(db.DroneError, match="drone_exchange_finish is due"):
+                g.plan.spmm(db.OP_AT, xl[:, :64].contiguous(), out=ref, push_up_to=g.xplan.handle)
+            gs.exchange_finish(g.xplan, ref)
+            with pytest.raises(db.DroneError, match="cannot be combined"):
+                g.plan.spmm(db.OP_AT, xl[:, :64].contiguous(), out=ref, relu=True, push_up_to=g.xplan.handle)
+            # row groups, mirror rows leaving from each group's aggregation, against the copy-kernel form
+            want_bits = {}
+            for f in (64, 41):
+                want_bits[f] = g.plan.spmm(db.OP_AT, xl[:, :f].contiguous())
+                gs.exchange_sum(g.xplan, comm, want_bits[f])
+            for fused_push in (True, False):
+                piped = gs.PipelinedAggregation(g, comm, fmax, n_groups=3, fused_push=fused_push)
+                for f in (64, 41):
+                    src = xl[:, :f].contiguous()
+                    out = torch.full((g.n_local, f), float("nan"), device=dev)
+                    for _ in range(2):
+                        piped(db.OP_AT, src, out)
+                    torch.cuda.synchronize()
+                    assert torch.equal(out, want_bits[f]), (fused_push, f)
+                piped.close()
+                g.plan.set_row_classes(None, 1)
+            dist.barrier()
+            g.xplan.close()
+        ok[rank] = 1
+        dist.barrier()
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_mirror_rows_sent_from_the_aggregation_store():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    run_ranks(_fused_push_rank, 2, (28300 + os.getpid() % 2000,))
+
+
 def test_peer_transport_setup_fails_on_every_rank_together():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
