@@ -81,6 +81,8 @@ def _declare(lib):
         "drone_plan_set_row_classes": (i, [vp, vp, i, vp]),
         "drone_spmm_rows": (i, [vp, i, i, i, vp, i, vp, i, vp]),
         "drone_spmm_host": (i, [vp, i, i, vp, vp]),
+        "drone_spmm_host_submit": (i, [vp, i, i, vp, vp, C.POINTER(C.c_longlong)]),
+        "drone_spmm_host_wait": (i, [vp, C.c_longlong]),
         "drone_spmm_static_scratch": (i, [vp, i, i, vp, i, vp, i, vp]),
         "drone_host_alloc": (i, [C.POINTER(vp), C.c_size_t]),
         "drone_host_free": (i, [vp]),

@@ -497,6 +497,9 @@ int p2p_push_up(drone_xplan *x, const float *d_rows, int F, int ld, cudaStream_t
 
 // Upward half done by the caller's kernels: opens the epoch and hands out the routing tables.
 int p2p_route_begin(drone_xplan *x, int n_rows, int F, const int2 **route, float *const **peer_rows) {
+    *route = nullptr;
+    *peer_rows = nullptr;
+    if (x->nranks == 1) return DRONE_OK;      // one rank: no mirrors, nothing to send (the caller sees no table)
     drone_p2p *p = x->p2p;
     if (!p) return set_error(DRONE_E_STATE, "peer-memory transport is not enabled on this exchange plan");
     if (n_rows != x->n_local)

@@ -869,6 +869,13 @@ int drone_plan_destroy(drone_plan *p) {
     cudaFree(p->scratch);
     cudaFree(p->stage_x);
     cudaFree(p->stage_y);
+    for (int s = 0; s < 2; ++s) {
+        cudaFree(p->queue_x[s]);
+        cudaFree(p->queue_y[s]);
+        for (cudaEvent_t e : {p->queue_in[s], p->queue_done[s], p->queue_out[s]})
+            if (e) cudaEventDestroy(e);
+    }
+    if (p->out_stream) cudaStreamDestroy(p->out_stream);
     if (p->own_stream) cudaStreamDestroy(p->own_stream);
     if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
     for (cudaEvent_t e : p->half_loaded)

@@ -124,6 +124,13 @@ struct drone_plan {
     // drone_spmm_host with pinned operands: second stream and one event per column half for the copy that runs ahead
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t half_loaded[2] = {nullptr, nullptr};
+    // drone_spmm_host_submit / _wait: a second pair of staging buffers, a stream for the copies out, and per slot the
+    // events "operand landed", "aggregation done", "result copied out"; `submitted` counts the calls queued so far
+    float *queue_x[2] = {nullptr, nullptr}, *queue_y[2] = {nullptr, nullptr};
+    size_t queue_bytes = 0;
+    cudaStream_t out_stream = nullptr;
+    cudaEvent_t queue_in[2] = {nullptr, nullptr}, queue_done[2] = {nullptr, nullptr}, queue_out[2] = {nullptr, nullptr};
+    long long submitted = 0;
     // second stream and fork/join events: the short-row kernel runs beside the chunk kernels of the same call
     cudaStream_t side_stream = nullptr;
     cudaEvent_t fork_event = nullptr, join_event = nullptr;

@@ -134,13 +134,14 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
     }
     // The upward half of the exchange inside this call: the kernels store mirror rows into their owners' memory
     // (rows read as float4 where they lie), or the copy kernel sends them afterwards (any other layout).
-    bool routed = false;
+    bool routed = false, send_after = false;
     const int2 *route = nullptr;
     float *const *peer_rows = nullptr;
     if (opt.push_up_to) {
         const int rc = p2p_route_begin(opt.push_up_to, p->n_rows, F, &route, &peer_rows);
         if (rc) return rc;
-        routed = vec4 && !padded;
+        routed = route != nullptr && vec4 && !padded;
+        send_after = route != nullptr && !routed;
     }
     const int slice = slice_width(p, F, vec4);
     const int width = slice > 0 ? slice : F;
@@ -193,7 +194,7 @@ static int spmm_impl(drone_plan *p, int orientation, int F, const float *X, long
             DRONE_LAUNCH_CHECK("unpad_rows_kernel");
         }
     }
-    if (opt.push_up_to && !routed) return p2p_push_up(opt.push_up_to, caller_Y, caller_F, (int)caller_ldy, st);
+    if (send_after) return p2p_push_up(opt.push_up_to, caller_Y, caller_F, (int)caller_ldy, st);
     return DRONE_OK;
 }
 
@@ -412,6 +413,76 @@ int drone_spmm_host(drone_plan *p, int orientation, int F, const float *h_X, flo
     if ((rc = spmm_impl(p, orientation, F, p->stage_x, F, p->stage_y, F, p->own_stream))) return rc;
     DRONE_CUDA(cudaMemcpyAsync(h_Y, p->stage_y, bytes, cudaMemcpyDeviceToHost, p->own_stream));
     DRONE_CUDA(cudaStreamSynchronize(p->own_stream));
+    return DRONE_OK;
+}
+
+// Queue of host-operand calls.  Slot s = call number mod 2 owns one pair of staging buffers; three streams carry
+// the three stages of a call (copy in, aggregation, copy out), chained by events, so that call k's operands come in
+// while call k-1 is aggregated and call k-2's result goes out: PCIe is busy in both directions at once.
+static int ensure_queue(drone_plan *p, size_t bytes) {
+    if (!p->own_stream) DRONE_CUDA(cudaStreamCreateWithFlags(&p->own_stream, cudaStreamNonBlocking));
+    if (!p->copy_stream) DRONE_CUDA(cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
+    if (!p->out_stream) DRONE_CUDA(cudaStreamCreateWithFlags(&p->out_stream, cudaStreamNonBlocking));
+    for (int s = 0; s < 2; ++s)
+        for (cudaEvent_t *e : {&p->queue_in[s], &p->queue_done[s], &p->queue_out[s]})
+            if (!*e) DRONE_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+    if (bytes <= p->queue_bytes) return DRONE_OK;
+    DRONE_CUDA(cudaDeviceSynchronize());      // calls in flight use the buffers about to be replaced
+    for (int s = 0; s < 2; ++s) {
+        cudaFree(p->queue_x[s]);
+        cudaFree(p->queue_y[s]);
+        p->queue_x[s] = p->queue_y[s] = nullptr;
+    }
+    p->queue_bytes = 0;
+    for (int s = 0; s < 2; ++s) {
+        DRONE_CUDA(cudaMalloc(&p->queue_x[s], bytes));
+        DRONE_CUDA(cudaMalloc(&p->queue_y[s], bytes));
+    }
+    p->queue_bytes = bytes;
+    return DRONE_OK;
+}
+
+int drone_spmm_host_submit(drone_plan *p, int orientation, int F, const float *h_X, float *h_Y, long long *ticket) {
+    DRONE_REQUIRE(p != nullptr, "drone_spmm_host_submit: plan is NULL");
+    DRONE_REQUIRE(orientation == DRONE_OP_A || orientation == DRONE_OP_AT, "drone_spmm_host_submit: orientation=%d",
+                  orientation);
+    DRONE_REQUIRE(p->side[orientation].ready, "drone_spmm_host_submit: orientation %d was not prepared", orientation);
+    DRONE_REQUIRE(F >= 1 && F <= 1024, "drone_spmm_host_submit: feature width F=%d outside 1..1024", F);
+    DRONE_REQUIRE(ticket != nullptr, "drone_spmm_host_submit: ticket is NULL");
+    DRONE_REQUIRE(p->n_rows == 0 || (h_X && h_Y), "drone_spmm_host_submit: NULL operand");
+    DeviceGuard guard;
+    int rc = guard.enter(p->device);
+    if (rc) return rc;
+    const long long k = p->submitted;
+    const int s = (int)(k & 1);
+    if (p->n_rows > 0) {
+        const size_t bytes = sizeof(float) * (size_t)p->n_rows * (size_t)F;
+        if ((rc = ensure_queue(p, bytes))) return rc;
+        // the slot's previous call (k - 2) must have left it: its result copied out, hence its operands consumed
+        if (k >= 2) DRONE_CUDA(cudaEventSynchronize(p->queue_out[s]));
+        DRONE_CUDA(cudaMemcpyAsync(p->queue_x[s], h_X, bytes, cudaMemcpyHostToDevice, p->copy_stream));
+        DRONE_CUDA(cudaEventRecord(p->queue_in[s], p->copy_stream));
+        DRONE_CUDA(cudaStreamWaitEvent(p->own_stream, p->queue_in[s], 0));
+        if ((rc = spmm_impl(p, orientation, F, p->queue_x[s], F, p->queue_y[s], F, p->own_stream))) return rc;
+        DRONE_CUDA(cudaEventRecord(p->queue_done[s], p->own_stream));
+        DRONE_CUDA(cudaStreamWaitEvent(p->out_stream, p->queue_done[s], 0));
+        DRONE_CUDA(cudaMemcpyAsync(h_Y, p->queue_y[s], bytes, cudaMemcpyDeviceToHost, p->out_stream));
+        DRONE_CUDA(cudaEventRecord(p->queue_out[s], p->out_stream));
+    }
+    *ticket = k;
+    p->submitted = k + 1;
+    return DRONE_OK;
+}
+
+int drone_spmm_host_wait(drone_plan *p, long long ticket) {
+    DRONE_REQUIRE(p != nullptr, "drone_spmm_host_wait: plan is NULL");
+    DRONE_REQUIRE(ticket >= 0 && ticket < p->submitted, "drone_spmm_host_wait: ticket %lld was not issued (%lld calls so far)",
+                  ticket, p->submitted);
+    if (p->n_rows == 0 || ticket + 2 < p->submitted) return DRONE_OK;     // a later submit on the slot waited for it
+    DeviceGuard guard;
+    const int rc = guard.enter(p->device);
+    if (rc) return rc;
+    DRONE_CUDA(cudaEventSynchronize(p->queue_out[ticket & 1]));
     return DRONE_OK;
 }
 

@@ -166,6 +166,20 @@ class AggregationPlan:
         check(_lib.lib().drone_spmm_host(self._h, int(orientation), int(f), C.c_void_p(xp), C.c_void_p(yp)))
         return out_host
 
+    def spmm_host_submit(self, orientation, x_host, out_host):
+        """Queue the same call without waiting (drone_spmm_host_submit); returns the ticket for spmm_host_wait.  At
+        most two calls are in flight; x_host / out_host must stay as they are until the ticket has been waited for."""
+        f = x_host.shape[1]
+        xp = x_host.data_ptr() if hasattr(x_host, "data_ptr") else x_host.ctypes.data
+        yp = out_host.data_ptr() if hasattr(out_host, "data_ptr") else out_host.ctypes.data
+        ticket = C.c_longlong(-1)
+        check(_lib.lib().drone_spmm_host_submit(self._h, int(orientation), int(f), C.c_void_p(xp), C.c_void_p(yp),
+                                                C.byref(ticket)))
+        return ticket.value
+
+    def spmm_host_wait(self, ticket):
+        check(_lib.lib().drone_spmm_host_wait(self._h, int(ticket)))
+
 
 class _DeviceArray:
     """Borrowed device memory described through the CUDA array interface."""

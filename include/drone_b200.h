@@ -221,6 +221,23 @@ int drone_spmm_host(drone_plan *plan, int orientation, int F,
                     const float *h_X, float *h_Y);
 
 /*
+ * The same with a queue, for a caller that has a series of host-operand calls to make (a batch of feature blocks,
+ * one call per layer and direction over several inputs).  drone_spmm_host_submit queues Y = op(A) X and returns a
+ * ticket without waiting; drone_spmm_host_wait returns when h_Y of that ticket is complete.  At most two calls of a
+ * plan are in flight: a third submit first waits for the call two tickets earlier.  Inside the library a call is
+ * three stages on three streams (copy in, aggregation, copy out) over two sets of staging buffers, so the operands of
+ * call k cross PCIe while call k-1 is aggregated and the result of call k-2 crosses it in the other direction.  One
+ * call alone takes as long as drone_spmm_host; a series approaches the time of the copies in one direction.
+ * h_X must not change and h_Y must not be read until the wait returns; pinned memory on both, or the copies are not
+ * asynchronous.  Calls of one plan are queued in order; results are bit-identical to drone_spmm.  Not to be mixed
+ * with other calls on the same plan while tickets are outstanding.  No counterpart in the reference, whose operands
+ * never leave the device.
+ */
+int drone_spmm_host_submit(drone_plan *plan, int orientation, int F,
+                           const float *h_X, float *h_Y, long long *ticket);
+int drone_spmm_host_wait(drone_plan *plan, long long ticket);
+
+/*
  * drone_spmm for callers that cannot allocate device memory: programs that give
  * all of it to their own pool at start-up, so that an allocation made behind
  * their back fails or fragments the pool, and threads that must never block on

@@ -381,3 +381,22 @@ def test_graphsum_over_nccl_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     run_ranks(_nccl_rank, 2, (29600 + os.getpid() % 2000,))
+
+
+def test_push_up_to_needs_the_peer_transport_and_is_nothing_on_one_rank(cuda_device, oracle):
+    """push_up_to on an exchange plan without the peer-memory transport is refused before anything is launched; on
+    a one-rank plan there is nobody to send to, and the two calls give the plain aggregation."""
+    n, part, in_deg, out_deg, x, want_fwd, _ = setup_case(oracle, 2, scale=10, seed=9, f=16)
+    g = gs.DeviceGraph(part.local_graph(0), in_deg, out_deg, cuda_device, max_features=16)
+    xl = torch.as_tensor(x[g.host.l2g], device=cuda_device)
+    with pytest.raises(db.DroneError, match="peer-memory transport is not enabled"):
+        g.plan.spmm(db.OP_AT, xl, push_up_to=g.xplan.handle)
+    with pytest.raises(db.DroneError, match="no aggregation call has sent"):
+        gs.exchange_finish(g.xplan, xl)
+    n1, part1, in1, out1, x1, want1, _ = setup_case(oracle, 1, scale=10, seed=9, f=16)
+    g1 = gs.DeviceGraph(part1.local_graph(0), in1, out1, cuda_device, max_features=16)
+    x1l = torch.as_tensor(x1[g1.host.l2g], device=cuda_device)
+    y = g1.plan.spmm(db.OP_AT, x1l, push_up_to=g1.xplan.handle)
+    gs.exchange_finish(g1.xplan, y)
+    assert torch.equal(y, g1.plan.spmm(db.OP_AT, x1l))
+    assert_close_to_oracle(y.cpu().numpy(), want1[g1.host.l2g])

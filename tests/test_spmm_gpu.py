@@ -388,6 +388,32 @@ def test_host_operand_entry_point(cuda_device, oracle):
     assert np.array_equal(yn, plan.spmm(db.OP_A, xh.to(cuda_device)).cpu().numpy())
 
 
+def test_queue_of_host_operand_calls(cuda_device, oracle):
+    """drone_spmm_host_submit / _wait: six calls on alternating operand sets and widths, two in flight; every result
+    equals the device call on the same operand bit for bit; tickets are checked."""
+    n, u, v = gg.rmat_graph(11, 16, seed=36, symmetrise=False, self_loops="add")
+    index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u.numpy(), v.numpy())
+    plan = make_plan(cuda_device, index, dst, in_deg, out_deg)
+    calls = [(db.OP_AT, 64), (db.OP_A, 64), (db.OP_AT, 41), (db.OP_A, 8), (db.OP_AT, 64), (db.OP_AT, 64)]
+    xh = [torch.as_tensor(gg.seeded_normal(50 + i, (n, f))).pin_memory() for i, (_, f) in enumerate(calls)]
+    yh = [torch.full((n, f), float("nan")).pin_memory() for _, f in calls]
+    tickets = []
+    for i, (op, f) in enumerate(calls):
+        tickets.append(plan.spmm_host_submit(op, xh[i], yh[i]))
+        if i >= 1:
+            plan.spmm_host_wait(tickets[i - 1])
+    plan.spmm_host_wait(tickets[-1])
+    assert tickets == list(range(len(calls)))
+    for i, (op, f) in enumerate(calls):
+        want = plan.spmm(op, xh[i].to(cuda_device)).cpu()
+        assert torch.equal(yh[i], want), i
+    plan.spmm_host_wait(tickets[0])                      # long finished: returns at once
+    with pytest.raises(db.DroneError, match="was not issued"):
+        plan.spmm_host_wait(len(calls))
+    w, a = oracle.spmm_csr_f64(*oracle.transpose_csr(n, n, index, dst, val), xh[0].numpy(), with_abs=True)
+    assert_close_to_oracle(yh[0].numpy(), w, a)
+
+
 def test_argument_errors(cuda_device, oracle):
     n, u, v = gg.tiny_graphs()["path5"]
     index, dst, in_deg, out_deg, val = graph_case(gg, oracle, n, u, v)
