@@ -16,6 +16,13 @@
 // run out too instead of reading rows that were never written), and the next call reports DRONE_E_STATE.  Nothing here uses TMA or cluster multicast; peers are reached with plain
 // loads and stores.
 //
+// The upward half has a second form: an aggregation call (drone_spmm_ex with push_up_to) is given this plan's route
+// table and the peers' receive areas, and its kernels store every finished mirror row where push_up would have put
+// it; a one-block kernel behind them publishes the epoch (p2p_route_begin / p2p_route_publish), and
+// drone_exchange_finish runs add_push_down and scatter.  The ordering argument below holds unchanged with "the
+// aggregation of call k+1" in the place of "push_up of call k+1", as long as that aggregation is ordered behind this
+// rank's scatter of call k (same stream, or an event between the streams).
+//
 // Why no host synchronisation is needed between calls: a rank stores into a peer's up-receive area in call k+1 only
 // after its own scatter of call k, which waited for that peer's down flag of call k, which the peer wrote after it
 // had consumed its up-receive area of call k.  Symmetrically a rank stores into a peer's down-receive area in call
