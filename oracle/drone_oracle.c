@@ -10,7 +10,13 @@
  * reference's own tests).  What it does hold, and what this oracle is pinned
  * against in tests/test_oracle.py, is the cuSPARSE SpMM known-answer case of
  * cuda_gcn/src/tools/sparse.cu:28-49 (4x4, 9 nonzeros, times a 4x3 dense) and
- * the transpose print-out case of cuda_gcn/src/tools/test.cu:47-70.
+ * the transpose print-out case of cuda_gcn/src/tools/test.cu:47-70.  Where a
+ * GPU is present the tests also run the reference's own compiled code beside it
+ * (oracle/_ref, built from the reference sources by oracle/Makefile): local
+ * numbering and coefficients of build_graph, CUDAGraphSum::forward / backward
+ * on one and two workers, the first-epoch loss of CUDAGCN::train_epoch, and
+ * the pr / cc / sssp jobs (tests/test_reference_gpu.py,
+ * tests/test_reference_jobs_gpu.py).
  *
  * The sparse x dense product itself lives in a third-party dependency that is
  * not in the reference tree: cuSPARSE (cusparseSpMM, CSR, fp32, row-major,

@@ -10,7 +10,10 @@ Backward: GraphSum (A·grad), Matmul (dA = dC·W^T first, then dW = A^T·dC; on 
 are zeroed before dW so that every vertex counts once, cuda_module.cu:50-61,88-105, and dW is summed over workers,
 cuda_communicate.cu:107-115), ReLU mask, GraphSum, Matmul.
 On one unpartitioned graph every vertex occurs once, which is what the partitioned run must reproduce.
-"parity unpinned": the reference has no fixture for any of these values.
+The reference has no fixture for any of these values.  Pinned instead against the reference's own code where a GPU
+is present: the first-epoch loss of its CUDAGCN::train_epoch (compiled from the reference sources into oracle/_ref)
+on the same graph, features, labels and starting weights equals this restatement's to 1e-5
+(tests/test_reference_gpu.py).  Gradients have no such pin and are checked against this restatement only.
 """
 import numpy as np
 import scipy.sparse as sp
