@@ -289,11 +289,14 @@ def _fused_push_rank(rank, world, port, ok):
         fmax = 128
         n, part, in_deg, out_deg, x, want_fwd, want_bwd = setup_case(oracle, world, scale=11, seed=12, f=fmax, sym=False)
         comm = gs.Comm(rank, world)
-        for slice_width in (None, "32"):
-            if slice_width:
-                os.environ["DRONE_SLICE_WIDTH"] = slice_width
+        # plans in one piece, cut into column slices, and with a table of hot rows (tagged columns)
+        for slice_width, plan_env in ((None, {}), ("32", {"DRONE_SLICE_WIDTH": "32"}),
+                                      (None, {"DRONE_HOT_MIN_ROWS": "1", "DRONE_HOT_TABLE_MB": "1"})):
+            os.environ.update(plan_env)
             g = gs.DeviceGraph(part.local_graph(rank), in_deg, out_deg, dev, max_features=fmax)
-            os.environ.pop("DRONE_SLICE_WIDTH", None)
+            for key in plan_env:
+                os.environ.pop(key, None)
+            assert (g.plan.stats().hot_rows_tagged > 0) == ("DRONE_HOT_MIN_ROWS" in plan_env)
             g.plan.reserve(47, padded_rows=True)
             g.xplan.enable_p2p(comm)
             xl = torch.as_tensor(x[g.host.l2g], device=dev)
@@ -309,6 +312,16 @@ def _fused_push_rank(rank, world, port, ok):
                     torch.cuda.synchronize()
                     assert torch.equal(fused, plain), (slice_width, f, op)
                     assert_close_to_oracle(fused.cpu().numpy(), want[g.host.l2g][:, :f])
+            # value-free coefficients with the row factor applied in the store: the scaled row is what leaves
+            scale = torch.rand(g.n_local, device=dev) + 0.5
+            src = xl[:, :64].contiguous()
+            plain = g.plan.spmm(db.OP_A, src, unit_values=True, row_scale=scale)
+            gs.exchange_sum(g.xplan, comm, plain)
+            fused = torch.full((g.n_local, 64), float("nan"), device=dev)
+            g.plan.spmm(db.OP_A, src, out=fused, unit_values=True, row_scale=scale, push_up_to=g.xplan.handle)
+            gs.exchange_finish(g.xplan, fused)
+            torch.cuda.synchronize()
+            assert torch.equal(fused, plain)
             if slice_width:      # the calls above did run in slices
                 g.plan.spmm(db.OP_AT, xl[:, :64].contiguous())
                 assert g.plan.stats().last_slice_width == 32
