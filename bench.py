@@ -513,6 +513,15 @@ def run_ours(args, cfg):
             parity["oracle_rmat13_max_rel_err"] = small_case_parity(device)
         except Exception as e:
             parity["oracle_error"] = repr(e)
+        try:      # and the timed workload itself, at full size, through its column sums
+            plan.spmm(db.OP_AT, xs[0], out=ys[0])
+            torch.cuda.synchronize()
+            parity["checksum_identity"] = checksum_report(
+                *checksum_terms(plan, db.OP_AT, xs[0], ys[0]),
+                "column sums of Y against (sum of the stored coefficients per gathered row)^T X, in double, relative to "
+                "the sum of the absolute terms; the whole %d x %d result of the timed workload" % (n, f))
+        except Exception as e:
+            parity["checksum_identity"] = {"error": repr(e)}
 
     if "cusparse" in chosen:
         try:
@@ -547,7 +556,8 @@ def run_ours(args, cfg):
             line["cusparse"] = {"error": repr(e)}
     if parity:
         parity["tolerance"] = 1e-5
-        parity["ok"] = all(v <= 1e-5 for k, v in parity.items() if k.endswith("_err") or k.endswith("_diff"))
+        parity["ok"] = all(v <= 1e-5 for k, v in parity.items() if k.endswith("_err") or k.endswith("_diff")) and \
+            bool(parity.get("checksum_identity", {"ok": True}).get("ok", False))
         line["parity"] = parity
 
     if args.pagerank_iters > 0:      # the path at F = 1 on the workload's own graph, for comparison with several GPUs
@@ -590,6 +600,42 @@ def run_ours(args, cfg):
         raise SystemExit("bench.py: parity check failed: %r" % parity)
 
 
+def checksum_terms(plan, op, x, y, own_rows=None):
+    """A property of the product that needs no second implementation and no small graph: summed over its rows,
+    Y = M X has the column sums  1^T Y = (M^T 1)^T X,  and M^T 1 (the sum of the stored coefficients per gathered
+    row) comes straight from the plan's CSR arrays.  Returns three float64 vectors of length F: the sums of the rows of
+    y (own_rows: only those rows), s^T x with s = M^T 1, and sum_u |s[u]| |x[u, :]| (the magnitude to judge the
+    difference of the first two against).  On several GPUs the three are summed over the ranks before comparing."""
+    _, col, val = plan.csr(op)
+    n, f = x.shape
+    s = torch.zeros(n, dtype=torch.float64, device=x.device)
+    piece = 1 << 27
+    for k0 in range(0, col.numel(), piece):
+        s.index_add_(0, col[k0:k0 + piece].long(), val[k0:k0 + piece].double())
+    del col, val
+    want = torch.zeros(f, dtype=torch.float64, device=x.device)
+    scale = torch.zeros(f, dtype=torch.float64, device=x.device)
+    got = torch.zeros(f, dtype=torch.float64, device=x.device)
+    rows = 1 << 21
+    for r0 in range(0, n, rows):
+        xb = x[r0:r0 + rows].double()
+        sb = s[r0:r0 + rows, None]
+        want += (sb * xb).sum(0)
+        scale += (sb.abs() * xb.abs()).sum(0)
+        yb = y[r0:r0 + rows]
+        if own_rows is not None:
+            yb = yb * own_rows[r0:r0 + rows, None]
+        got += yb.sum(0, dtype=torch.float64)
+    return got, want, scale
+
+
+def checksum_report(got, want, scale, what):
+    rel = float(((got - want).abs() / scale.clamp_min(1e-300)).max())
+    if rel != rel:      # a rank could not form its terms
+        return {"max_rel_diff": None, "tolerance": 1e-5, "ok": False, "what": what}
+    return {"max_rel_diff": rel, "tolerance": 1e-5, "ok": bool(rel <= 1e-5), "what": what}
+
+
 def large_graph_timing(device, workload, steps=10):
     """The aggregation on one of the large directed R-MAT graphs (the workload the roofline target is stated on),
     one GPU, device-resident operands rotating over two buffer sets; plus 20 PageRank power iterations (F = 1) on the
@@ -618,6 +664,15 @@ def large_graph_timing(device, workload, steps=10):
            "nnzF_per_s": nnz * f / (ms * 1e-3), "algorithmic_bytes": b_alg,
            "algorithmic_GBps": b_alg / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": b_alg / (ms * 1e-3) / 1e9 / peak,
            "peak": peak, "peak_source": peak_src, "hot_row_table": bool(plan.stats().hot_rows_tagged)}
+    try:      # the full-size result, checked through its column sums
+        step(0)
+        torch.cuda.synchronize()
+        out["checksum_identity"] = checksum_report(
+            *checksum_terms(plan, db.OP_AT, xs[0], ys[0]),
+            "column sums of Y against (sum of the stored coefficients per gathered row)^T X, in double, relative to "
+            "the sum of the absolute terms; the whole %d x %d result" % (n, f))
+    except Exception as e:
+        out["checksum_identity"] = {"error": repr(e)}
     del xs, ys
     plan.close()
     torch.cuda.empty_cache()
@@ -1193,6 +1248,22 @@ def run_partitioned_workload(args, cfg, device, rank, world, comm, sync, headlin
     xchg = torch.tensor([float(np.median(blocks_x)) / args.steps, spmm_ms], device=device)
     dist.all_reduce(xchg, op=dist.ReduceOp.MAX)
 
+    # the full-size result of one step, checked through its column sums over all ranks: rows a rank owns (masters and
+    # unreplicated vertices) against the coefficient sums of every rank's own part applied to that rank's operand
+    step(0)
+    torch.cuda.synchronize()
+    try:
+        own = torch.as_tensor(graph.host.mirror2worker < 0, device=device)
+        terms = torch.stack(checksum_terms(graph.plan, db.OP_AT, xs[0], ys[0], own_rows=own))
+    except Exception as e:      # every rank still joins the reduction below
+        print("bench.py: rank %d could not form its checksum terms: %r" % (rank, e), file=sys.stderr)
+        terms = torch.full((3, f), float("nan"), dtype=torch.float64, device=device)
+    dist.all_reduce(terms)
+    checksum = checksum_report(terms[0], terms[1], terms[2],
+                               "column sums of the owned rows of Y over all ranks against the sum over the parts of "
+                               "(coefficient sums per gathered row)^T X of that part, in double, relative to the sum of "
+                               "the absolute terms; aggregation + exchange on the timed graph")
+
     # PageRank power iterations (F = 1) over the same partition: pull along in-edges + the same exchange per iteration
     pr_result = None
     if args.pagerank_iters > 0:
@@ -1308,6 +1379,7 @@ def run_partitioned_workload(args, cfg, device, rank, world, comm, sync, headlin
                              "upward half is part of the aggregation when mirror_rows_sent_from_aggregation_store",
                      "dense_boundary_rows": dense.boundary_rows() if dense is not None else None},
         "gpu_launches": int(g[:, 3].sum()), "clocks": clocks, "setup_s": setup_s, "partition_seconds": part_s,
+        "checksum_identity": checksum,
     }
     if e2e is not None:
         line["e2e"] = {"value": nnz_total * f / e2e, "unit": "nnz*F/s", "h2d_bytes_per_step": int(g[:, 0].sum()) * f * 4,
