@@ -186,6 +186,53 @@ def test_column_slices_chosen_by_size(cuda_device, oracle):
     assert auto.stats().last_slice_width == 64 and whole.stats().last_slice_width == 0
 
 
+def test_full_size_workload_through_its_properties(cuda_device):
+    """The benchmark's own workload at its full size (R-MAT scale 20, edge factor 16, symmetrised, self-loops;
+    1,048,576 rows, about 32 M nonzeros, F = 64), where the CPU oracle would take minutes: checked through properties
+    that hold at any size.  (1) Column sums: 1^T (M X) = (M^T 1)^T X with M^T 1 summed in double from the plan's own
+    CSR arrays.  (2) Sampled rows against a double-precision evaluation of their CSR rows.  (3) The graph is
+    symmetric and in- and out-degrees coincide, so both orientations are the same matrix: the two results agree to
+    rounding.  (4) Linearity in X.  (5) Two calls give the same bits."""
+    dev = cuda_device
+    n, u, v = gg.rmat_graph(20, 16, seed=20261126, device=dev, symmetrise=True, self_loops="add")
+    index, dst = gg.csr_by_source(u, v, n)
+    in_deg, out_deg = gg.degrees(u, v, n)
+    assert torch.equal(in_deg, out_deg) and dst.numel() > 30_000_000
+    plan = db.AggregationPlan(index, dst, in_degree=in_deg, out_degree=out_deg)
+    f = 64
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    x = torch.randn((n, f), device=dev, generator=gen)
+    x2 = torch.randn((n, f), device=dev, generator=gen)
+    results = {}
+    for op in (db.OP_AT, db.OP_A):
+        y = plan.spmm(op, x)
+        assert torch.equal(y, plan.spmm(op, x))                                   # (5)
+        rowptr, col, val = plan.csr(op)
+        s = torch.zeros(n, dtype=torch.float64, device=dev).index_add_(0, col.long(), val.double())
+        want = (s[:, None] * x.double()).sum(0)
+        scale = (s.abs()[:, None] * x.double().abs()).sum(0)
+        got = y.sum(0, dtype=torch.float64)
+        assert float(((got - want).abs() / scale).max()) <= 1e-9                  # (1)
+        # (2) the longest row, the first rows and a spread of others, term by term in double
+        lengths = rowptr[1:] - rowptr[:-1]
+        picks = torch.cat([lengths.argmax().reshape(1), torch.arange(0, 8, device=dev),
+                           torch.arange(0, n, n // 50, device=dev)]).unique().tolist()
+        for r in picks:
+            k0, k1 = int(rowptr[r]), int(rowptr[r + 1])
+            terms = val[k0:k1].double()[:, None] * x[col[k0:k1].long()].double()
+            bound = REL_TOL * terms.abs().sum(0) + 1e-30
+            assert bool(((y[r].double() - terms.sum(0)).abs() <= bound).all()), (op, r, k1 - k0)
+        lin = plan.spmm(op, 2.0 * x - x2)                                          # (4)
+        y2 = plan.spmm(op, x2)
+        assert float((lin - (2.0 * y - y2)).abs().max()) <= REL_TOL * float(lin.abs().max())
+        results[op] = y
+        del rowptr, col, val, s
+    diff = (results[db.OP_AT] - results[db.OP_A]).abs().max()                     # (3)
+    assert float(diff) <= REL_TOL * float(results[db.OP_A].abs().max())
+    plan.close()
+
+
 @pytest.mark.parametrize("f", [3, 32, 41, 64, 256])
 def test_relu_and_row_scale_in_the_store(cuda_device, oracle, f):
     """drone_spmm_ex: Y = max(row_scale * (A x), 0) equals the same steps applied to drone_spmm's output, bit for
