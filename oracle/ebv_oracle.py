@@ -12,12 +12,29 @@ Pinned against the reference's own partitioner, compiled from EBV_mpi.cpp over s
 its MPI and gflags calls (oracle/ref_shim/ebv, `make -C oracle ref_ebv`) and run as P ranks:
 tests/golden/ebv_golden.npz holds the files it wrote.  Where no rank has more than 16 edges
 (std::sort keeps input order there) this restatement reproduces them exactly; on larger
-inputs the C++ partitioner, which this restatement equals in stable order, reproduces them
-byte for byte once it sorts with std::sort too (tests/test_partition.py).
+inputs it reproduces them edge for edge, owners and replica counts included, when it orders
+the shares with std::sort too (std_sort_ties, through oracle/std_sort_order.cpp), and so does
+the C++ partitioner, byte for byte (tests/test_partition.py).
 """
 
 
-def ebv_partition(n_vertices, edges, n_parts, keep_self_loops=True):
+def _std_sort(share, deg):
+    """share ordered as std::sort orders the reference's records (oracle/std_sort_order.cpp)."""
+    import ctypes
+    import os
+    import numpy as np
+    lib = ctypes.CDLL(os.path.join(os.path.dirname(os.path.abspath(__file__)), "_build", "libebv_std_sort.so"))
+    u = np.array([e[0] for e in share], np.int32)
+    v = np.array([e[1] for e in share], np.int32)
+    key = np.array([deg[e[0]] + deg[e[1]] for e in share], np.int32)
+    ptr = ctypes.POINTER(ctypes.c_int)
+    lib.ebv_std_sort(u.ctypes.data_as(ptr), v.ctypes.data_as(ptr), key.ctypes.data_as(ptr), ctypes.c_long(len(share)))
+    return list(zip(u.tolist(), v.tolist()))
+
+
+def ebv_partition(n_vertices, edges, n_parts, keep_self_loops=True, std_sort_ties=False):
+    """std_sort_ties: order every rank's share with std::sort itself (what the reference's binary does) instead of
+    the stable sort; the parts then equal the reference's edge for edge."""
     P = n_parts
     share = [[] for _ in range(P)]
     for i, (u, v) in enumerate(edges):
@@ -29,7 +46,10 @@ def ebv_partition(n_vertices, edges, n_parts, keep_self_loops=True):
         for u, v in share[r]:
             deg[u] = deg.get(u, 0) + 1
             deg[v] = deg.get(v, 0) + 1
-        share[r] = sorted(share[r], key=lambda e: deg[e[0]] + deg[e[1]])   # stable
+        if std_sort_ties:
+            share[r] = _std_sort(share[r], deg)
+        else:
+            share[r] = sorted(share[r], key=lambda e: deg[e[0]] + deg[e[1]])   # stable
     has = [set() for _ in range(P)]
     edge_count = [0] * P
     vertex_count = [0] * P

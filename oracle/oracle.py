@@ -16,8 +16,11 @@ _SO = os.path.join(_HERE, "_build", "libdrone_oracle.so")
 
 def build(force=False):
     """Compile the oracle with the committed Makefile (gcc, a few seconds)."""
-    srcs = [os.path.join(_HERE, f) for f in ("drone_oracle.c", "pagerank_oracle.c", "minprop_oracle.c", "Makefile")]
-    if force or not os.path.exists(_SO) or any(os.path.getmtime(s) > os.path.getmtime(_SO) for s in srcs):
+    srcs = [os.path.join(_HERE, f) for f in ("drone_oracle.c", "pagerank_oracle.c", "minprop_oracle.c",
+                                             "std_sort_order.cpp", "Makefile")]
+    sort_so = os.path.join(_HERE, "_build", "libebv_std_sort.so")
+    if force or not os.path.exists(_SO) or not os.path.exists(sort_so) or \
+            any(os.path.getmtime(s) > min(os.path.getmtime(_SO), os.path.getmtime(sort_so)) for s in srcs):
         subprocess.run(["make", "-C", _HERE, "-B" if force else "-s"], check=True,
                        stdout=subprocess.DEVNULL)
     return _SO

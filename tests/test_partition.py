@@ -190,6 +190,27 @@ def test_restatement_equals_reference_partitioner_without_ties_in_play(tmp_path)
     assert written_files(p, str(tmp_path)) == ref_files
 
 
+@pytest.mark.parametrize("name", ["uniform_p3", "skewed_p2", "skewed_p8"])
+def test_python_restatement_equals_reference_partitioner(name):
+    """The pure-Python restatement with the reference's tie order: the edges of every part in the reference's order,
+    and owners / replica counts that give the reference's Master and Mirror files."""
+    from oracle import oracle
+    oracle.build()
+    n, u, v, parts, keep, ref_files = golden_case(name)
+    ref_parts, ref_owner, ref_rep = ebv_oracle.ebv_partition(n, list(zip(u.tolist(), v.tolist())), parts, keep,
+                                                             std_sort_ties=True)
+    for q in range(parts):
+        lines = ref_files["G.%d" % q].decode().split("\n")[:-1]
+        assert ["%d %d" % e for e in ref_parts[q]] == lines
+    masters = {}
+    for q in range(parts):
+        for line in ref_files["Master.%d" % q].decode().split("\n")[:-1]:
+            ids = [int(t) for t in line.split()]
+            masters[ids[0]] = (q, len(ids))          # vertex -> (owner, replicas)
+    want = {x: (ref_owner[x], ref_rep[x]) for x in range(n) if ref_rep[x] > 1}
+    assert masters == want
+
+
 @pytest.mark.parametrize("name", GOLDEN_CASES[1:])
 def test_stable_order_cuts_as_well_as_reference(name):
     """The default (stable) order changes which of several equally ranked edges goes first, not the quality of the cut:
