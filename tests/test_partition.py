@@ -241,6 +241,12 @@ def test_reference_partitioner_live(tmp_path):
         ref_files = oracle.reference_ebv_partition(n, u, v, 3, keep, str(tmp_path / ("ref%d" % keep)))
         p = pt.ebv_partition(n, u, v, 3, keep_self_loops=keep, std_sort_ties=True)
         assert written_files(p, str(tmp_path / ("mine%d" % keep))) == ref_files
+    # a million edges of an R-MAT graph over 8 ranks: batches of the full 1000 edges, long runs of equal degree sums
+    n, u, v = gg.rmat_graph(16, 16, seed=78, symmetrise=False, self_loops="add")
+    u, v = u.numpy(), v.numpy()
+    ref_files = oracle.reference_ebv_partition(n, u, v, 8, True, str(tmp_path / "ref_rmat"))
+    p = pt.ebv_partition(n, u, v, 8, keep_self_loops=True, std_sort_ties=True)
+    assert written_files(p, str(tmp_path / "mine_rmat")) == ref_files
 
 
 @pytest.mark.parametrize("name", ["uniform_p3", "skewed_p4_blocks"])
